@@ -1,0 +1,88 @@
+"""Host re-packer: canonical / reference-tiled / b200 formats, checked against the
+oracle's numpy restatement and against a slow, literal reading of the b200 layout."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import quant_oracle as qo
+from tilus_b200 import dtypes as D
+from tilus_b200 import packing as P
+
+
+@pytest.mark.parametrize("b", range(1, 9))
+def test_canonical_and_ref_tiled_match_oracle(b):
+    rng = np.random.default_rng(10 + b)
+    codes = rng.integers(0, 1 << b, size=(32, 64), dtype=np.uint8)
+    t = torch.from_numpy(codes)
+    np.testing.assert_array_equal(P.pack_canonical(t, b).numpy(), qo.pack_canonical(codes, b))
+    np.testing.assert_array_equal(P.pack_ref_tiled(t, b).numpy(), qo.pack_ref_tiled(codes, b))
+    np.testing.assert_array_equal(
+        P.unpack_canonical(torch.from_numpy(qo.pack_canonical(codes, b)), b, 32, 64).numpy(), codes
+    )
+    np.testing.assert_array_equal(
+        P.unpack_ref_tiled(torch.from_numpy(qo.pack_ref_tiled(codes, b)), b, 32, 64).numpy(), codes
+    )
+
+
+def _literal_b200(codes, dt):
+    """Bit-by-bit construction of the b200 layout from its written description."""
+    b = dt.nbits
+    K, N = codes.shape
+    KB, NT = K // 512, N // 16
+    out = np.zeros(K * N * b // 32, dtype=np.uint64)
+    planes = P.PLANES[b]
+    for nt in range(NT):
+        for kb in range(KB):
+            blk = (nt * KB + kb) * b * 2 * 32 * 4
+            for half in range(2):
+                for r in range(8):
+                    n = nt * 16 + half * 8 + r
+                    for j in range(4):
+                        lane = r * 4 + j
+                        for c in range(4):
+                            k0 = kb * 512 + j * 128 + c * 32
+                            for h in range(16):
+                                for e in range(2):
+                                    q = int(codes[k0 + 2 * h + e, n])
+                                    if dt.kind == D.KIND_INT:
+                                        q ^= 1 << (b - 1)
+                                    lo, base = b, 0
+                                    for p in planes:
+                                        lo -= p
+                                        per = 16 // p
+                                        v = base + h // per
+                                        f = h % per
+                                        field = (q >> lo) & ((1 << p) - 1)
+                                        widx = blk + ((v * 2 + half) * 32 + lane) * 4 + c
+                                        out[widx] |= np.uint64(field << (16 * e + f * p))
+                                        base += p
+    return out.astype(np.uint32).view(np.uint8)
+
+
+@pytest.mark.parametrize("dt", [D.uint1b, D.uint2b, D.int3b, D.uint4b, D.int4b, D.uint5b, D.float6_e3m2,
+                                D.int7b, D.uint8, D.int8], ids=lambda d: d.name)
+def test_b200_layout_literal(dt):
+    rng = np.random.default_rng(dt.nbits)
+    codes = rng.integers(0, 1 << dt.nbits, size=(1024, 32), dtype=np.uint8)
+    got = P.interleave(torch.from_numpy(codes), dt).numpy()
+    assert got.size == codes.size * dt.nbits // 8
+    np.testing.assert_array_equal(got, _literal_b200(codes, dt))
+    back = P.deinterleave(torch.from_numpy(got), dt, 1024, 32).numpy()
+    np.testing.assert_array_equal(back, codes)
+
+
+def test_b200_column_shards_are_contiguous():
+    dt = D.uint4b
+    rng = np.random.default_rng(0)
+    codes = rng.integers(0, 16, size=(512, 64), dtype=np.uint8)
+    full = P.interleave(torch.from_numpy(codes), dt)
+    for n0, n1 in ((0, 32), (32, 64), (16, 48)):
+        part = P.interleave(torch.from_numpy(np.ascontiguousarray(codes[:, n0:n1])), dt)
+        assert torch.equal(P.shard_columns(full, dt, 512, 64, n0, n1), part)
+
+
+def test_shape_check():
+    with pytest.raises(ValueError):
+        P.interleave(torch.zeros(256, 16, dtype=torch.uint8), D.uint4b)
+    with pytest.raises(ValueError):
+        P.interleave(torch.zeros(512, 24, dtype=torch.uint8), D.uint4b)

@@ -1,0 +1,3 @@
+"""B200-native weight-only quantized matmul (drop-in for the reference's
+examples/quantization/matmul_a16wx.py operator surface)."""
+from .dtypes import *  # noqa: F401,F403
