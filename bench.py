@@ -1,0 +1,351 @@
+"""Benchmark of the weight-only quantized matmul hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+Headline workload (one GPU): decode GEMV, M=1, K=N=8192, uint4 codes with zero point 8,
+group 128, fp16 scales - the "u4 g128" decode configuration the metric is quoted on.
+One step = one pass over R distinct layers of that shape (R * weights > L2, so every
+launch streams its weights from HBM); the R launches are replayed from a CUDA graph.
+`value` is algorithmic GB/s: (packed weights + scales + activations + output) bytes of
+all launches divided by the device time of the timed region.  With N > 1 GPUs every rank
+runs the same per-GPU workload on its own column shard (weak scaling, no collective on
+the data path) and `value` is the aggregate.
+
+The JSON line also carries: `roofline` (HBM, for the GEMV kernel), `e2e` (same metric
+through QuantizedLinear.forward with pinned host activations copied in and the result
+copied out every call), `cpu_baseline` (the CPU oracle - the reference's PyTorch
+dequantize + matmul semantics - timed on this host), `clocks`, `gpu_launches`, and an
+`extra` sweep (other bit widths, M=16, and the M=4096 prefill GEMM in TFLOP/s).
+
+`--impl reference` times the CPU dequantize + matmul path alone (the reference operator's
+semantics on the host cores), on the same workload and metric.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+M, K, N, GROUP, NBITS = 1, 8192, 8192, 128, 4
+WORKLOAD = "decode_gemv_u4_g128_M1_K8192_N8192"
+METRIC = "quant-GEMM HBM GB/s (u4 g128, M=1, K=N=8192)"
+
+
+def _peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(hbm_gbs=float(p["hbm_gbs"]), tflops=float(p.get("bf16_tflops", 0.0)),
+                    tflops_sustained=float(p.get("bf16_tflops_sustained", 0.0)), source="measured")
+    return dict(hbm_gbs=6650.0, tflops=1590.0, tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.proc = None
+        self.gpu_index = gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.gpu_index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                smax.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def _cpu_gemv_seconds(prob, repeats: int) -> float:
+    """The oracle's dequantize + matmul (reference semantics) on the host cores."""
+    from oracle import quant_oracle as qo
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    a, codes, scales = prob["a"].numpy(), prob["codes"].numpy(), prob["scales"].numpy()
+    qo.quantized_matmul(a, codes, scales, prob["dtype"], prob["group_size"], prob["zero_point"])  # warm
+    t0 = time.perf_counter()
+    for _ in range(repeats):
+        qo.quantized_matmul(a, codes, scales, prob["dtype"], prob["group_size"], prob["zero_point"])
+    return (time.perf_counter() - t0) / repeats
+
+
+def run_reference(args) -> None:
+    from tilus_b200 import dtypes, synth
+
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    prob = synth.make_problem(M, N, K, dtypes.uint4b, GROUP, seed=0)
+    nbytes = synth.gemm_bytes(M, N, K, NBITS, GROUP)
+    for _ in range(max(args.warmup, 1)):
+        _cpu_gemv_seconds(prob, 1)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        _cpu_gemv_seconds(prob, 1)
+    dt = (time.perf_counter() - t0) / args.steps
+    val = nbytes / dt / 1e9
+    cores = os.cpu_count() or 1
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "l2": "n/a (CPU)"},
+        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": cores, "kind": "port",
+                         "sample": "one full M=1 K=N=8192 u4 g128 dequantize+matmul per step (oracle, torch CPU)"},
+        "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def _time_graph(graph, reps: int) -> float:
+    """Device milliseconds of `reps` replays, CUDA events on the current stream."""
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(reps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1)
+
+
+def _make_layers(dt, m, n, k, group, count, dev, seed=0, scale_range=(0.005, 0.02)):
+    from tilus_b200 import QuantizedLinear, float16, synth
+
+    layers, acts = [], []
+    for i in range(count):
+        prob = synth.make_problem(m, n, k, dt, group, seed=seed + i, scale_range=scale_range)
+        layer = QuantizedLinear(float16, dt, group, k, n, zero_point=prob["zero_point"]).to(dev)
+        layer.load_codes(prob["codes"].to(dev), prob["scales"].to(dev))
+        layers.append(layer)
+        acts.append(prob["a"].to(dev))
+    return layers, acts
+
+
+def _capture(layers, acts):
+    outs = [None] * len(layers)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):  # warm on the capture stream: its workspace exists before capture
+        for layer, a in zip(layers, acts):
+            layer(a)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=side):
+        for i, (layer, a) in enumerate(zip(layers, acts)):
+            outs[i] = layer(a)
+    return g, outs
+
+
+def _sweep_entry(dt, m, n, k, group, dev, reps, scale_range=(0.005, 0.02)):
+    """GB/s and TFLOP/s of one shape, layers rotated so the weights stream from HBM."""
+    from tilus_b200 import synth
+
+    wbytes = k * n * dt.nbits // 8
+    count = max(2, min(16, (300 * 2**20 + wbytes - 1) // wbytes))
+    layers, acts = _make_layers(dt, m, n, k, group, count, dev, seed=100, scale_range=scale_range)
+    g, _ = _capture(layers, acts)
+    _time_graph(g, 3)
+    ms = _time_graph(g, reps) / (reps * count)
+    nbytes = synth.gemm_bytes(m, n, k, dt.nbits, group)
+    del layers, acts, g
+    torch.cuda.empty_cache()
+    return {"us": ms * 1e3, "gbs": nbytes / (ms * 1e-3) / 1e9, "tflops": synth.gemm_flops(m, n, k) / (ms * 1e-3) / 1e12}
+
+
+def run_b200(args) -> None:
+    import torch.distributed as dist
+
+    from tilus_b200 import dtypes, synth
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    peaks = _peaks()
+    dt = dtypes.uint4b
+    R = 10  # distinct layers per step: 10 x 33.5 MB of weights = 335 MB > 126 MB L2
+    layers, acts = _make_layers(dt, M, N, K, GROUP, R, dev, seed=1000 * rank)
+    graph, outs = _capture(layers, acts)
+    nbytes = synth.gemm_bytes(M, N, K, NBITS, GROUP)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        graph.replay()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    # keep the region long enough for a few clock samples
+    inner = max(1, int(0.4 / (R * 6e-6 * args.steps)))
+    barrier()
+    ms = _time_graph(graph, args.steps * inner)
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    launches = args.steps * inner * R
+    per_launch_s = ms * 1e-3 / launches
+    value = world * nbytes / per_launch_s / 1e9
+
+    # ---- end to end through the public module, host buffers in and out --------------
+    host_in = [a.cpu().pin_memory() for a in acts]
+    host_out = torch.empty(M, N, dtype=torch.float16).pin_memory()
+    dev_in = torch.empty(M, K, dtype=torch.float16, device=dev)
+
+    def e2e_step():
+        for layer, h in zip(layers, host_in):
+            dev_in.copy_(h, non_blocking=True)
+            c = layer(dev_in)
+            host_out.copy_(c, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    e2e_steps = max(args.steps, 5)
+    for _ in range(e2e_steps):
+        e2e_step()
+    torch.cuda.synchronize()
+    e2e_s = (time.perf_counter() - t0) / (e2e_steps * R)
+    t = torch.tensor([e2e_s], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_val = world * nbytes / float(t.item()) / 1e9
+
+    if rank != 0:
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+
+    # ---- correctness of what was timed ---------------------------------------------
+    from oracle import quant_oracle as qo
+
+    prob0 = synth.make_problem(M, N, K, dt, GROUP, seed=0)
+    ref = qo.quantized_matmul(prob0["a"].numpy(), prob0["codes"].numpy(), prob0["scales"].numpy(), dt, GROUP, 8)
+    got = outs[0].float().cpu().numpy()
+    rel = float(abs(got - ref.astype("float32")).max() / abs(ref.astype("float32")).max())
+
+    # ---- CPU baseline (bounded sample) -----------------------------------------------
+    cpu_s = _cpu_gemv_seconds(prob0, 5)
+    cpu_baseline = {"value": nbytes / cpu_s / 1e9, "unit": "GB/s", "cores": os.cpu_count() or 1, "kind": "port",
+                    "sample": "5 full M=1 K=N=8192 u4 g128 dequantize+matmul calls (oracle, torch CPU threads)"}
+
+    # ---- extra sweep -------------------------------------------------------------------
+    extra = {}
+    if world == 1 and not args.no_sweep:
+        del graph, layers, acts
+        torch.cuda.empty_cache()
+        for d in (dtypes.uint1b, dtypes.uint2b, dtypes.uint3b, dtypes.uint6b, dtypes.uint8):
+            r = _sweep_entry(d, 1, N, K, GROUP, dev, 20)
+            extra[f"decode_{d.short_name}_M1"] = {"us": round(r["us"], 3), "gbs": round(r["gbs"], 1),
+                                                  "hbm_frac": round(r["gbs"] / peaks["hbm_gbs"], 4)}
+        r = _sweep_entry(dtypes.uint4b, 16, 8192, 8192, GROUP, dev, 20)
+        extra["decode_u4_M16"] = {"us": round(r["us"], 3), "gbs": round(r["gbs"], 1),
+                                  "hbm_frac": round(r["gbs"] / peaks["hbm_gbs"], 4)}
+        r = _sweep_entry(dtypes.uint4b, 16, 4096, 4096, GROUP, dev, 20)
+        extra["config0_u4_M16_K4096_N4096"] = {"us": round(r["us"], 3), "gbs": round(r["gbs"], 1),
+                                               "hbm_frac": round(r["gbs"] / peaks["hbm_gbs"], 4)}
+        if not args.no_prefill:
+            r = _sweep_entry(dtypes.int4b, 4096, 28672, 8192, GROUP, dev, 2)
+            extra["prefill_i4_M4096_K8192_N28672"] = {
+                "ms": round(r["us"] / 1e3, 4), "tflops": round(r["tflops"], 1),
+                "tensor_frac_of_measured_burst": round(r["tflops"] / peaks["tflops"], 4) if peaks["tflops"] else None}
+
+    achieved = nbytes / per_launch_s / 1e9
+    line = {
+        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "layers_per_step": R, "replays_per_step": inner,
+                   "l2": f"inputs larger than L2: {R} distinct weight sets, {R * K * N // 2 // 2**20} MiB, rotated",
+                   "sharding": "one column shard of this shape per GPU, no data-path collective"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                     "kernel": "skinny_kernel<u4 zp8, MT=1>", "bytes_per_launch": nbytes,
+                     "us_per_launch": per_launch_s * 1e6},
+        "cpu_baseline": cpu_baseline,
+        "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": R * M * K * 2,
+                "d2h_bytes_per_step": R * M * N * 2, "us_per_call": e2e_s * 1e6},
+        "gpu_launches": launches,
+        "clocks": clocks,
+        "parity": {"rel_err_vs_oracle": rel, "tolerance": 1e-2},
+        "extra": extra,
+    }
+    print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-sweep", action="store_true", help="skip the extra dtype / shape sweep")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the M=4096 prefill entry of the sweep")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

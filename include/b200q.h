@@ -1,0 +1,108 @@
+/* b200q - B200 (sm_100a) weight-only quantized matmul, C ABI.
+ *
+ *   C[M, N] (fp16) = A[M, K] (fp16) x dequant(Bq[K, N]),   W[k, n] = fp16_rn(value(q[k, n]) * s[k / group, n])
+ *
+ * This library replaces, for that one operator, the launch entry the reference JIT
+ * generates per kernel: `tilus_launch(int32 m_size, void_p a_ptr, void_p b_ptr,
+ * void_p scale_ptr, void_p c_ptr)` exported through tvm_ffi as "launch"
+ * (python/tilus/hidet/backend/codegen.py:650-660, :1021-1025 of the reference; called from
+ * python/tilus/lang/instantiated_script.py:824-858 and, for this operator, from
+ * examples/quantization/matmul_a16wx.py:535-548).  N, K, the weight dtype and the group
+ * size, which the reference bakes into each generated kernel, are explicit arguments
+ * here.  All pointers are device pointers; `stream` is a cudaStream_t passed as void*
+ * (NULL = the default stream) and replaces the reference's implicit environment stream
+ * (python/tilus/hidet/include/tilus/stream.h:12-16).  Nothing here allocates device memory except
+ * where a function says so; the caller owns every buffer, including the workspace that
+ * replaces the reference's process-global zero-restored pool
+ * (python/tilus/hidet/include/tilus/context.h:30-42, :97-131).
+ *
+ * Every function returns a status code (0 = ok); no exception crosses this boundary.
+ */
+#ifndef B200Q_H_
+#define B200Q_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  B200Q_OK = 0,
+  B200Q_ERR_INVALID_ARG = 1,    /* null / misaligned pointer, non-positive size */
+  B200Q_ERR_UNSUPPORTED = 2,    /* dtype, zero point, shape or group size not covered */
+  B200Q_ERR_WORKSPACE = 3,      /* workspace missing or smaller than b200q_workspace_bytes */
+  B200Q_ERR_CUDA = 4,           /* a CUDA runtime call failed; see b200q_last_cuda_error */
+  B200Q_ERR_DEVICE_TIMEOUT = 5  /* a bounded device-side wait gave up; see b200q_device_status */
+};
+
+/* Weight dtype tag: kind << 16 | nbits << 8 | exponent_bits << 4 | mantissa_bits,
+ * kind 0 = unsigned integer, 1 = two's-complement integer, 2 = float (sign/exponent/mantissa,
+ * bias 2^(e-1)-1, all exponent codes finite when e < 5).  These are the reference's
+ * uintNb / intNb / floatN_eXmY types (python/tilus/hidet/ir/dtypes/integer_subbyte.py:66-98,
+ * floats_subbyte.py:89-109). */
+#define B200Q_WTYPE(kind, nbits, e, m) (((kind) << 16) | ((nbits) << 8) | ((e) << 4) | (m))
+
+/* Activation / output dtype tags. */
+enum { B200Q_F16 = 0 };
+
+/* Kernel selection made by the static shape table (replaces the reference's autotuner,
+ * python/tilus/lang/instantiated_script.py:700-801).  Filled by b200q_plan; may be edited
+ * and passed to b200q_gemm_planned for experiments. */
+typedef struct b200q_plan {
+  int32_t kernel;        /* 0 = split-K mma.sync path (M <= 16 per pass), 1 = tcgen05 path */
+  int32_t m_tiles;       /* kernel 0: 8-row activation tiles per pass (1 or 2) */
+  int32_t splits;        /* split-K factor S */
+  int32_t ctas_per_split;/* kernel 0: column ranges P; grid = S * P */
+  int32_t smem_bytes;    /* dynamic shared memory per CTA */
+  int32_t tile_m;        /* kernel 1: activation rows per CTA tile (multiple of 16, <= 256) */
+  int32_t stages;        /* kernel 1: pipeline depth */
+  int32_t passes;        /* launches needed to cover M */
+  uint64_t workspace_bytes;
+} b200q_plan_t;
+
+/* Library / weight-layout versions.  The layout version tags the private interleaved
+ * weight format produced by the host re-packer (tilus_b200/packing.py). */
+int b200q_version(void);
+int b200q_layout_version(void);
+const char* b200q_status_string(int status);
+/* Last CUDA runtime error code seen by this thread inside the library (cudaError_t). */
+int b200q_last_cuda_error(void);
+
+/* Static shape -> tile table for the current device.  Replaces the reference's per-shape
+ * autotuning and dispatch table (python/tilus/lang/instantiated_script.py:327-358, :700-801). */
+int b200q_plan(int M, int N, int K, int wtype, int zero_point, int group, b200q_plan_t* plan);
+
+/* Bytes of workspace b200q_gemm needs for this problem.  The workspace must be zeroed
+ * once by the caller; every call leaves it zeroed again (as the reference's
+ * `requires_clean` global tensors do, python/tilus/lang/instantiated_script.py +
+ * python/tilus/hidet/include/tilus/context.h:97-117).  One workspace per stream. */
+size_t b200q_workspace_bytes(int M, int N, int K, int wtype, int zero_point, int group);
+
+/* C = A x dequant(Bq).  a: fp16 [M, K] (row stride lda elements), bq: b200-packed weights,
+ * scales: fp16 [K/group, N], c: fp16 [M, N] (row stride ldc).  Replaces tilus_launch for
+ * QuantizedMatmul (examples/quantization/matmul_a16wx.py:231-405). */
+int b200q_gemm(const void* a, int lda, const void* bq, const void* scales, void* c, int ldc, int M, int N, int K,
+               int wtype, int zero_point, int group, int act_dtype, void* workspace, size_t workspace_bytes,
+               void* stream);
+
+/* Same, with the kernel selection supplied by the caller. */
+int b200q_gemm_planned(const void* a, int lda, const void* bq, const void* scales, void* c, int ldc, int M, int N,
+                       int K, int wtype, int zero_point, int group, int act_dtype, void* workspace,
+                       size_t workspace_bytes, void* stream, const b200q_plan_t* plan);
+
+/* W[K, N] (fp16, row-major) = dequantized weights, bit-exact with the reference's
+ * cast-then-scale (examples/quantization/matmul_a16wx.py:316-320; cast kernel
+ * python/tilus/kernels/cast.py:27-55). */
+int b200q_dequantize(const void* bq, const void* scales, void* w, int N, int K, int wtype, int zero_point, int group,
+                     void* stream);
+
+/* Reads the device status header of a workspace (synchronises `stream`): status[0] is 0 or
+ * B200Q_ERR_DEVICE_TIMEOUT, status[1..3] say which wait gave up.  Clears the header. */
+int b200q_device_status(void* workspace, int32_t status[4], void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200Q_H_ */

@@ -1,0 +1,78 @@
+"""The C-ABI library loads, exports every symbol include/b200q.h declares, validates
+arguments and plans shapes - all without a GPU (no compute calls here)."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from tilus_b200 import _lib, ops
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from tilus_b200 import build
+
+    build.build()
+    return _lib.load()
+
+
+def test_header_symbols_are_exported_and_bound(lib):
+    header = open(os.path.join(ROOT, "include", "b200q.h")).read()
+    declared = set(re.findall(r"\b(b200q_[a-z_]+)\s*\(", header))
+    assert declared, "no declarations found"
+    assert declared == set(_lib.SYMBOLS), (declared ^ set(_lib.SYMBOLS))
+    for name in declared:
+        assert hasattr(lib, name), name
+
+
+def test_versions_and_strings(lib):
+    from tilus_b200 import packing
+
+    assert lib.b200q_version() >= 100
+    assert lib.b200q_layout_version() == packing.LAYOUT_VERSION
+    assert lib.b200q_status_string(0) == b"ok"
+    for st in range(1, 6):
+        assert lib.b200q_status_string(st)
+
+
+def test_plan_static_table():
+    p = ops.plan(1, 8192, 8192, "uint4b", 8, 128)
+    assert p["kernel"] == 0 and p["splits"] * p["ctas_per_split"] <= 148 * 2
+    assert p["workspace_bytes"] >= 256 + 8192 * 4
+    p16 = ops.plan(16, 4096, 4096, "uint4b", 8, 128)
+    assert p16["m_tiles"] == 2 and p16["smem_bytes"] <= 227 * 1024
+    # per-channel scales, float weights
+    assert ops.plan(4, 4096, 4096, "float6_e3m2", 0, 4096)["passes"] == 1
+
+
+def test_rejects_bad_problems(lib):
+    pl = _lib.Plan()
+    u4 = (0 << 16) | (4 << 8)
+    assert lib.b200q_plan(1, 8192, 8192, u4, 8, 128, ctypes.byref(pl)) == _lib.ST_OK
+    assert lib.b200q_plan(1, 8192, 8192, u4, 3, 128, ctypes.byref(pl)) == _lib.ST_UNSUPPORTED  # zero point
+    assert lib.b200q_plan(1, 8200, 8192, u4, 8, 128, ctypes.byref(pl)) == _lib.ST_UNSUPPORTED  # N % 16
+    assert lib.b200q_plan(1, 8192, 8000, u4, 8, 128, ctypes.byref(pl)) == _lib.ST_UNSUPPORTED  # K % 512
+    assert lib.b200q_plan(1, 8192, 8192, u4, 8, 48, ctypes.byref(pl)) == _lib.ST_UNSUPPORTED   # group % 32
+    assert lib.b200q_plan(0, 8192, 8192, u4, 8, 128, ctypes.byref(pl)) == _lib.ST_INVALID_ARG
+    assert lib.b200q_plan(1, 8192, 8192, (2 << 16) | (6 << 8) | (3 << 4) | 1, 0, 128, ctypes.byref(pl)) \
+        == _lib.ST_UNSUPPORTED  # float6 with e+m != 5
+    assert lib.b200q_workspace_bytes(1, 8192, 8000, u4, 8, 128) == 0
+    # null pointers are refused before anything is launched
+    assert lib.b200q_gemm(None, 8192, None, None, None, 8192, 1, 8192, 8192, u4, 8, 128, 0, None, 0, None) \
+        == _lib.ST_INVALID_ARG
+    assert lib.b200q_dequantize(None, None, None, 8192, 8192, u4, 8, 128, None) == _lib.ST_INVALID_ARG
+
+
+def test_ops_refuse_cpu_tensors():
+    import torch
+
+    a = torch.zeros(1, 512, dtype=torch.float16)
+    bq = torch.zeros(512 * 16 // 2, dtype=torch.uint8)
+    sc = torch.ones(4, 16, dtype=torch.float16)
+    with pytest.raises(ValueError):
+        ops.quantized_matmul(a, bq, sc, "uint4b", 128, 8)
+    with pytest.raises(ValueError):
+        ops.dequantize(bq, sc, "uint4b", 128, 8)

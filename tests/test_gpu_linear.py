@@ -1,0 +1,71 @@
+"""QuantizedLinear (the reference's operator surface) on the GPU, against the oracle."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import quant_oracle as qo
+from tilus_b200 import QuantizedLinear, float16
+from tilus_b200 import dtypes as D
+from tilus_b200 import packing
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("dt", [D.int4b, D.int3b, D.int6b, D.int8, D.float6_e3m2, D.float4_e2m1, D.float3_e1m1,
+                                D.float8_e5m2], ids=lambda d: d.name)
+@pytest.mark.parametrize("m", [1, 16, 33])
+def test_load_and_quantize_forward(dt, m):
+    """Mirrors the reference example's own check (examples/quantization/matmul_a16wx.py:590-607)
+    and tightens it: the kernel output must match the oracle's quantize -> dequantize -> matmul."""
+    torch.manual_seed(0)
+    k, n, group = 1024, 256, 128
+    layer = QuantizedLinear(x_dtype=float16, w_dtype=dt, group_size=group, in_features=k, out_features=n).cuda()
+    a = ((torch.rand(m, k) - 0.5) / np.sqrt(k)).to(torch.float16)
+    b = ((torch.rand(k, n) - 0.5) / np.sqrt(k)).to(torch.float16)
+    layer.load_and_quantize(b.T.contiguous())
+    c = layer(a.cuda())
+    torch.cuda.synchronize()
+    assert c.shape == (m, n) and c.dtype == torch.float16 and c.is_cuda
+
+    codes, scales = qo.quantize_weight(b.T.contiguous().numpy(), dt, group)
+    np.testing.assert_array_equal(layer.codes().cpu().numpy(), codes)
+    np.testing.assert_array_equal(layer.scales.data.cpu().numpy().view(np.uint16), scales.view(np.uint16))
+    w = qo.dequantize(codes, scales, dt, group)
+    np.testing.assert_array_equal(layer.dequantized_weight().cpu().numpy().view(np.uint16), w.view(np.uint16))
+    ref = qo.gemm_fp16(a.numpy(), w).astype(np.float64)
+    got = c.cpu().numpy().astype(np.float64)
+    assert np.abs(got - ref).max() / np.abs(ref).max() <= 1e-2
+    # the reference example's own (loose) criterion against the unquantized product
+    if dt.nbits >= 6:
+        torch.testing.assert_close(c.cpu(), (a.float() @ b.float()).half(), atol=1e-2, rtol=1e-2)
+
+
+def test_load_packed_reference_formats():
+    torch.manual_seed(1)
+    k, n, group = 512, 64, 128
+    dt = D.int4b
+    codes = torch.randint(0, 16, (k, n), dtype=torch.int32).to(torch.uint8)
+    scales = (torch.rand(k // group, n) * 0.015 + 0.005).to(torch.float16)
+    a = torch.randn(4, k).to(torch.float16)
+    ref = qo.quantized_matmul(a.numpy(), codes.numpy(), scales.numpy(), dt, group).astype(np.float64)
+    for layout, storage in (
+        ("canonical", torch.from_numpy(qo.pack_canonical(codes.numpy(), 4))),
+        ("ref_tiled", torch.from_numpy(qo.pack_ref_tiled(codes.numpy(), 4))),
+        ("k_major", torch.from_numpy(qo.pack_along_k(codes.numpy(), 4))),
+    ):
+        layer = QuantizedLinear(float16, dt, group, k, n).cuda()
+        layer.load_packed(storage.cuda(), scales.cuda(), layout=layout)
+        got = layer(a.cuda()).cpu().numpy().astype(np.float64)
+        assert np.abs(got - ref).max() / np.abs(ref).max() <= 1e-2, layout
+
+
+def test_state_dict_round_trip():
+    k, n = 512, 32
+    layer = QuantizedLinear(float16, D.int4b, 128, k, n).cuda()
+    layer.load_and_quantize(torch.randn(n, k))
+    sd = layer.state_dict()
+    assert int(sd["layout_version"]) == packing.LAYOUT_VERSION
+    other = QuantizedLinear(float16, D.int4b, 128, k, n).cuda()
+    other.load_state_dict(sd)
+    x = torch.randn(2, k, dtype=torch.float16, device="cuda")
+    assert torch.equal(layer(x), other(x))

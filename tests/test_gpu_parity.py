@@ -1,0 +1,165 @@
+"""GPU parity tests: the CUDA library, called through its C ABI (ctypes), against the CPU
+oracle on the same seeded inputs.  Dequantized weights must match bit for bit; GEMM
+outputs within rel-err 1e-2 (fp32 accumulate, fp16 out), the tolerance the task states."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import quant_oracle as qo
+from tilus_b200 import dtypes as D
+from tilus_b200 import ops, packing, synth, variants
+
+pytestmark = pytest.mark.gpu
+
+REL_TOL = 1e-2
+
+
+def _dev():
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    return torch.device("cuda:0")
+
+
+def _cases():
+    out = []
+    for dt in variants.supported_weight_dtypes():
+        out.append((dt, 0))
+        if dt.kind == D.KIND_UINT:
+            out.append((dt, 1 << (dt.nbits - 1)))
+    return out
+
+
+def _rel_err(c, ref):
+    c = c.astype(np.float64)
+    ref = ref.astype(np.float64)
+    return np.abs(c - ref).max() / max(np.abs(ref).max(), 1e-30)
+
+
+def _run(prob, M_override=None, plan_override=None):
+    dev = _dev()
+    dt, g, zp = prob["dtype"], prob["group_size"], prob["zero_point"]
+    bq = packing.interleave(prob["codes"], dt).to(dev)
+    sc = prob["scales"].to(dev)
+    a = prob["a"].to(dev)
+    c = ops.quantized_matmul(a, bq, sc, dt, g, zp, plan_override=plan_override)
+    torch.cuda.synchronize()
+    return c.cpu().numpy(), bq, sc
+
+
+@pytest.mark.parametrize("dt,zp", _cases(), ids=lambda x: getattr(x, "name", str(x)))
+@pytest.mark.parametrize("group", [32, 128, 1024])
+def test_dequantize_bit_exact(dt, zp, group):
+    dev = _dev()
+    K, N = 1024, 64
+    prob = synth.make_problem(1, N, K, dt, group, seed=group + dt.nbits, symmetric_unsigned=False)
+    codes = prob["codes"]
+    # make sure every code occurs
+    codes.view(-1)[: 1 << dt.nbits] = torch.arange(1 << dt.nbits, dtype=torch.int32).to(torch.uint8)
+    if dt.is_float() and dt.exponent_nbits == 5:
+        tbl = np.abs(qo.decode_table(dt))
+        bad = torch.from_numpy(~(tbl <= dt.max_value))
+        codes[bad[codes.long()]] = 0
+    bq = packing.interleave(codes, dt).to(dev)
+    w = ops.dequantize(bq, prob["scales"].to(dev), dt, group, zp).cpu().numpy()
+    want = qo.dequantize(codes.numpy(), prob["scales"].numpy(), dt, group, zp)
+    np.testing.assert_array_equal(w.view(np.uint16), want.view(np.uint16))
+
+
+@pytest.mark.parametrize("dt,zp", _cases(), ids=lambda x: getattr(x, "name", str(x)))
+def test_gemm_small_all_variants(dt, zp):
+    prob = synth.make_problem(5, 64, 1024, dt, 128, seed=3, symmetric_unsigned=False)
+    prob["zero_point"] = zp
+    c, _, _ = _run(prob)
+    ref = qo.quantized_matmul(prob["a"].numpy(), prob["codes"].numpy(), prob["scales"].numpy(), dt, 128, zp)
+    assert _rel_err(c, ref) <= REL_TOL
+
+
+@pytest.mark.parametrize("M", [1, 2, 7, 8, 9, 16, 17, 40])
+def test_gemm_ragged_m(M):
+    prob = synth.make_problem(M, 128, 2048, D.uint4b, 128, seed=M)
+    c, _, _ = _run(prob)
+    ref = qo.quantized_matmul(prob["a"].numpy(), prob["codes"].numpy(), prob["scales"].numpy(), D.uint4b, 128, 8)
+    assert c.shape == (M, 128)
+    assert _rel_err(c, ref) <= REL_TOL
+
+
+@pytest.mark.parametrize("splits,ctas", [(1, 1), (1, 5), (2, 3), (4, 8), (4, 37)])
+def test_gemm_split_k_shapes_and_clean_workspace(splits, ctas):
+    dev = _dev()
+    M, N, K = 3, 272, 2048
+    prob = synth.make_problem(M, N, K, D.int4b, 128, seed=11)
+    dt = D.int4b
+    bq = packing.interleave(prob["codes"], dt).to(dev)
+    ws = torch.zeros(ops.workspace_bytes(M, N, K, dt, 0, 128), dtype=torch.uint8, device=dev)
+    ref = qo.quantized_matmul(prob["a"].numpy(), prob["codes"].numpy(), prob["scales"].numpy(), dt, 128, 0)
+    for _ in range(2):  # second call runs on the workspace the first one left behind
+        c = ops.quantized_matmul(prob["a"].to(dev), bq, prob["scales"].to(dev), dt, 128, 0, workspace=ws,
+                                 plan_override=dict(splits=splits, ctas_per_split=ctas))
+        torch.cuda.synchronize()
+        assert _rel_err(c.cpu().numpy(), ref) <= REL_TOL
+        assert int(ws.count_nonzero()) == 0, "workspace not restored to zero"
+
+
+def test_config0_m16_k4096_n4096_u4():
+    prob = synth.make_problem(16, 4096, 4096, D.uint4b, 128, seed=0)
+    c, bq, sc = _run(prob)
+    w = ops.dequantize(bq, sc, D.uint4b, 128, 8).cpu().numpy()
+    want_w = qo.dequantize(prob["codes"].numpy(), prob["scales"].numpy(), D.uint4b, 128, 8)
+    np.testing.assert_array_equal(w.view(np.uint16), want_w.view(np.uint16))
+    ref = qo.gemm_fp16(prob["a"].numpy(), want_w)
+    assert _rel_err(c, ref) <= REL_TOL
+
+
+@pytest.mark.parametrize("dt", [D.uint1b, D.uint2b, D.uint3b, D.uint4b, D.uint6b, D.uint8], ids=lambda d: d.name)
+def test_config1_decode_m1_k8192_n8192(dt):
+    prob = synth.make_problem(1, 8192, 8192, dt, 128, seed=0)
+    c, _, _ = _run(prob)
+    ref = qo.quantized_matmul(prob["a"].numpy(), prob["codes"].numpy(), prob["scales"].numpy(), dt, 128,
+                              prob["zero_point"])
+    assert _rel_err(c, ref) <= REL_TOL
+
+
+@pytest.mark.parametrize("dt", [D.float6_e3m2, D.int3b], ids=lambda d: d.name)
+@pytest.mark.parametrize("M", [1, 4, 16, 64, 256])
+def test_config3_per_channel(dt, M):
+    K = N = 4096
+    prob = synth.make_problem(M, N, K, dt, K, seed=0, scale_range=(0.5, 2.0))
+    c, _, _ = _run(prob)
+    ref = qo.quantized_matmul(prob["a"].numpy(), prob["codes"].numpy(), prob["scales"].numpy(), dt, K, 0)
+    assert _rel_err(c, ref) <= REL_TOL
+
+
+def test_linearity_full_size():
+    """Size-independent property at full decode size: C(a1 + a2) == C(a1) + C(a2) up to
+    fp16 output rounding, and scaling a column's scales by 2 doubles that column."""
+    dev = _dev()
+    N = K = 8192
+    prob = synth.make_problem(2, N, K, D.uint4b, 128, seed=5)
+    bq = packing.interleave(prob["codes"], D.uint4b).to(dev)
+    sc = prob["scales"].to(dev)
+    a = prob["a"].to(dev)
+    a = (a * 0.25).to(torch.float16)
+    a_sum = (a[0:1].float() + a[1:2].float()).to(torch.float16)
+    c12 = ops.quantized_matmul(a, bq, sc, D.uint4b, 128, 8).float()
+    cs = ops.quantized_matmul(a_sum, bq, sc, D.uint4b, 128, 8).float()
+    torch.cuda.synchronize()
+    scale_ref = c12.abs().max().item()
+    assert (cs[0] - (c12[0] + c12[1])).abs().max().item() <= 1e-2 * scale_ref
+    sc2 = sc.clone()
+    sc2[:, ::2] *= 2
+    c2 = ops.quantized_matmul(a, bq, sc2, D.uint4b, 128, 8).float()
+    torch.cuda.synchronize()
+    assert (c2[:, ::2] - 2 * c12[:, ::2]).abs().max().item() <= 4e-3 * scale_ref
+    assert torch.equal(c2[:, 1::2], c12[:, 1::2])
+
+
+def test_errors_are_loud():
+    dev = _dev()
+    prob = synth.make_problem(1, 64, 1024, D.uint4b, 128, seed=1)
+    bq = packing.interleave(prob["codes"], D.uint4b).to(dev)
+    with pytest.raises(Exception):
+        ops.quantized_matmul(prob["a"], bq, prob["scales"].to(dev), D.uint4b, 128, 8)  # CPU activations
+    with pytest.raises(Exception):
+        ops.quantized_matmul(prob["a"].to(dev), bq, prob["scales"].to(dev), D.uint4b, 128, 3)  # bad zero point
+    small_ws = torch.zeros(256, dtype=torch.uint8, device=dev)
+    with pytest.raises(Exception):
+        ops.quantized_matmul(prob["a"].to(dev), bq, prob["scales"].to(dev), D.uint4b, 128, 8, workspace=small_ws)

@@ -1,0 +1,119 @@
+"""QuantizedLinear: the reference's operator surface
+(examples/quantization/matmul_a16wx.py:408-548) over the sm_100a kernels.
+
+Same constructor arguments, parameters and methods as the reference class:
+
+    QuantizedLinear(x_dtype, w_dtype, group_size, in_features, out_features)
+      .quantized_weight : uint8[out_features * in_features * nbits / 8]
+      .scales           : x_dtype[in_features / group_size, out_features]
+      .load_and_quantize(weight[out_features, in_features])
+      .forward(x[M, in_features]) -> [M, out_features]
+
+``quantized_weight`` holds this library's interleaved layout (packing.LAYOUT_VERSION),
+not the reference's mma-fragment tiling; ``load_packed`` converts from the reference's
+formats.  The forward pass always runs the CUDA library; there is no CPU path.
+"""
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+from . import ops, packing, quantize
+from .dtypes import KIND_UINT, act_dtype, float16, weight_dtype
+
+
+class QuantizedLinear(nn.Module):
+    def __init__(self, x_dtype, w_dtype, group_size: int, in_features: int, out_features: int,
+                 zero_point: int | None = None):
+        super().__init__()
+        x_dtype = act_dtype(x_dtype)
+        w_dtype = weight_dtype(w_dtype)
+        if x_dtype is not float16:
+            raise NotImplementedError("only float16 activations are implemented")
+        # The reference class demands float or signed types ("symmetric quantization",
+        # matmul_a16wx.py:421-423) while its kernel takes any 1-8 bit type (:163-165).
+        # Unsigned types are accepted here with an explicit zero point.
+        if zero_point is None:
+            zero_point = 0
+        if w_dtype.kind != KIND_UINT and zero_point != 0:
+            raise ValueError("a zero point is only meaningful for unsigned weight types")
+        assert in_features % group_size == 0, "in_features must be divisible by group_size"
+        assert in_features * out_features * w_dtype.nbits % 8 == 0
+        packing.check_shape(in_features, out_features)
+        if group_size % 32 != 0:
+            raise ValueError("group_size must be a multiple of 32")
+
+        self.x_dtype = x_dtype
+        self.w_dtype = w_dtype
+        self.group_size = group_size
+        self.in_features = in_features
+        self.out_features = out_features
+        self.zero_point = int(zero_point)
+
+        self.quantized_weight = nn.Parameter(
+            torch.empty(out_features * in_features * w_dtype.nbits // 8, dtype=torch.uint8), requires_grad=False
+        )
+        self.scales = nn.Parameter(
+            torch.empty(in_features // group_size, out_features, dtype=torch.float16), requires_grad=False
+        )
+        self.register_buffer("layout_version", torch.tensor(packing.LAYOUT_VERSION, dtype=torch.int32))
+
+    # -- loading ---------------------------------------------------------------------
+    def load_and_quantize(self, weight: torch.Tensor):
+        """Quantize a dense weight[out_features, in_features] and store it packed."""
+        assert (self.out_features, self.in_features) == tuple(weight.shape), "weight shape mismatch"
+        if self.w_dtype.kind == KIND_UINT:
+            raise ValueError("load_and_quantize is symmetric: use a signed or float weight type "
+                             "(unsigned codes come in through load_codes / load_packed)")
+        dev = self.quantized_weight.device
+        codes, scales = quantize.quantize_weight(weight.to(dev), self.w_dtype, self.group_size)
+        self.load_codes(codes, scales)
+
+    def load_codes(self, codes: torch.Tensor, scales: torch.Tensor):
+        """codes uint8[in_features, out_features] (type-native codes), scales [K/group, N]."""
+        dev = self.quantized_weight.device
+        packed = packing.interleave(codes.to(dev), self.w_dtype)
+        with torch.no_grad():
+            self.quantized_weight.copy_(packed)
+            self.scales.copy_(scales.to(dev).reshape(self.scales.shape))
+
+    def load_packed(self, storage: torch.Tensor, scales: torch.Tensor, layout: str = "canonical"):
+        """Load weights packed by the reference: ``canonical`` (tilus.Tensor storage of the
+        [K, N] matrix), ``ref_tiled`` (the reference QuantizedLinear's quantized_weight) or
+        ``k_major`` (bit-dense along K per column)."""
+        K, N, b = self.in_features, self.out_features, self.w_dtype.nbits
+        if layout == "canonical":
+            codes = packing.unpack_canonical(storage, b, K, N)
+        elif layout == "ref_tiled":
+            codes = packing.unpack_ref_tiled(storage, b, K, N)
+        elif layout == "k_major":
+            codes = packing.unpack_canonical(storage, b, N, K).t().contiguous()
+        elif layout == "b200":
+            with torch.no_grad():
+                self.quantized_weight.copy_(storage.reshape(-1))
+                self.scales.copy_(scales.reshape(self.scales.shape))
+            return
+        else:
+            raise ValueError(f"unknown layout {layout!r}")
+        self.load_codes(codes, scales)
+
+    def codes(self) -> torch.Tensor:
+        """Type-native codes uint8[in_features, out_features] (inverse of load_codes)."""
+        return packing.deinterleave(self.quantized_weight.data, self.w_dtype, self.in_features, self.out_features)
+
+    def dequantized_weight(self) -> torch.Tensor:
+        """fp16 [in_features, out_features]: the weights forward() multiplies by."""
+        return ops.dequantize(self.quantized_weight.data, self.scales.data, self.w_dtype, self.group_size,
+                              self.zero_point)
+
+    # -- compute ---------------------------------------------------------------------
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, self.in_features)
+        out = ops.quantized_matmul(x2, self.quantized_weight.data, self.scales.data, self.w_dtype, self.group_size,
+                                   self.zero_point)
+        return out.reshape(*lead, self.out_features)
+
+    def extra_repr(self) -> str:
+        return (f"in_features={self.in_features}, out_features={self.out_features}, w_dtype={self.w_dtype.name}, "
+                f"group_size={self.group_size}, zero_point={self.zero_point}")

@@ -1,0 +1,116 @@
+"""Low-level operators over the C ABI: quantized_matmul, dequantize, plan.
+
+Tensors are torch CUDA tensors used only as device memory; the stream is torch's
+current stream.  Mirrors the reference's kernel call
+``kernel(m_size, n_size, k_size, a_ptr, b_ptr, scale_ptr, c_ptr)``
+(examples/quantization/matmul_a16wx.py:539-547) with the dtype / group arguments that
+the reference fixes at JIT time made explicit.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+from .dtypes import weight_dtype
+from .packing import BLOCK_K, BLOCK_N
+
+_workspaces = {}
+
+
+def _stream_ptr(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def workspace_bytes(M: int, N: int, K: int, w_dtype, zero_point: int = 0, group_size: int = 128) -> int:
+    dt = weight_dtype(w_dtype)
+    n = _lib.load().b200q_workspace_bytes(M, N, K, dt.code, zero_point, group_size)
+    if n == 0:
+        raise _lib.B200QError(_lib.ST_UNSUPPORTED, f"no kernel for M={M} N={N} K={K} {dt.name} zp={zero_point} g={group_size}")
+    return int(n)
+
+
+def get_workspace(device, nbytes: int) -> torch.Tensor:
+    """Per (device, stream) zero-initialised workspace, grown on demand.  The kernels
+    leave it zeroed, so it is cleared only when (re)allocated."""
+    key = (torch.device(device).index, _stream_ptr(device))
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def plan(M: int, N: int, K: int, w_dtype, zero_point: int = 0, group_size: int = 128) -> dict:
+    dt = weight_dtype(w_dtype)
+    pl = _lib.Plan()
+    _lib.check(_lib.load().b200q_plan(M, N, K, dt.code, zero_point, group_size, ctypes.byref(pl)))
+    return pl.as_dict()
+
+
+def quantized_matmul(a: torch.Tensor, bq: torch.Tensor, scales: torch.Tensor, w_dtype, group_size: int,
+                     zero_point: int = 0, out: torch.Tensor | None = None, workspace: torch.Tensor | None = None,
+                     plan_override: dict | None = None) -> torch.Tensor:
+    """C[M, N] = A[M, K] x dequant(Bq).  ``bq`` is the b200-packed weight (packing.interleave),
+    ``scales`` is fp16 [K/group, N]."""
+    lib = _lib.load()
+    dt = weight_dtype(w_dtype)
+    if not (a.is_cuda and bq.is_cuda and scales.is_cuda):
+        raise ValueError("quantized_matmul needs CUDA tensors (there is no CPU path)")
+    if a.dtype != torch.float16 or scales.dtype != torch.float16:
+        raise TypeError("activations and scales must be float16")
+    if a.dim() != 2 or a.stride(1) != 1:
+        raise ValueError("a must be a 2-D tensor with unit inner stride")
+    M, K = a.shape
+    G, N = scales.shape
+    if G * group_size != K or not scales.is_contiguous():
+        raise ValueError("scales must be a contiguous [K/group_size, N] tensor")
+    if bq.dtype != torch.uint8 or bq.numel() * 8 != K * N * dt.nbits or not bq.is_contiguous():
+        raise ValueError("bq must be a contiguous uint8 tensor of K*N*nbits/8 bytes")
+    if out is None:
+        out = torch.empty(M, N, dtype=a.dtype, device=a.device)
+    if M == 0:
+        return out
+    with torch.cuda.device(a.device):
+        if workspace is None:
+            workspace = get_workspace(a.device, workspace_bytes(M, N, K, dt, zero_point, group_size))
+        args = (a.data_ptr(), a.stride(0), bq.data_ptr(), scales.data_ptr(), out.data_ptr(), out.stride(0),
+                M, N, K, dt.code, zero_point, group_size, _lib.ACT_F16, workspace.data_ptr(), workspace.numel(),
+                _stream_ptr(a.device))
+        if plan_override is None:
+            st = lib.b200q_gemm(*args)
+        else:
+            pl = _lib.Plan()
+            _lib.check(lib.b200q_plan(M, N, K, dt.code, zero_point, group_size, ctypes.byref(pl)))
+            for k, v in plan_override.items():
+                setattr(pl, k, v)
+            st = lib.b200q_gemm_planned(*args, ctypes.byref(pl))
+    _lib.check(st)
+    return out
+
+
+def dequantize(bq: torch.Tensor, scales: torch.Tensor, w_dtype, group_size: int, zero_point: int = 0) -> torch.Tensor:
+    """W[K, N] fp16, the weights the GEMM multiplies by (bit-exact with the reference's
+    cast-then-scale)."""
+    lib = _lib.load()
+    dt = weight_dtype(w_dtype)
+    G, N = scales.shape
+    K = G * group_size
+    if not (bq.is_cuda and scales.is_cuda):
+        raise ValueError("dequantize needs CUDA tensors (there is no CPU path)")
+    if bq.dtype != torch.uint8 or bq.numel() * 8 != K * N * dt.nbits:
+        raise ValueError("bq must be a uint8 tensor of K*N*nbits/8 bytes")
+    w = torch.empty(K, N, dtype=torch.float16, device=bq.device)
+    with torch.cuda.device(bq.device):
+        _lib.check(lib.b200q_dequantize(bq.data_ptr(), scales.contiguous().data_ptr(), w.data_ptr(), N, K, dt.code,
+                                        zero_point, group_size, _stream_ptr(bq.device)))
+    return w
+
+
+def device_status(workspace: torch.Tensor) -> list:
+    arr = (ctypes.c_int32 * 4)()
+    st = _lib.load().b200q_device_status(workspace.data_ptr(), ctypes.byref(arr), _stream_ptr(workspace.device))
+    if st not in (_lib.ST_OK, _lib.ST_DEVICE_TIMEOUT):
+        _lib.check(st)
+    return list(arr)
