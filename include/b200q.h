@@ -54,11 +54,15 @@ typedef struct b200q_plan {
   int32_t kernel;        /* 0 = split-K mma.sync path (M <= 16 per pass), 1 = tcgen05 path */
   int32_t m_tiles;       /* kernel 0: 8-row activation tiles per pass (1 or 2) */
   int32_t splits;        /* split-K factor S */
+  int32_t cluster;       /* kernel 0: CTAs per cluster; that many of the S splits reduce in shared memory */
   int32_t ctas_per_split;/* kernel 0: column ranges P; grid = S * P */
   int32_t smem_bytes;    /* dynamic shared memory per CTA */
   int32_t tile_m;        /* kernel 1: activation rows per CTA tile (multiple of 16, <= 256) */
-  int32_t stages;        /* kernel 1: pipeline depth */
+  int32_t stages;        /* pipeline depth (kernel 0: weight items in flight per warp) */
+  int32_t warps;         /* kernel 0: warps per CTA (output only) */
   int32_t passes;        /* launches needed to cover M */
+  int32_t pdl;           /* 1: launch with programmatic stream serialization (overlap with the previous kernel) */
+  int32_t debug;         /* 0; non-zero values switch parts of kernel 0 off for timing experiments */
   uint64_t workspace_bytes;
 } b200q_plan_t;
 

@@ -82,8 +82,11 @@ def test_gemm_ragged_m(M):
     assert _rel_err(c, ref) <= REL_TOL
 
 
-@pytest.mark.parametrize("splits,ctas", [(1, 1), (1, 5), (2, 3), (4, 8), (4, 37)])
-def test_gemm_split_k_shapes_and_clean_workspace(splits, ctas):
+@pytest.mark.parametrize("splits,ctas", [(1, 1), (1, 5), (2, 3), (4, 8), (4, 17)])
+@pytest.mark.parametrize("cluster", [1, 2])
+def test_gemm_split_k_shapes_and_clean_workspace(splits, ctas, cluster):
+    if splits % cluster:
+        pytest.skip("cluster size must divide the split count")
     dev = _dev()
     M, N, K = 3, 272, 2048
     prob = synth.make_problem(M, N, K, D.int4b, 128, seed=11)
@@ -93,7 +96,7 @@ def test_gemm_split_k_shapes_and_clean_workspace(splits, ctas):
     ref = qo.quantized_matmul(prob["a"].numpy(), prob["codes"].numpy(), prob["scales"].numpy(), dt, 128, 0)
     for _ in range(2):  # second call runs on the workspace the first one left behind
         c = ops.quantized_matmul(prob["a"].to(dev), bq, prob["scales"].to(dev), dt, 128, 0, workspace=ws,
-                                 plan_override=dict(splits=splits, ctas_per_split=ctas))
+                                 plan_override=dict(splits=splits, ctas_per_split=ctas, cluster=cluster))
         torch.cuda.synchronize()
         assert _rel_err(c.cpu().numpy(), ref) <= REL_TOL
         assert int(ws.count_nonzero()) == 0, "workspace not restored to zero"
@@ -149,7 +152,8 @@ def test_linearity_full_size():
     c2 = ops.quantized_matmul(a, bq, sc2, D.uint4b, 128, 8).float()
     torch.cuda.synchronize()
     assert (c2[:, ::2] - 2 * c12[:, ::2]).abs().max().item() <= 4e-3 * scale_ref
-    assert torch.equal(c2[:, 1::2], c12[:, 1::2])
+    # untouched columns: equal up to the order of the fp32 split-K additions
+    assert (c2[:, 1::2] - c12[:, 1::2]).abs().max().item() <= 2e-3 * scale_ref
 
 
 def test_errors_are_loud():

@@ -33,14 +33,14 @@ def _literal_b200(codes, dt):
     planes = P.PLANES[b]
     for nt in range(NT):
         for kb in range(KB):
-            blk = (nt * KB + kb) * b * 2 * 32 * 4
+            blk = (nt * KB + kb) * b * 2 * 32 * 4  # words per block
             for half in range(2):
                 for r in range(8):
                     n = nt * 16 + half * 8 + r
                     for j in range(4):
                         lane = r * 4 + j
                         for c in range(4):
-                            k0 = kb * 512 + j * 128 + c * 32
+                            k0 = kb * 512 + c * 128 + j * 32
                             for h in range(16):
                                 for e in range(2):
                                     q = int(codes[k0 + 2 * h + e, n])
@@ -53,7 +53,7 @@ def _literal_b200(codes, dt):
                                         v = base + h // per
                                         f = h % per
                                         field = (q >> lo) & ((1 << p) - 1)
-                                        widx = blk + ((v * 2 + half) * 32 + lane) * 4 + c
+                                        widx = blk + ((c * 2 + half) * 32 + lane) * b + v
                                         out[widx] |= np.uint64(field << (16 * e + f * p))
                                         base += p
     return out.astype(np.uint32).view(np.uint8)

@@ -9,7 +9,7 @@ import ctypes
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libb200q.so")
+LIB_PATH = os.path.join(HERE, os.environ.get("B200Q_LIB_NAME", "libb200q.so"))
 
 ST_OK, ST_INVALID_ARG, ST_UNSUPPORTED, ST_WORKSPACE, ST_CUDA, ST_DEVICE_TIMEOUT = range(6)
 ACT_F16 = 0
@@ -26,11 +26,15 @@ class Plan(ctypes.Structure):
         ("kernel", ctypes.c_int32),
         ("m_tiles", ctypes.c_int32),
         ("splits", ctypes.c_int32),
+        ("cluster", ctypes.c_int32),
         ("ctas_per_split", ctypes.c_int32),
         ("smem_bytes", ctypes.c_int32),
         ("tile_m", ctypes.c_int32),
         ("stages", ctypes.c_int32),
+        ("warps", ctypes.c_int32),
         ("passes", ctypes.c_int32),
+        ("pdl", ctypes.c_int32),
+        ("debug", ctypes.c_int32),
         ("workspace_bytes", ctypes.c_uint64),
     ]
 

@@ -17,6 +17,13 @@ OBJ = os.path.join(CSRC, "_build")
 LIB = os.path.join(HERE, "libb200q.so")
 NPARTS = 8
 
+# Extra -D definitions for experiments (e.g. B200Q_EXTRA_DEFS="-DB200Q_GPW=2") and an
+# alternative output name (B200Q_LIB_NAME) so that several builds can sit side by side.
+EXTRA_DEFS = os.environ.get("B200Q_EXTRA_DEFS", "").split()
+if os.environ.get("B200Q_LIB_NAME"):
+    LIB = os.path.join(HERE, os.environ["B200Q_LIB_NAME"])
+    OBJ = OBJ + "_" + os.environ["B200Q_LIB_NAME"].replace(".", "_")
+
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O3", "-lineinfo",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
@@ -56,7 +63,7 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
         out = os.path.join(OBJ, obj)
         if not force and os.path.exists(out) and os.path.getmtime(out) >= newest:
             return (obj, "")
-        cmd = [nvcc, *NVCC_FLAGS, *defs, "-c", os.path.join(CSRC, src), "-o", out]
+        cmd = [nvcc, *NVCC_FLAGS, *EXTRA_DEFS, *defs, "-c", os.path.join(CSRC, src), "-o", out]
         if ptxas_info:
             cmd[1:1] = ["-Xptxas", "-v"]
         r = subprocess.run(cmd, capture_output=True, text=True)

@@ -69,13 +69,27 @@ static DeviceInfo device_info() {
 }
 
 // shared-memory row pitch (halfs) of an activation chunk of kc columns: 16 bytes of padding
-// per 128 columns, and pitch bytes = 64 (mod 128) so that 8 lanes reading 16 bytes each from
-// two rows x four 128-column segments touch 8 different 16-byte bank groups
+// per 32 columns, and pitch bytes = 64 (mod 128), so that 8 lanes reading 16 bytes each from
+// two rows x four 32-column units touch 8 different 16-byte bank groups
 static int skinny_pitch(int kc) {
-  int bytes = kc * 2 + (kc / 128) * 16;
+  int bytes = kc * 2 + (kc / 32) * 16;
   if (bytes % 128 != 64) bytes += (64 - bytes % 128 + 128) % 128;
   return bytes / 2;
 }
+// warps per CTA of the skinny kernel (fixed by its launch bounds)
+// mirrors of skinny_kernel.cu: 8 warps per CTA, one weight ring per warp, items of GI groups
+static const int kSkinnyWarps = 8;
+static int skinny_item_bytes(int bits) { return (bits <= 2 ? 4 : 2) * 256 * bits; }
+// dynamic shared memory of the skinny kernel: barriers + per-warp weight rings + output tile
+// sums + activation chunk + per-group activation sums
+static int skinny_smem(int m_pass, int kc, int bits, int stages, int tiles_max) {
+  const int mt = (m_pass + 7) / 8;
+  return 512 + kSkinnyWarps * stages * skinny_item_bytes(bits) + tiles_max * 16 * 8 * mt * 4 +
+         m_pass * skinny_pitch(kc) * 2 + (kc / 128) * 8 * mt * 4;
+}
+// k splits inside a cluster (reduced through distributed shared memory): pairs of CTAs
+// (clusters of four 200 KB CTAs measured twice as slow: fewer of them fit a GPC at once)
+static int skinny_cluster(int splits) { return splits % 2 == 0 ? 2 : 1; }
 
 // ---- static shape -> tile table ------------------------------------------------------------
 // Exact entries for the shapes this library is benchmarked on come first; anything else
@@ -86,57 +100,78 @@ struct TableEntry {
 };
 static const TableEntry kSkinnyTable[] = {
     // bits  M range   N      K     S
-    {4, 1, 16, 8192, 8192, 2},
+    {4, 1, 8, 8192, 8192, 1},
 };
 
 static int plan_skinny(int m_pass, int N, int K, int bits, const DeviceInfo& di, b200q_plan_t* pl) {
   const int KB = K / BLOCK_K, NT = N / BLOCK_N;
-  const int occ_regs = bits <= 4 ? 2 : 1;  // register budget of the kernel (launch bounds)
+  const int mt = (m_pass + 7) / 8;
+  const int ipb = bits <= 2 ? 1 : 2;  // items per block
   int forced = 0;
   for (const TableEntry& t : kSkinnyTable)
     if (t.bits == bits && m_pass >= t.m_lo && m_pass <= t.m_hi && t.N == N && t.K == K) forced = t.splits;
   double best_cost = 1e30;
-  int best_s = 0, best_p = 0;
+  int best_s = 0, best_p = 0, best_st = 0;
   for (int pass = 0; pass < 2 && !best_s; ++pass) {  // pass 0 honours the table, pass 1 ignores it
-    for (int s = 1; s <= KB; ++s) {
+    for (int s = 1; s <= KB && s <= di.sm_count; ++s) {
       if (KB % s) continue;
       if (pass == 0 && forced && s != forced) continue;
       const int kbc = KB / s;
-      const int smem = m_pass * skinny_pitch(kbc * 512) * 2;
-      if (smem + 1024 > di.max_smem) continue;
-      for (int occ = 1; occ <= occ_regs; ++occ) {
-        if ((smem + 1024) * occ > di.max_smem) continue;
-        const int slots = di.sm_count * occ;
-        if (s > slots) continue;
-        int P = slots / s;
+      for (int occ = 2; occ >= 1; --occ) {  // CTAs per SM
+        int P = di.sm_count * occ / s;
+        if (P < 1) continue;
         if (P > NT) P = NT;
         const int tiles_max = (NT + P - 1) / P;
-        const int warp_items = (tiles_max * kbc + 7) / 8;
-        // time ~ items the busiest SM streams + staging the activation chunk + reduction traffic
-        const double cost = warp_items * 8.0 * occ + 0.05 * m_pass * kbc * occ + 0.2 * s;
-        if (cost < best_cost) { best_cost = cost; best_s = s; best_p = P; }
+        const int fixed = skinny_smem(m_pass, kbc * 512, bits, 0, tiles_max);
+        const int cap = (di.max_smem + 1024) / occ - 1024 - (occ == 2 ? 1024 : 0);
+        int stages = (cap - fixed) / (kSkinnyWarps * skinny_item_bytes(bits));
+        if (stages > 8) stages = 8;
+        if (stages < 2) continue;
+        const int cta_items = tiles_max * kbc * ipb;
+        const int warp_items = (cta_items + kSkinnyWarps - 1) / kSkinnyWarps;
+        const int gs = s / skinny_cluster(s);
+        // time ~ the busiest SM's longest warp, staging the activation chunk, reduction traffic
+        const double cost = (double)warp_items * kSkinnyWarps * occ / ipb + 0.05 * m_pass * kbc * occ + 0.3 * s +
+                            2.0 * (s > 1) + 3.0 * (gs > 1) + (stages < 3 ? 2.0 : 0.0) + (occ == 1 ? 1.0 : 0.0);
+        if (cost < best_cost) { best_cost = cost; best_s = s; best_p = P; best_st = stages; }
       }
     }
   }
   if (!best_s) return ST_UNSUPPORTED;
   const int kbc = KB / best_s;
+  // enough bytes in flight per CTA to cover the memory latency; more only costs shared memory
+  while (best_st > 3 && kSkinnyWarps * (best_st - 1) * skinny_item_bytes(bits) >= 64 * 1024) --best_st;
   pl->kernel = 0;
-  pl->m_tiles = (m_pass + 7) / 8;
+  pl->m_tiles = mt;
   pl->splits = best_s;
+  pl->cluster = skinny_cluster(best_s);
   pl->ctas_per_split = best_p;
-  pl->smem_bytes = m_pass * skinny_pitch(kbc * 512) * 2;
+  pl->warps = kSkinnyWarps;
+  pl->stages = best_st;
+  pl->smem_bytes = skinny_smem(m_pass, kbc * 512, bits, best_st, (NT + best_p - 1) / best_p);
   pl->tile_m = 0;
-  pl->stages = 0;
+  pl->pdl = 1;
+  pl->debug = 0;
   return ST_OK;
 }
 
-static int check_problem(int M, int N, int K, int wtype, int zero_point, int group, int* var) {
+// group_mult: 128 for the GEMM kernels (one scale per 128-row group and column), 32 for
+// the dequantize kernel
+static int check_problem(int M, int N, int K, int wtype, int zero_point, int group, int group_mult, int* var) {
   if (M < 1 || N < 1 || K < 1 || group < 1) return ST_INVALID_ARG;
   *var = variant_of(wtype, zero_point);
   if (*var < 0) return ST_UNSUPPORTED;
   if (K % BLOCK_K != 0 || N % BLOCK_N != 0) return ST_UNSUPPORTED;
-  if (group % 32 != 0 || K % group != 0) return ST_UNSUPPORTED;
+  if (group % group_mult != 0 || K % group != 0) return ST_UNSUPPORTED;
+  // the GEMM kernels index scale rows with a shift: group = 128 * 2^s, or one group per column
+  if (group_mult == 128 && group != K && ((group / 128) & (group / 128 - 1)) != 0) return ST_UNSUPPORTED;
   return ST_OK;
+}
+static int gshift_of(int group, int K) {
+  if (group == K) return -1;
+  int s = 0;
+  while ((128 << s) < group) ++s;
+  return s;
 }
 
 static int make_plan(int M, int N, int K, int var, b200q_plan_t* pl) {
@@ -160,6 +195,10 @@ static int run_gemm(const void* a, int lda, const void* bq, const void* scales, 
   if (lda < K || ldc < N || (lda % 8) != 0) return ST_INVALID_ARG;
   if (pl.kernel != 0) return ST_UNSUPPORTED;
   if (pl.splits < 1 || (K / BLOCK_K) % pl.splits != 0 || pl.ctas_per_split < 1) return ST_INVALID_ARG;
+  const int bits = var_bits(var);
+  if (pl.stages < 1 || pl.stages > 8) return ST_INVALID_ARG;
+  if (pl.cluster < 1 || pl.cluster > 8 || pl.splits % pl.cluster != 0) return ST_INVALID_ARG;
+  if (pl.ctas_per_split > N / BLOCK_N) return ST_INVALID_ARG;
   const int m_pass = M < 16 ? M : 16;
   const size_t need = WS_HEADER_BYTES + ws_counter_bytes(N) + (size_t)m_pass * N * sizeof(float);
   if (!workspace || ws_bytes < need || ((uintptr_t)workspace & 255)) return ST_WORKSPACE;
@@ -169,16 +208,22 @@ static int run_gemm(const void* a, int lda, const void* bq, const void* scales, 
   p.scales = reinterpret_cast<const __half*>(scales);
   p.counters = reinterpret_cast<int*>(reinterpret_cast<char*>(workspace) + WS_HEADER_BYTES);
   p.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + WS_HEADER_BYTES + ws_counter_bytes(N));
-  p.N = N; p.K = K; p.group = group; p.lda = lda; p.ldc = ldc;
+  p.N = N; p.K = K; p.group = group; p.gshift = gshift_of(group, K); p.lda = lda; p.ldc = ldc;
   p.KB = K / BLOCK_K; p.NT = N / BLOCK_N;
-  p.S = pl.splits; p.P = pl.ctas_per_split; p.KBc = p.KB / p.S;
+  p.CS = pl.cluster; p.GS = pl.splits / pl.cluster; p.P = pl.ctas_per_split; p.KBc = p.KB / pl.splits;
+  p.tiles_max = (p.NT + p.P - 1) / p.P;
   p.pitch = skinny_pitch(p.KBc * 512);
+  p.stages = pl.stages;
+  p.status = reinterpret_cast<int*>(workspace);
+  p.debug_skip = pl.debug;
+  p.pdl = pl.pdl;
   for (int m0 = 0; m0 < M; m0 += 16) {
     const int mc = (M - m0) < 16 ? (M - m0) : 16;
     p.a = reinterpret_cast<const __half*>(a) + (size_t)m0 * lda;
     p.c = reinterpret_cast<__half*>(c) + (size_t)m0 * ldc;
     p.M = mc;
-    const int smem = mc * p.pitch * 2;
+    const int smem = skinny_smem(mc, p.KBc * 512, bits, pl.stages, p.tiles_max);
+    if (smem > device_info().max_smem) return ST_UNSUPPORTED;
     cudaError_t e = skinny_launch(var, p, (mc + 7) / 8, smem, stream);
     if (e != cudaSuccess) { g_last_cuda_error = (int)e; return ST_CUDA; }
   }
@@ -211,7 +256,7 @@ int b200q_last_cuda_error(void) { return g_last_cuda_error; }
 int b200q_plan(int M, int N, int K, int wtype, int zero_point, int group, b200q_plan_t* plan) {
   if (!plan) return ST_INVALID_ARG;
   int var;
-  int st = check_problem(M, N, K, wtype, zero_point, group, &var);
+  int st = check_problem(M, N, K, wtype, zero_point, group, 128, &var);
   if (st != ST_OK) return st;
   return make_plan(M, N, K, var, plan);
 }
@@ -228,7 +273,7 @@ int b200q_gemm_planned(const void* a, int lda, const void* bq, const void* scale
   if (!plan) return ST_INVALID_ARG;
   if (act_dtype != B200Q_F16) return ST_UNSUPPORTED;
   int var;
-  int st = check_problem(M, N, K, wtype, zero_point, group, &var);
+  int st = check_problem(M, N, K, wtype, zero_point, group, 128, &var);
   if (st != ST_OK) return st;
   return run_gemm(a, lda, bq, scales, c, ldc, M, N, K, var, group, workspace, workspace_bytes,
                   reinterpret_cast<cudaStream_t>(stream), *plan);
@@ -239,7 +284,7 @@ int b200q_gemm(const void* a, int lda, const void* bq, const void* scales, void*
                void* stream) {
   if (act_dtype != B200Q_F16) return ST_UNSUPPORTED;
   int var;
-  int st = check_problem(M, N, K, wtype, zero_point, group, &var);
+  int st = check_problem(M, N, K, wtype, zero_point, group, 128, &var);
   if (st != ST_OK) return st;
   b200q_plan_t pl;
   st = make_plan(M, N, K, var, &pl);
@@ -251,7 +296,7 @@ int b200q_gemm(const void* a, int lda, const void* bq, const void* scales, void*
 int b200q_dequantize(const void* bq, const void* scales, void* w, int N, int K, int wtype, int zero_point, int group,
                      void* stream) {
   int var;
-  int st = check_problem(1, N, K, wtype, zero_point, group, &var);
+  int st = check_problem(1, N, K, wtype, zero_point, group, 32, &var);
   if (st != ST_OK) return st;
   if (!bq || !scales || !w) return ST_INVALID_ARG;
   if (((uintptr_t)bq | (uintptr_t)w) & 15) return ST_INVALID_ARG;

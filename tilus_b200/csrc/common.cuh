@@ -41,10 +41,17 @@ struct SkinnyParams {
   float* partial;        // [M, N] fp32, zero on entry, zero on exit
   int* counters;         // [N/16], zero on entry, zero on exit
   int M, N, K, group;
+  int gshift;            // log2(group / 128), or -1 when there is one group per column (group == K)
   int lda, ldc;
   int KB, NT;            // K/512, N/16
-  int S, P, KBc;         // k splits, CTAs per split, k-blocks per split
+  int GS, CS, P, KBc;    // global k splits, cluster size (k splits inside a cluster), column ranges,
+                         // k-blocks per CTA (K/512 / (GS*CS))
+  int tiles_max;         // most column tiles any cluster owns: ceil(NT / P)
   int pitch;             // shared-memory row pitch of the activation chunk, in halfs
+  int stages;            // items in flight per warp (<= 8)
+  int* status;           // workspace status header
+  int debug_skip;        // diagnosis: 1 stream the weights but skip the math, 2 skip the loop, 3 and the staging
+  int pdl;               // launch with programmatic stream serialization
 };
 
 // ---- dequantize kernel -----------------------------------------------------------------------
@@ -73,6 +80,15 @@ __device__ __forceinline__ void mma_m16n8k16(float (&d)[4], uint32_t a0, uint32_
       "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// same, first step of a chain: the accumulator input is zero
+__device__ __forceinline__ void mma_m16n8k16_init(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                  uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
 }
 
 }  // namespace b200q

@@ -149,6 +149,31 @@ B200Q_HD uint32_t pair_raw(const uint32_t* w) {
   }
 }
 
+// "Linear" pattern of pair H: a half2 bit pattern whose fp16 value is proportional to the
+// decoded value, with no arithmetic at all.  Integers: the code sits in the mantissa of an
+// fp16 subnormal at bit T, value = code * 2^(T-24).  Floats: pair_raw, value = true value *
+// 2^-(15 - bias).  The GEMV path feeds these straight to the tensor core and repairs the
+// factors afterwards (activations pre-multiplied by 2^-T, accumulators by lin_factor).
+template <int VAR, int H>
+B200Q_HD uint32_t pair_lin(const uint32_t* w) {
+  constexpr int B = var_bits(VAR);
+  if constexpr (!var_is_float(VAR)) {
+    constexpr int T = int_target(B, H);
+    return gather_pair<B, H, T>(w, 0u);
+  } else {
+    return pair_raw<VAR, H>(w);
+  }
+}
+
+// exponent e such that activations of pair h are pre-multiplied by 2^-e
+B200Q_HD constexpr int lin_prescale_shift(int var, int h) {
+  return var_is_float(var) ? 0 : int_target(var_bits(var), h);
+}
+// log2 of the factor the accumulated linear products are multiplied by
+B200Q_HD constexpr int lin_factor_log2(int var) {
+  return var_is_float(var) ? 15 - ((1 << (var_float_ebits(var) - 1)) - 1) : 24;
+}
+
 template <int VAR, int H>
 B200Q_HD constexpr int pair_target() {
   constexpr int B = var_bits(VAR);
@@ -195,6 +220,19 @@ struct UnitLoop {
     if constexpr (H + 1 < 16) UnitLoop<VAR, H + 1>::run(w, scale, out);
   }
 };
+
+template <int VAR, int H>
+struct UnitLinLoop {
+  static __device__ __forceinline__ void run(const uint32_t* w, uint32_t* out) {
+    out[H] = pair_lin<VAR, H>(w);
+    if constexpr (H + 1 < 16) UnitLinLoop<VAR, H + 1>::run(w, out);
+  }
+};
+// out[h] = linear patterns of pair h (see pair_lin)
+template <int VAR>
+__device__ __forceinline__ void unit_decode_linear(const uint32_t* w, uint32_t* out) {
+  UnitLinLoop<VAR, 0>::run(w, out);
+}
 
 // out[h] = fp16_rn(value(k0+2h) * s) | fp16_rn(value(k0+2h+1) * s) << 16, h = 0..15
 template <int VAR>

@@ -5,7 +5,7 @@
 // b = cast(q) * scale).
 //
 // One warp per 16-column x 512-row block; lane (r, j) decodes columns r and r+8, rows
-// j*128 .. j*128+127, as in the packed layout.  The block is transposed through shared
+// c*128 + j*32 .. +31 of each 128-row group c, as in the packed layout.  The block is transposed through shared
 // memory so that the global stores are 32-byte row segments.
 #include "common.cuh"
 
@@ -14,38 +14,31 @@ namespace b200q {
 template <int VAR>
 __global__ void __launch_bounds__(128) dequant_kernel(const DequantParams p) {
   constexpr int B = var_bits(VAR);
-  __shared__ __half tile[4][128][16 + 2];  // per warp: 128 rows (one j segment at a time) x 16 columns
+  __shared__ __half tile[4][128][16 + 2];  // per warp: one 128-row group x 16 columns
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int r = lane >> 2, j = lane & 3;
   const long long blk = (long long)blockIdx.x * 4 + warp;
   const long long nblk = (long long)p.NT * p.KB;
   if (blk >= nblk) return;
   const int nt = (int)(blk / p.KB), kb = (int)(blk % p.KB);
-  const uint4* base = p.bq + (size_t)blk * (size_t)(B * 64) + lane;
-  uint4 v[2 * B];
-#pragma unroll
-  for (int q = 0; q < 2 * B; ++q) v[q] = ld_stream_u4(base + q * 32);
+  const uint32_t* base = reinterpret_cast<const uint32_t*>(p.bq) + (size_t)blk * (size_t)(B * 256);
 
-  for (int jj = 0; jj < 4; ++jj) {  // rows jj*128 .. +127 of the block, from the lanes with j == jj
-    if (j == jj) {
+  for (int c = 0; c < 4; ++c) {  // 128-row group c of the block
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+    for (int h = 0; h < 2; ++h) {
+      uint32_t w[B], out[16];
+      const uint32_t* src = base + ((c * 2 + h) * 32 + lane) * B;
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          uint32_t w[B], out[16];
+      for (int q = 0; q < B; ++q) w[q] = __ldg(src + q);
+      const int n = nt * 16 + h * 8 + r;
+      const int k0 = kb * 512 + c * 128 + j * 32;
+      const __half s = p.scales[(size_t)(k0 / p.group) * p.N + n];
+      unit_decode_scaled<VAR>(w, __half2half2(s), out);
 #pragma unroll
-          for (int q = 0; q < B; ++q) w[q] = u4_comp(v[q * 2 + h], u);
-          const int n = nt * 16 + h * 8 + r;
-          const int k0 = kb * 512 + j * 128 + u * 32;
-          const __half s = p.scales[(size_t)(k0 / p.group) * p.N + n];
-          unit_decode_scaled<VAR>(w, __half2half2(s), out);
-#pragma unroll
-          for (int pair = 0; pair < 16; ++pair) {
-            const __half2 x = h2_from_bits(out[pair]);
-            tile[warp][u * 32 + 2 * pair][h * 8 + r] = __low2half(x);
-            tile[warp][u * 32 + 2 * pair + 1][h * 8 + r] = __high2half(x);
-          }
-        }
+      for (int pair = 0; pair < 16; ++pair) {
+        const __half2 x = h2_from_bits(out[pair]);
+        tile[warp][j * 32 + 2 * pair][h * 8 + r] = __low2half(x);
+        tile[warp][j * 32 + 2 * pair + 1][h * 8 + r] = __high2half(x);
       }
     }
     __syncwarp();
@@ -55,7 +48,7 @@ __global__ void __launch_bounds__(128) dequant_kernel(const DequantParams p) {
       __half tmp[8];
 #pragma unroll
       for (int q = 0; q < 8; ++q) tmp[q] = tile[warp][row][hh * 8 + q];
-      const size_t k = (size_t)kb * 512 + jj * 128 + row;
+      const size_t k = (size_t)kb * 512 + c * 128 + row;
       *reinterpret_cast<uint4*>(p.w + k * p.N + nt * 16 + hh * 8) = *reinterpret_cast<uint4*>(tmp);
     }
     __syncwarp();

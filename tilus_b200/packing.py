@@ -25,11 +25,14 @@ pair as the two 16-bit halves of a register, ready for the fp16 magic-number
 conversion.  Signed integer codes are stored with the sign bit flipped (offset
 binary) so that signed and unsigned types decode with one subtraction.
 
-*Block*: 16 columns x 512 rows = 64 (column, 128-row segment) pairs x 4 units.
-Stored as 16-byte vectors [v = 0..b-1][half = 0..1][lane = 0..31]: lane = r*4 + j
-holds column n = nt*16 + half*8 + r, rows kb*512 + j*128 + [0, 128); component
-c = 0..3 of vector v is word v of the unit covering rows ... + c*32 + [0, 32).
-A warp reads one vector index as 512 contiguous bytes.
+*Block*: 16 columns x 512 rows = 4 row groups of 128 x 16 columns x 4 units of 32.
+Stored group by group; inside group c the units are ordered [half = 0..1][lane = 0..31]
+with lane = r*4 + j holding column n = nt*16 + half*8 + r, rows kb*512 + c*128 + j*32 +
+[0, 32), each unit as its b words: word offset ((c*2 + half)*32 + lane)*b + v.  So a
+128-row group of the block (one scale per column when group_size is a multiple of 128)
+is 256*b contiguous bytes, a whole block 1024*b contiguous bytes, the four lanes that
+share a column split a group in 32-row units, and the 128 rows of one column of a
+group are 16*b contiguous bytes.
 
 *Matrix*: blocks in [nt][kb] order (column-tile major), so a contiguous range of
 column tiles - an N shard - is a contiguous byte range.
@@ -185,15 +188,14 @@ def interleave(codes: torch.Tensor, dt, chunk_tiles: int = 64) -> torch.Tensor:
     K, N = codes.shape
     check_shape(K, N)
     KB, NT = K // BLOCK_K, N // BLOCK_N
-    out = torch.empty(NT, KB, b, 2, 32, 4, dtype=torch.int32, device=codes.device)
+    out = torch.empty(NT, KB, 4, 2, 32, b, dtype=torch.int32, device=codes.device)
     sc = stored_codes(codes.to(torch.uint8), dt)
     for t0 in range(0, NT, chunk_tiles):
         t1 = min(NT, t0 + chunk_tiles)
-        blk = sc[:, t0 * 16 : t1 * 16].reshape(KB, 4, 4, 32, t1 - t0, 2, 8)  # kb j u i nt half r
-        blk = blk.permute(4, 0, 5, 6, 1, 2, 3)  # nt kb half r j u i
-        words = _unit_words(blk.to(torch.int32), b)  # nt kb half r j u v
-        words = words.permute(0, 1, 6, 2, 3, 4, 5)  # nt kb v half r j u
-        out[t0:t1] = words.reshape(t1 - t0, KB, b, 2, 32, 4)
+        blk = sc[:, t0 * 16 : t1 * 16].reshape(KB, 4, 4, 32, t1 - t0, 2, 8)  # kb c j i nt half r
+        blk = blk.permute(4, 0, 1, 5, 6, 2, 3)  # nt kb c half r j i
+        words = _unit_words(blk.to(torch.int32), b)  # nt kb c half r j v
+        out[t0:t1] = words.reshape(t1 - t0, KB, 4, 2, 32, b)
     return out.reshape(-1).view(torch.uint8)
 
 
@@ -205,10 +207,9 @@ def deinterleave(storage: torch.Tensor, dt, K: int, N: int) -> torch.Tensor:
     KB, NT = K // BLOCK_K, N // BLOCK_N
     st = storage.reshape(-1).contiguous()
     assert st.dtype == torch.uint8 and st.numel() * 8 == K * N * b
-    words = st.view(torch.int32).reshape(NT, KB, b, 2, 8, 4, 4)  # nt kb v half r j u
-    words = words.permute(0, 1, 3, 4, 5, 6, 2)  # nt kb half r j u v
-    codes = _words_to_codes(words, b)  # nt kb half r j u i
-    codes = codes.permute(1, 4, 5, 6, 0, 2, 3).reshape(K, N)  # kb j u i nt half r
+    words = st.view(torch.int32).reshape(NT, KB, 4, 2, 8, 4, b)  # nt kb c half r j v
+    codes = _words_to_codes(words, b)  # nt kb c half r j i
+    codes = codes.permute(1, 2, 5, 6, 0, 3, 4).reshape(K, N)  # kb c j i nt half r
     return stored_codes(codes.contiguous(), dt)
 
 
