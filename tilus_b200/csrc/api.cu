@@ -3,6 +3,8 @@
 #include <cstdio>
 #include <cstring>
 
+#include <cuda.h>
+
 #include "../../include/b200q.h"
 #include "common.cuh"
 
@@ -17,6 +19,11 @@ namespace b200q {
 B200Q_DECL_PART(0) B200Q_DECL_PART(1) B200Q_DECL_PART(2) B200Q_DECL_PART(3)
 B200Q_DECL_PART(4) B200Q_DECL_PART(5) B200Q_DECL_PART(6) B200Q_DECL_PART(7)
 cudaError_t dequant_launch(int var, const DequantParams& p, cudaStream_t stream);
+#define B200Q_DECL_UPART(i) \
+  cudaError_t umma_launch_part##i(int, const UmmaParams&, const void*, int, cudaStream_t);
+B200Q_DECL_UPART(0) B200Q_DECL_UPART(1) B200Q_DECL_UPART(2) B200Q_DECL_UPART(3)
+B200Q_DECL_UPART(4) B200Q_DECL_UPART(5) B200Q_DECL_UPART(6) B200Q_DECL_UPART(7)
+int umma_smem_bytes(int tm);
 
 static thread_local int g_last_cuda_error = 0;
 
@@ -31,6 +38,35 @@ static cudaError_t skinny_launch(int var, const SkinnyParams& p, int mt, int sme
     case 6: return skinny_launch_part6(var, p, mt, smem, s);
     default: return skinny_launch_part7(var, p, mt, smem, s);
   }
+}
+
+static cudaError_t umma_launch(int var, const UmmaParams& p, const void* tmap, int smem, cudaStream_t s) {
+  switch (var % B200Q_NPARTS) {
+    case 0: return umma_launch_part0(var, p, tmap, smem, s);
+    case 1: return umma_launch_part1(var, p, tmap, smem, s);
+    case 2: return umma_launch_part2(var, p, tmap, smem, s);
+    case 3: return umma_launch_part3(var, p, tmap, smem, s);
+    case 4: return umma_launch_part4(var, p, tmap, smem, s);
+    case 5: return umma_launch_part5(var, p, tmap, smem, s);
+    case 6: return umma_launch_part6(var, p, tmap, smem, s);
+    default: return umma_launch_part7(var, p, tmap, smem, s);
+  }
+}
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point lookup (no link to libcuda)
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
 }
 
 // wtype tag + zero point -> kernel variant (decode.cuh), or -1
@@ -174,15 +210,86 @@ static int gshift_of(int group, int K) {
   return s;
 }
 
+// tcgen05 kernel: tile rows, tiles and split-K so that the grid fills the SMs
+static void plan_umma(int M, int N, int K, const DeviceInfo& di, b200q_plan_t* pl) {
+  const int tm = M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+  const int m_tiles = (M + tm - 1) / tm, n_tiles = (N + 127) / 128;
+  const int ctas = m_tiles * n_tiles;
+  const int kblocks = K / 64;
+  int splits = 1;
+  if (ctas * 2 <= di.sm_count && ctas <= N / BLOCK_N) {
+    for (int s = 2; s <= 16; ++s)
+      if (kblocks % s == 0 && kblocks / s >= 8 && ctas * s <= di.sm_count + di.sm_count / 8) splits = s;
+  }
+  pl->kernel = 1;
+  pl->m_tiles = m_tiles;
+  pl->splits = splits;
+  pl->cluster = 1;
+  pl->ctas_per_split = ctas;
+  pl->smem_bytes = umma_smem_bytes(tm);
+  pl->tile_m = tm;
+  pl->stages = 4;
+  pl->warps = 10;
+  pl->passes = 1;
+  pl->pdl = 0;
+  pl->debug = 0;
+}
+
 static int make_plan(int M, int N, int K, int var, b200q_plan_t* pl) {
   const DeviceInfo di = device_info();
   std::memset(pl, 0, sizeof(*pl));
   const int bits = var_bits(var);
+  if (M > 16) {
+    plan_umma(M, N, K, di, pl);
+    const size_t part = pl->splits > 1 ? (size_t)M * N * sizeof(float) : 0;
+    pl->workspace_bytes = WS_HEADER_BYTES + ws_counter_bytes(N) + part;
+    return ST_OK;
+  }
   const int m_pass = M < 16 ? M : 16;
   int st = plan_skinny(m_pass, N, K, bits, di, pl);
   if (st != ST_OK) return st;
   pl->passes = (M + 15) / 16;
   pl->workspace_bytes = WS_HEADER_BYTES + ws_counter_bytes(N) + (size_t)m_pass * N * sizeof(float);
+  return ST_OK;
+}
+
+static int run_umma(const void* a, int lda, const void* bq, const void* scales, void* c, int ldc, int M, int N, int K,
+                    int var, int group, void* workspace, size_t ws_bytes, cudaStream_t stream,
+                    const b200q_plan_t& pl) {
+  const int tm = pl.tile_m;
+  if (tm != 32 && tm != 64 && tm != 128 && tm != 256) return ST_INVALID_ARG;
+  const int m_tiles = (M + tm - 1) / tm, n_tiles = (N + 127) / 128;
+  const int kblocks = K / 64;
+  if (pl.splits < 1 || kblocks % pl.splits != 0) return ST_INVALID_ARG;
+  if (pl.splits > 1 && m_tiles * n_tiles > N / BLOCK_N) return ST_INVALID_ARG;  // counters region
+  const size_t need = WS_HEADER_BYTES + ws_counter_bytes(N) + (pl.splits > 1 ? (size_t)M * N * sizeof(float) : 0);
+  if (!workspace || ws_bytes < need || ((uintptr_t)workspace & 255)) return ST_WORKSPACE;
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return ST_CUDA;
+  CUtensorMap tmap;
+  const cuuint64_t gdim[2] = {(cuuint64_t)K, (cuuint64_t)M};
+  const cuuint64_t gstride[1] = {(cuuint64_t)lda * 2};
+  const cuuint32_t box[2] = {64u, (cuuint32_t)tm};
+  const cuuint32_t estr[2] = {1u, 1u};
+  CUresult r = enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(a), gdim, gstride, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { g_last_cuda_error = (int)r; return ST_CUDA; }
+  UmmaParams p;
+  p.bq = reinterpret_cast<const uint4*>(bq);
+  p.scales = reinterpret_cast<const __half*>(scales);
+  p.c = reinterpret_cast<__half*>(c);
+  p.status = reinterpret_cast<int*>(workspace);
+  p.counters = reinterpret_cast<int*>(reinterpret_cast<char*>(workspace) + WS_HEADER_BYTES);
+  p.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + WS_HEADER_BYTES + ws_counter_bytes(N));
+  p.M = M; p.N = N; p.K = K; p.KB = K / BLOCK_K; p.ldc = ldc;
+  p.gshift = gshift_of(group, K);
+  p.tm = tm; p.m_tiles = m_tiles; p.n_tiles = n_tiles;
+  p.splits = pl.splits; p.kblocks_per_split = kblocks / pl.splits;
+  const int smem = umma_smem_bytes(tm);
+  if (smem > device_info().max_smem) return ST_UNSUPPORTED;
+  cudaError_t e = umma_launch(var, p, &tmap, smem, stream);
+  if (e != cudaSuccess) { g_last_cuda_error = (int)e; return ST_CUDA; }
   return ST_OK;
 }
 
@@ -193,6 +300,8 @@ static int run_gemm(const void* a, int lda, const void* bq, const void* scales, 
   if (((uintptr_t)a | (uintptr_t)bq | (uintptr_t)c) & 15) return ST_INVALID_ARG;
   if (((uintptr_t)scales) & 1) return ST_INVALID_ARG;
   if (lda < K || ldc < N || (lda % 8) != 0) return ST_INVALID_ARG;
+  if (pl.kernel == 1)
+    return run_umma(a, lda, bq, scales, c, ldc, M, N, K, var, group, workspace, ws_bytes, stream, pl);
   if (pl.kernel != 0) return ST_UNSUPPORTED;
   if (pl.splits < 1 || (K / BLOCK_K) % pl.splits != 0 || pl.ctas_per_split < 1) return ST_INVALID_ARG;
   const int bits = var_bits(var);

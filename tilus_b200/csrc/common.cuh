@@ -54,6 +54,23 @@ struct SkinnyParams {
   int pdl;               // launch with programmatic stream serialization
 };
 
+// ---- tcgen05 kernel (any M; used for M > 16) ---------------------------------------------------
+struct UmmaParams {
+  const uint4* bq;       // b200 layout
+  const __half* scales;  // [K/group, N]
+  __half* c;             // [M, N], leading dimension ldc
+  float* partial;        // [M, N] fp32 split-K scratch, zero on entry and on exit
+  int* counters;         // [n_tiles * m_tiles], zero on entry and on exit
+  int* status;           // workspace status header
+  int M, N, K, KB;       // KB = K / 512
+  int ldc;
+  int gshift;            // log2(group / 128), or -1 when group == K
+  int tm;                // activation rows per CTA tile = N extent of the MMA (32, 64, 128 or 256)
+  int m_tiles, n_tiles;  // ceil(M / tm), ceil(N / 128)
+  int splits;            // split-K factor
+  int kblocks_per_split; // 64-row k blocks per CTA
+};
+
 // ---- dequantize kernel -----------------------------------------------------------------------
 struct DequantParams {
   const uint4* bq;
