@@ -96,6 +96,25 @@ int b200q_gemm_planned(const void* a, int lda, const void* bq, const void* scale
                        int K, int wtype, int zero_point, int group, int act_dtype, void* workspace,
                        size_t workspace_bytes, void* stream, const b200q_plan_t* plan);
 
+/* C = A x dequant(Bq) for callers that cannot hand over a workspace because they must not
+ * allocate device memory: a plugin inside a serving runtime that owns the whole GPU heap, a
+ * step that runs after the framework has frozen its memory plan, code on a path where
+ * cudaMalloc's implicit synchronisation is not acceptable.  (No counterpart in the
+ * reference, whose launcher always draws from its own growing pool,
+ * python/tilus/hidet/include/tilus/context.h:97-131.)
+ *
+ * Same arguments and results as b200q_gemm without `workspace`: the split-K scratch is a
+ * fixed array inside the library, b200q_static_workspace_limit() bytes (8 MiB) per GPU, held
+ * from library load to process exit.  Problems whose b200q_workspace_bytes exceeds that limit
+ * return B200Q_ERR_WORKSPACE and launch nothing.  The function allocates nothing and frees
+ * nothing.  The first call on each device looks the array's address up and clears it, so make
+ * that call outside any stream capture.  All calls on a device share the one array: calls
+ * that may overlap on the GPU (different streams) race on it and must be serialised by the
+ * caller; back-to-back calls on one stream are fine, each leaves the scratch zeroed. */
+int b200q_gemm_static_ws(const void* a, int lda, const void* bq, const void* scales, void* c, int ldc, int M, int N,
+                         int K, int wtype, int zero_point, int group, int act_dtype, void* stream);
+size_t b200q_static_workspace_limit(void);
+
 /* W[K, N] (fp16, row-major) = dequantized weights, bit-exact with the reference's
  * cast-then-scale (examples/quantization/matmul_a16wx.py:316-320; cast kernel
  * python/tilus/kernels/cast.py:27-55). */

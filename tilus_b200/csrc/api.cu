@@ -2,6 +2,7 @@
 // shape -> tile table, and kernel dispatch.  No torch types, no allocation.
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 
 #include <cuda.h>
 
@@ -399,6 +400,55 @@ int b200q_gemm(const void* a, int lda, const void* bq, const void* scales, void*
   st = make_plan(M, N, K, var, &pl);
   if (st != ST_OK) return st;
   return run_gemm(a, lda, bq, scales, c, ldc, M, N, K, var, group, workspace, workspace_bytes,
+                  reinterpret_cast<cudaStream_t>(stream), pl);
+}
+
+// ---- GEMM without a caller-supplied workspace and without any allocation ----------------------
+// The split-K scratch (status header, arrival counters, fp32 partial sums) lives in this
+// file-scope device array instead of a caller buffer.  Every GPU that loads the library holds
+// these bytes until the process exits.  In host code `g_static_ws` is only a handle for the
+// symbol, not a device address: the address each device uses is looked up once with
+// cudaGetSymbolAddress while that device is current.
+#define B200Q_STATIC_WS_BYTES (8u << 20)
+static __device__ __align__(256) unsigned char g_static_ws[B200Q_STATIC_WS_BYTES];
+
+static int static_ws_pointer(void** out, cudaStream_t stream) {
+  static std::mutex mu;
+  static void* ptrs[16] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) { g_last_cuda_error = (int)e; return ST_CUDA; }
+  if (dev < 0 || dev >= 16) return ST_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!ptrs[dev]) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_static_ws);  // device `dev` is current
+    if (e != cudaSuccess || !ptr) { g_last_cuda_error = (int)e; return ST_CUDA; }
+    // the kernels expect zeros and leave zeros; start from a known state all the same
+    e = cudaMemsetAsync(ptr, 0, B200Q_STATIC_WS_BYTES, stream);
+    if (e != cudaSuccess) { g_last_cuda_error = (int)e; return ST_CUDA; }
+    ptrs[dev] = ptr;
+  }
+  *out = ptrs[dev];
+  return ST_OK;
+}
+
+size_t b200q_static_workspace_limit(void) { return (size_t)B200Q_STATIC_WS_BYTES; }
+
+int b200q_gemm_static_ws(const void* a, int lda, const void* bq, const void* scales, void* c, int ldc, int M, int N,
+                         int K, int wtype, int zero_point, int group, int act_dtype, void* stream) {
+  if (act_dtype != B200Q_F16) return ST_UNSUPPORTED;
+  int var;
+  int st = check_problem(M, N, K, wtype, zero_point, group, 128, &var);
+  if (st != ST_OK) return st;
+  b200q_plan_t pl;
+  st = make_plan(M, N, K, var, &pl);
+  if (st != ST_OK) return st;
+  if (pl.workspace_bytes > (uint64_t)B200Q_STATIC_WS_BYTES) return ST_WORKSPACE;  // beyond the built-in scratch
+  void* ws = nullptr;
+  st = static_ws_pointer(&ws, reinterpret_cast<cudaStream_t>(stream));
+  if (st != ST_OK) return st;
+  return run_gemm(a, lda, bq, scales, c, ldc, M, N, K, var, group, ws, (size_t)B200Q_STATIC_WS_BYTES,
                   reinterpret_cast<cudaStream_t>(stream), pl);
 }
 
