@@ -1,24 +1,30 @@
 """Benchmark of the weight-only quantized matmul hot path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+                    [--no-sweep] [--no-prefill] [--profile-case decode|prefill|batch16]
 
 Headline workload (one GPU): decode GEMV, M=1, K=N=8192, uint4 codes with zero point 8,
 group 128, fp16 scales - the "u4 g128" decode configuration the metric is quoted on.
-One step = one pass over R distinct layers of that shape (R * weights > L2, so every
-launch streams its weights from HBM); the R launches are replayed from a CUDA graph.
-`value` is algorithmic GB/s: (packed weights + scales + activations + output) bytes of
-all launches divided by the device time of the timed region.  With N > 1 GPUs every rank
-runs the same per-GPU workload on its own column shard (weak scaling, no collective on
-the data path) and `value` is the aggregate.
+One step = ROUNDS passes over R distinct layers of that shape (R * weights > L2, so every
+launch streams its weights from HBM); the R * ROUNDS launches are replayed from one CUDA
+graph.  `value` is algorithmic GB/s: (packed weights + scales + activations + output)
+bytes of all launches divided by the device time of the timed region.  With N > 1 GPUs
+every rank runs the same per-GPU workload on its own column shard (weak scaling, no
+collective on the data path) and `value` is the aggregate.
 
 The JSON line also carries: `roofline` (HBM, for the GEMV kernel), `e2e` (same metric
 through QuantizedLinear.forward with pinned host activations copied in and the result
-copied out every call), `cpu_baseline` (the CPU oracle - the reference's PyTorch
+copied out every step), `cpu_baseline` (the CPU oracle - the reference's PyTorch
 dequantize + matmul semantics - timed on this host), `clocks`, `gpu_launches`, and an
-`extra` sweep (other bit widths, M=16, and the M=4096 prefill GEMM in TFLOP/s).
+`extra` sweep: the other bit widths at M=1, M=16, the M=16 K=N=4096 configuration, the
+per-channel float6 / int3 batch sweep, the Llama-3-8B layer shapes at M in {1, 8, 32, 64}
+and the M=4096 prefill GEMM in TFLOP/s.
 
 `--impl reference` times the CPU dequantize + matmul path alone (the reference operator's
 semantics on the host cores), on the same workload and metric.
+
+`--profile-case X` runs a few plain launches of one kernel on a problem larger than L2 and
+prints its CUDA-event time: the command line used for the ncu captures under profiles/.
 """
 from __future__ import annotations
 
@@ -39,6 +45,11 @@ import torch  # noqa: E402
 M, K, N, GROUP, NBITS = 1, 8192, 8192, 128, 4
 WORKLOAD = "decode_gemv_u4_g128_M1_K8192_N8192"
 METRIC = "quant-GEMM HBM GB/s (u4 g128, M=1, K=N=8192)"
+R_LAYERS = 10   # distinct layers per pass: 10 x 33.5 MB of weights = 335 MB > 126 MB L2
+ROUNDS = 10     # passes per graph: 100 launches per replay
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the headline kernel, from the
+# ncu capture summarised in profiles/stream_kernel_u4_m1_k8192_n8192.md
+DECODE_DRAM_TRAFFIC_BYTES = 34_700_000
 
 
 def _peaks():
@@ -152,20 +163,33 @@ def _time_graph(graph, reps: int) -> float:
     return e0.elapsed_time(e1)
 
 
-def _make_layers(dt, m, n, k, group, count, dev, seed=0, scale_range=(0.005, 0.02)):
+def _make_layers(dt, n, k, group, count, dev, seed=0, scale_range=(0.005, 0.02), distinct=True):
+    """`count` QuantizedLinear layers [k -> n] on the device.  distinct=False generates one
+    synthetic problem and gives every layer its own copy of it (same timing, faster set-up)."""
     from tilus_b200 import QuantizedLinear, float16, synth
 
-    layers, acts = [], []
+    layers = []
+    first = None
     for i in range(count):
-        prob = synth.make_problem(m, n, k, dt, group, seed=seed + i, scale_range=scale_range)
-        layer = QuantizedLinear(float16, dt, group, k, n, zero_point=prob["zero_point"]).to(dev)
-        layer.load_codes(prob["codes"].to(dev), prob["scales"].to(dev))
+        if distinct or first is None:
+            prob = synth.make_problem(1, n, k, dt, group, seed=seed + i, scale_range=scale_range)
+            layer = QuantizedLinear(float16, dt, group, k, n, zero_point=prob["zero_point"]).to(dev)
+            layer.load_codes(prob["codes"].to(dev), prob["scales"].to(dev))
+            if first is None:
+                first = layer
+        else:
+            layer = QuantizedLinear(float16, dt, group, k, n, zero_point=first.zero_point).to(dev)
+            layer.load_packed(first.quantized_weight.data.clone(), first.scales.data.clone(), layout="b200")
         layers.append(layer)
-        acts.append(prob["a"].to(dev))
-    return layers, acts
+    return layers
 
 
-def _capture(layers, acts):
+def _acts(m, k, count, dev, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randn(m, k, generator=g, dtype=torch.float32).to(torch.float16).to(dev) for _ in range(count)]
+
+
+def _capture(layers, acts, rounds=1):
     outs = [None] * len(layers)
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
@@ -175,25 +199,70 @@ def _capture(layers, acts):
     torch.cuda.synchronize()
     g = torch.cuda.CUDAGraph()
     with torch.cuda.graph(g, stream=side):
-        for i, (layer, a) in enumerate(zip(layers, acts)):
-            outs[i] = layer(a)
+        for _ in range(rounds):
+            for i, (layer, a) in enumerate(zip(layers, acts)):
+                outs[i] = layer(a)
     return g, outs
 
 
-def _sweep_entry(dt, m, n, k, group, dev, reps, scale_range=(0.005, 0.02)):
-    """GB/s and TFLOP/s of one shape, layers rotated so the weights stream from HBM."""
+def _layer_count(dt, n, k):
+    """Enough layers that one pass streams more than 300 MiB of weights (> L2)."""
+    wbytes = k * n * dt.nbits // 8
+    return max(2, min(40, (300 * 2**20 + wbytes - 1) // wbytes))
+
+
+def _sweep_shape(dt, n, k, group, ms_list, dev, reps, scale_range=(0.005, 0.02)):
+    """us / GB/s / TFLOP/s of one layer shape for each M, layers rotated so weights stream from HBM."""
     from tilus_b200 import synth
 
-    wbytes = k * n * dt.nbits // 8
-    count = max(2, min(16, (300 * 2**20 + wbytes - 1) // wbytes))
-    layers, acts = _make_layers(dt, m, n, k, group, count, dev, seed=100, scale_range=scale_range)
-    g, _ = _capture(layers, acts)
-    _time_graph(g, 3)
-    ms = _time_graph(g, reps) / (reps * count)
-    nbytes = synth.gemm_bytes(m, n, k, dt.nbits, group)
-    del layers, acts, g
+    count = _layer_count(dt, n, k)
+    layers = _make_layers(dt, n, k, group, count, dev, seed=100, scale_range=scale_range, distinct=False)
+    out = {}
+    for m in ms_list:
+        acts = _acts(m, k, count, dev, seed=m)
+        rounds = max(1, 40 // count) if m <= 64 else 1
+        g, _ = _capture(layers, acts, rounds)
+        _time_graph(g, 3)
+        ms = _time_graph(g, reps) / (reps * count * rounds)
+        nbytes = synth.gemm_bytes(m, n, k, dt.nbits, group)
+        out[m] = {"us": ms * 1e3, "gbs": nbytes / (ms * 1e-3) / 1e9,
+                  "tflops": synth.gemm_flops(m, n, k) / (ms * 1e-3) / 1e12}
+        del g, acts
+    del layers
     torch.cuda.empty_cache()
-    return {"us": ms * 1e3, "gbs": nbytes / (ms * 1e-3) / 1e9, "tflops": synth.gemm_flops(m, n, k) / (ms * 1e-3) / 1e12}
+    return out
+
+
+def run_profile_case(args) -> None:
+    """A few plain (non-graph) launches of one kernel on inputs larger than L2."""
+    from tilus_b200 import dtypes
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    case = args.profile_case
+    if case == "decode":
+        dt, m, n, k, count = dtypes.uint4b, 1, 8192, 8192, 6
+    elif case == "batch16":
+        dt, m, n, k, count = dtypes.uint4b, 16, 8192, 8192, 6
+    elif case == "prefill":
+        dt, m, n, k, count = dtypes.int4b, 4096, 7168, 8192, 2
+    else:
+        raise SystemExit(f"unknown profile case {case}")
+    layers = _make_layers(dt, n, k, GROUP, count, dev, seed=0, distinct=False)
+    acts = _acts(m, k, count, dev)
+    for _ in range(2):
+        for layer, a in zip(layers, acts):
+            layer(a)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for layer, a in zip(layers, acts):
+        layer(a)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / count
+    print(json.dumps({"profile_case": case, "dtype": dt.name, "M": m, "N": n, "K": k, "launches": 3 * count,
+                      "us_per_launch_plain_stream": us}))
 
 
 def run_b200(args) -> None:
@@ -210,9 +279,9 @@ def run_b200(args) -> None:
         dist.init_process_group("nccl", device_id=dev)
     peaks = _peaks()
     dt = dtypes.uint4b
-    R = 10  # distinct layers per step: 10 x 33.5 MB of weights = 335 MB > 126 MB L2
-    layers, acts = _make_layers(dt, M, N, K, GROUP, R, dev, seed=1000 * rank)
-    graph, outs = _capture(layers, acts)
+    layers = _make_layers(dt, N, K, GROUP, R_LAYERS, dev, seed=1000 * rank)
+    acts = _acts(M, K, R_LAYERS, dev, seed=rank)
+    graph, outs = _capture(layers, acts, ROUNDS)
     nbytes = synth.gemm_bytes(M, N, K, NBITS, GROUP)
 
     def barrier():
@@ -226,8 +295,8 @@ def run_b200(args) -> None:
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    # keep the region long enough for a few clock samples
-    inner = max(1, int(0.4 / (R * 6e-6 * args.steps)))
+    # a step = `inner` graph replays, long enough for a few clock samples over the timed region
+    inner = max(1, int(0.5 / (R_LAYERS * ROUNDS * 8e-6 * args.steps)))
     barrier()
     ms = _time_graph(graph, args.steps * inner)
     barrier()
@@ -236,31 +305,33 @@ def run_b200(args) -> None:
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item())
-    launches = args.steps * inner * R
+    launches = args.steps * inner * R_LAYERS * ROUNDS
     per_launch_s = ms * 1e-3 / launches
     value = world * nbytes / per_launch_s / 1e9
 
     # ---- end to end through the public module, host buffers in and out --------------
+    # every step copies each layer's activations from pinned host memory, runs the layer and
+    # copies its result back; one synchronisation per step (the result is read on the host)
     host_in = [a.cpu().pin_memory() for a in acts]
-    host_out = torch.empty(M, N, dtype=torch.float16).pin_memory()
-    dev_in = torch.empty(M, K, dtype=torch.float16, device=dev)
+    host_out = [torch.empty(M, N, dtype=torch.float16).pin_memory() for _ in range(R_LAYERS)]
+    dev_in = [torch.empty(M, K, dtype=torch.float16, device=dev) for _ in range(R_LAYERS)]
 
     def e2e_step():
-        for layer, h in zip(layers, host_in):
-            dev_in.copy_(h, non_blocking=True)
-            c = layer(dev_in)
-            host_out.copy_(c, non_blocking=True)
-            torch.cuda.current_stream().synchronize()
+        for layer, h, d, o in zip(layers, host_in, dev_in, host_out):
+            d.copy_(h, non_blocking=True)
+            o.copy_(layer(d), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return float(host_out[-1][0, 0])
 
     for _ in range(3):
         e2e_step()
     barrier()
     t0 = time.perf_counter()
-    e2e_steps = max(args.steps, 5)
+    e2e_steps = max(args.steps, 5) * 20
     for _ in range(e2e_steps):
         e2e_step()
     torch.cuda.synchronize()
-    e2e_s = (time.perf_counter() - t0) / (e2e_steps * R)
+    e2e_s = (time.perf_counter() - t0) / (e2e_steps * R_LAYERS)
     t = torch.tensor([e2e_s], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -275,12 +346,13 @@ def run_b200(args) -> None:
     # ---- correctness of what was timed ---------------------------------------------
     from oracle import quant_oracle as qo
 
-    prob0 = synth.make_problem(M, N, K, dt, GROUP, seed=0)
-    ref = qo.quantized_matmul(prob0["a"].numpy(), prob0["codes"].numpy(), prob0["scales"].numpy(), dt, GROUP, 8)
+    prob0 = synth.make_problem(1, N, K, dt, GROUP, seed=0)
+    ref = qo.quantized_matmul(acts[0].cpu().numpy(), prob0["codes"].numpy(), prob0["scales"].numpy(), dt, GROUP, 8)
     got = outs[0].float().cpu().numpy()
     rel = float(abs(got - ref.astype("float32")).max() / abs(ref.astype("float32")).max())
 
     # ---- CPU baseline (bounded sample) -----------------------------------------------
+    prob0["a"] = acts[0].cpu()
     cpu_s = _cpu_gemv_seconds(prob0, 5)
     cpu_baseline = {"value": nbytes / cpu_s / 1e9, "unit": "GB/s", "cores": os.cpu_count() or 1, "kind": "port",
                     "sample": "5 full M=1 K=N=8192 u4 g128 dequantize+matmul calls (oracle, torch CPU threads)"}
@@ -288,39 +360,53 @@ def run_b200(args) -> None:
     # ---- extra sweep -------------------------------------------------------------------
     extra = {}
     if world == 1 and not args.no_sweep:
-        del graph, layers, acts
+        del graph, layers, acts, dev_in
         torch.cuda.empty_cache()
+        hbm = peaks["hbm_gbs"]
+
+        def mem_entry(r):
+            return {"us": round(r["us"], 3), "gbs": round(r["gbs"], 1), "hbm_frac": round(r["gbs"] / hbm, 4)}
+
         for d in (dtypes.uint1b, dtypes.uint2b, dtypes.uint3b, dtypes.uint6b, dtypes.uint8):
-            r = _sweep_entry(d, 1, N, K, GROUP, dev, 20)
-            extra[f"decode_{d.short_name}_M1"] = {"us": round(r["us"], 3), "gbs": round(r["gbs"], 1),
-                                                  "hbm_frac": round(r["gbs"] / peaks["hbm_gbs"], 4)}
-        r = _sweep_entry(dtypes.uint4b, 16, 8192, 8192, GROUP, dev, 20)
-        extra["decode_u4_M16"] = {"us": round(r["us"], 3), "gbs": round(r["gbs"], 1),
-                                  "hbm_frac": round(r["gbs"] / peaks["hbm_gbs"], 4)}
-        r = _sweep_entry(dtypes.uint4b, 16, 4096, 4096, GROUP, dev, 20)
-        extra["config0_u4_M16_K4096_N4096"] = {"us": round(r["us"], 3), "gbs": round(r["gbs"], 1),
-                                               "hbm_frac": round(r["gbs"] / peaks["hbm_gbs"], 4)}
+            extra[f"decode_{d.short_name}_M1"] = mem_entry(_sweep_shape(d, N, K, GROUP, [1], dev, 10)[1])
+        r = _sweep_shape(dtypes.uint4b, 8192, 8192, GROUP, [8, 16], dev, 10)
+        extra["decode_u4_M8"] = mem_entry(r[8])
+        extra["decode_u4_M16"] = mem_entry(r[16])
+        extra["config0_u4_M16_K4096_N4096"] = mem_entry(_sweep_shape(dtypes.uint4b, 4096, 4096, GROUP, [16], dev, 10)[16])
+        for d in (dtypes.float6_e3m2, dtypes.int3b):
+            r = _sweep_shape(d, 4096, 4096, 4096, [1, 4, 16, 64, 256], dev, 10, scale_range=(0.5, 2.0))
+            for m, v in r.items():
+                extra[f"perchannel_{d.short_name}_M{m}_K4096_N4096"] = mem_entry(v)
+        for name, k_in, n_out in (("qkv", 4096, 6144), ("o", 4096, 4096), ("gate_up", 4096, 28672),
+                                  ("down", 14336, 4096)):
+            r = _sweep_shape(dtypes.uint4b, n_out, k_in, GROUP, [1, 8, 32, 64], dev, 10)
+            for m, v in r.items():
+                extra[f"llama8b_{name}_M{m}"] = mem_entry(v)
         if not args.no_prefill:
-            r = _sweep_entry(dtypes.int4b, 4096, 28672, 8192, GROUP, dev, 2)
+            r = _sweep_shape(dtypes.int4b, 28672, 8192, GROUP, [4096], dev, 3)[4096]
             extra["prefill_i4_M4096_K8192_N28672"] = {
                 "ms": round(r["us"] / 1e3, 4), "tflops": round(r["tflops"], 1),
-                "tensor_frac_of_measured_burst": round(r["tflops"] / peaks["tflops"], 4) if peaks["tflops"] else None}
+                "tensor_frac_of_measured_burst": round(r["tflops"] / peaks["tflops"], 4) if peaks["tflops"] else None,
+                "tensor_frac_of_measured_sustained":
+                    round(r["tflops"] / peaks["tflops_sustained"], 4) if peaks["tflops_sustained"] else None}
 
     achieved = nbytes / per_launch_s / 1e9
     line = {
         "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "layers_per_step": R, "replays_per_step": inner,
-                   "l2": f"inputs larger than L2: {R} distinct weight sets, {R * K * N // 2 // 2**20} MiB, rotated",
+        "config": {"workload": WORKLOAD, "layers_per_pass": R_LAYERS, "passes_per_graph": ROUNDS,
+                   "replays_per_step": inner,
+                   "l2": f"inputs larger than L2: {R_LAYERS} distinct weight sets, "
+                         f"{R_LAYERS * K * N // 2 // 2**20} MiB, rotated",
                    "sharding": "one column shard of this shape per GPU, no data-path collective"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                     "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
-                     "kernel": "skinny_kernel<u4 zp8, MT=1>", "bytes_per_launch": nbytes,
-                     "us_per_launch": per_launch_s * 1e6},
+                     "frac": achieved / peaks["hbm_gbs"], "traffic": DECODE_DRAM_TRAFFIC_BYTES,
+                     "peak_source": peaks["source"], "kernel": "stream_kernel<u4 zp8, MT=1>",
+                     "bytes_per_launch": nbytes, "us_per_launch": per_launch_s * 1e6},
         "cpu_baseline": cpu_baseline,
-        "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": R * M * K * 2,
-                "d2h_bytes_per_step": R * M * N * 2, "us_per_call": e2e_s * 1e6},
+        "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": R_LAYERS * M * K * 2,
+                "d2h_bytes_per_step": R_LAYERS * M * N * 2, "us_per_call": e2e_s * 1e6},
         "gpu_launches": launches,
         "clocks": clocks,
         "parity": {"rel_err_vs_oracle": rel, "tolerance": 1e-2},
@@ -340,9 +426,13 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-sweep", action="store_true", help="skip the extra dtype / shape sweep")
     ap.add_argument("--no-prefill", action="store_true", help="skip the M=4096 prefill entry of the sweep")
+    ap.add_argument("--profile-case", default=None, choices=["decode", "batch16", "prefill"],
+                    help="run a few plain launches of one kernel (for ncu) instead of the benchmark")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.profile_case:
+        run_profile_case(args)
     else:
         run_b200(args)
 

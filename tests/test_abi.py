@@ -40,8 +40,12 @@ def test_versions_and_strings(lib):
 
 def test_plan_static_table():
     p = ops.plan(1, 8192, 8192, "uint4b", 8, 128)
-    assert p["kernel"] == 0 and p["splits"] * p["ctas_per_split"] <= 148 * 2
+    # decode shapes run the mma.sync stream kernel: two CTAs per SM, a CTA count that divides the
+    # 512 column tiles, at most half an SM's shared memory each
+    assert p["kernel"] == 2 and p["splits"] * p["ctas_per_split"] <= 148 * 2
+    assert (8192 // 16) % p["ctas_per_split"] == 0 and p["smem_bytes"] <= 113 * 1024 and p["stages"] >= 2
     assert p["workspace_bytes"] >= 256 + 8192 * 4
+    assert ops.plan(4096, 28672, 8192, "int4b", 0, 128)["kernel"] == 1  # prefill: tcgen05 kernel
     p16 = ops.plan(16, 4096, 4096, "uint4b", 8, 128)
     assert p16["m_tiles"] == 2 and p16["smem_bytes"] <= 227 * 1024
     # per-channel scales, float weights

@@ -82,24 +82,34 @@ def test_gemm_ragged_m(M):
     assert _rel_err(c, ref) <= REL_TOL
 
 
-@pytest.mark.parametrize("splits,ctas", [(1, 1), (1, 5), (2, 3), (4, 8), (4, 17)])
-@pytest.mark.parametrize("cluster", [1, 2])
-def test_gemm_split_k_shapes_and_clean_workspace(splits, ctas, cluster):
-    if splits % cluster:
-        pytest.skip("cluster size must divide the split count")
+def _forced(M, N, K, dt, zp, override, seed=11, group=128):
+    """Runs one problem twice with a forced plan on one workspace; checks parity and that the
+    workspace is left zeroed."""
     dev = _dev()
-    M, N, K = 3, 272, 2048
-    prob = synth.make_problem(M, N, K, D.int4b, 128, seed=11)
-    dt = D.int4b
+    prob = synth.make_problem(M, N, K, dt, group, seed=seed)
+    prob["zero_point"] = zp
     bq = packing.interleave(prob["codes"], dt).to(dev)
-    ws = torch.zeros(ops.workspace_bytes(M, N, K, dt, 0, 128), dtype=torch.uint8, device=dev)
-    ref = qo.quantized_matmul(prob["a"].numpy(), prob["codes"].numpy(), prob["scales"].numpy(), dt, 128, 0)
+    ws = torch.zeros(ops.workspace_bytes(M, N, K, dt, zp, group), dtype=torch.uint8, device=dev)
+    ref = qo.quantized_matmul(prob["a"].numpy(), prob["codes"].numpy(), prob["scales"].numpy(), dt, group, zp)
     for _ in range(2):  # second call runs on the workspace the first one left behind
-        c = ops.quantized_matmul(prob["a"].to(dev), bq, prob["scales"].to(dev), dt, 128, 0, workspace=ws,
-                                 plan_override=dict(splits=splits, ctas_per_split=ctas, cluster=cluster))
+        c = ops.quantized_matmul(prob["a"].to(dev), bq, prob["scales"].to(dev), dt, group, zp, workspace=ws,
+                                 plan_override=override)
         torch.cuda.synchronize()
         assert _rel_err(c.cpu().numpy(), ref) <= REL_TOL
         assert int(ws.count_nonzero()) == 0, "workspace not restored to zero"
+
+
+@pytest.mark.parametrize("splits,ctas", [(1, 1), (1, 5), (2, 3), (4, 8), (4, 17)])
+def test_stream_kernel_shapes_and_clean_workspace(splits, ctas):
+    """Kernel 2 (mma.sync, ring-fed) with forced k chunks and CTA counts: own tiles in shared
+    memory, left-over tiles through the global scratch."""
+    _forced(3, 272, 2048, D.int4b, 0, dict(kernel=2, splits=splits, ctas_per_split=ctas, cluster=1, stages=3, pdl=1))
+
+
+@pytest.mark.parametrize("dt,zp", [(D.uint4b, 8), (D.uint3b, 4), (D.float6_e3m2, 0), (D.uint8, 0)],
+                         ids=lambda x: getattr(x, "name", str(x)))
+def test_stream_kernel_variants(dt, zp):
+    _forced(9, 256, 1024, dt, zp, dict(kernel=2, splits=2, ctas_per_split=7, cluster=1, stages=2, pdl=1), seed=5)
 
 
 def test_config0_m16_k4096_n4096_u4():

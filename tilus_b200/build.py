@@ -38,7 +38,7 @@ def _nvcc() -> str:
 def _jobs():
     jobs = []
     for part in range(NPARTS):
-        jobs.append(("skinny_kernel.cu", f"skinny_part{part}.o", [f"-DB200Q_NPARTS={NPARTS}", f"-DB200Q_PART={part}"]))
+        jobs.append(("stream_kernel.cu", f"stream_part{part}.o", [f"-DB200Q_NPARTS={NPARTS}", f"-DB200Q_PART={part}"]))
     for part in range(NPARTS):
         jobs.append(("umma_kernel.cu", f"umma_part{part}.o", [f"-DB200Q_NPARTS={NPARTS}", f"-DB200Q_PART={part}"]))
     jobs.append(("dequant_kernel.cu", "dequant.o", []))

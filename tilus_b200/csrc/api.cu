@@ -15,29 +15,30 @@
 
 namespace b200q {
 
-#define B200Q_DECL_PART(i) \
-  cudaError_t skinny_launch_part##i(int, const SkinnyParams&, int, int, cudaStream_t);
-B200Q_DECL_PART(0) B200Q_DECL_PART(1) B200Q_DECL_PART(2) B200Q_DECL_PART(3)
-B200Q_DECL_PART(4) B200Q_DECL_PART(5) B200Q_DECL_PART(6) B200Q_DECL_PART(7)
+#define B200Q_DECL_SPART(i) \
+  cudaError_t stream_launch_part##i(int, const StreamParams&, int, int, cudaStream_t);
+B200Q_DECL_SPART(0) B200Q_DECL_SPART(1) B200Q_DECL_SPART(2) B200Q_DECL_SPART(3)
+B200Q_DECL_SPART(4) B200Q_DECL_SPART(5) B200Q_DECL_SPART(6) B200Q_DECL_SPART(7)
 cudaError_t dequant_launch(int var, const DequantParams& p, cudaStream_t stream);
 #define B200Q_DECL_UPART(i) \
   cudaError_t umma_launch_part##i(int, const UmmaParams&, const void*, int, cudaStream_t);
 B200Q_DECL_UPART(0) B200Q_DECL_UPART(1) B200Q_DECL_UPART(2) B200Q_DECL_UPART(3)
 B200Q_DECL_UPART(4) B200Q_DECL_UPART(5) B200Q_DECL_UPART(6) B200Q_DECL_UPART(7)
-int umma_smem_bytes(int tm);
+int umma_smem_bytes(int tm, int bits, int a_stages);
+int umma_a_stages(int tm, int bits, int max_smem);
 
 static thread_local int g_last_cuda_error = 0;
 
-static cudaError_t skinny_launch(int var, const SkinnyParams& p, int mt, int smem, cudaStream_t s) {
+static cudaError_t stream_launch(int var, const StreamParams& p, int mt, int smem, cudaStream_t s) {
   switch (var % B200Q_NPARTS) {
-    case 0: return skinny_launch_part0(var, p, mt, smem, s);
-    case 1: return skinny_launch_part1(var, p, mt, smem, s);
-    case 2: return skinny_launch_part2(var, p, mt, smem, s);
-    case 3: return skinny_launch_part3(var, p, mt, smem, s);
-    case 4: return skinny_launch_part4(var, p, mt, smem, s);
-    case 5: return skinny_launch_part5(var, p, mt, smem, s);
-    case 6: return skinny_launch_part6(var, p, mt, smem, s);
-    default: return skinny_launch_part7(var, p, mt, smem, s);
+    case 0: return stream_launch_part0(var, p, mt, smem, s);
+    case 1: return stream_launch_part1(var, p, mt, smem, s);
+    case 2: return stream_launch_part2(var, p, mt, smem, s);
+    case 3: return stream_launch_part3(var, p, mt, smem, s);
+    case 4: return stream_launch_part4(var, p, mt, smem, s);
+    case 5: return stream_launch_part5(var, p, mt, smem, s);
+    case 6: return stream_launch_part6(var, p, mt, smem, s);
+    default: return stream_launch_part7(var, p, mt, smem, s);
   }
 }
 
@@ -87,6 +88,18 @@ static int variant_of(int wtype, int zero_point) {
   return -1;
 }
 
+#ifdef B200Q_TIMELINE
+// side builds only: a buffer of [slots][grid][8] device timestamps, one slot per launch
+static unsigned long long* g_tl_buf = nullptr;
+static int g_tl_slots = 0, g_tl_next = 0;
+extern "C" int b200q_debug_set_timeline(void* buf, int slots) {
+  g_tl_buf = reinterpret_cast<unsigned long long*>(buf);
+  g_tl_slots = slots;
+  g_tl_next = 0;
+  return 0;
+}
+#endif
+
 struct DeviceInfo {
   int sm_count = 0;
   int max_smem = 0;
@@ -108,84 +121,68 @@ static DeviceInfo device_info() {
 // shared-memory row pitch (halfs) of an activation chunk of kc columns: 16 bytes of padding
 // per 32 columns, and pitch bytes = 64 (mod 128), so that 8 lanes reading 16 bytes each from
 // two rows x four 32-column units touch 8 different 16-byte bank groups
-static int skinny_pitch(int kc) {
+static int stream_pitch(int kc) {
   int bytes = kc * 2 + (kc / 32) * 16;
   if (bytes % 128 != 64) bytes += (64 - bytes % 128 + 128) % 128;
   return bytes / 2;
 }
-// warps per CTA of the skinny kernel (fixed by its launch bounds)
-// mirrors of skinny_kernel.cu: 8 warps per CTA, one weight ring per warp, items of GI groups
-static const int kSkinnyWarps = 8;
-static int skinny_item_bytes(int bits) { return (bits <= 2 ? 4 : 2) * 256 * bits; }
-// dynamic shared memory of the skinny kernel: barriers + per-warp weight rings + output tile
-// sums + activation chunk + per-group activation sums
-static int skinny_smem(int m_pass, int kc, int bits, int stages, int tiles_max) {
-  const int mt = (m_pass + 7) / 8;
-  return 512 + kSkinnyWarps * stages * skinny_item_bytes(bits) + tiles_max * 16 * 8 * mt * 4 +
-         m_pass * skinny_pitch(kc) * 2 + (kc / 128) * 8 * mt * 4;
+// ---- stream kernel (kernel 2): one CTA per SM, half an SM each ---------------------------------
+// Two consecutive launches share an SM (the second prefetches while the first computes), so a
+// CTA may use half of the SM's shared memory: (228 KB - 2 x 1 KB reserved) / 2.
+static const int kStreamSmemCap = 113 * 1024;
+static int stream_slot_bytes(int bits) { return stream_gi(bits) * 256 * bits; }
+// whole column tiles a CTA owns (their sums live in at most 16 KB of shared memory)
+static int stream_tiles_owned(int m_pass, int NT, int cpc) {
+  const int mt = (m_pass + 7) / 8, cap = 32 / mt;
+  const int t = NT / cpc;
+  return t < cap ? t : cap;
 }
-// k splits inside a cluster (reduced through distributed shared memory): pairs of CTAs
-// (clusters of four 200 KB CTAs measured twice as slow: fewer of them fit a GPC at once)
-static int skinny_cluster(int splits) { return splits % 2 == 0 ? 2 : 1; }
-
-// ---- static shape -> tile table ------------------------------------------------------------
-// Exact entries for the shapes this library is benchmarked on come first; anything else
-// goes through the balance rule below.
-struct TableEntry {
-  int bits, m_lo, m_hi, N, K;
-  int splits;
-};
-static const TableEntry kSkinnyTable[] = {
-    // bits  M range   N      K     S
-    {4, 1, 8, 8192, 8192, 1},
-};
-
-static int plan_skinny(int m_pass, int N, int K, int bits, const DeviceInfo& di, b200q_plan_t* pl) {
-  const int KB = K / BLOCK_K, NT = N / BLOCK_N;
+static int stream_fixed_smem(int m_pass, int kc, int t_own) {
   const int mt = (m_pass + 7) / 8;
-  const int ipb = bits <= 2 ? 1 : 2;  // items per block
-  int forced = 0;
-  for (const TableEntry& t : kSkinnyTable)
-    if (t.bits == bits && m_pass >= t.m_lo && m_pass <= t.m_hi && t.N == N && t.K == K) forced = t.splits;
-  double best_cost = 1e30;
-  int best_s = 0, best_p = 0, best_st = 0;
-  for (int pass = 0; pass < 2 && !best_s; ++pass) {  // pass 0 honours the table, pass 1 ignores it
+  // barriers, own-tile sums, activation chunk (+ 64 zero bytes), group sums as accumulator quads
+  return 1024 + STREAM_WARPS * STREAM_SC_GROUPS * 32 + t_own * 16 * 8 * mt * 4 + m_pass * stream_pitch(kc) * 2 + 64 +
+         (kc / 128) * 16 * mt * 4;
+}
+static int stream_smem(int m_pass, int kc, int bits, int stages, int t_own) {
+  return stream_fixed_smem(m_pass, kc, t_own) + STREAM_WARPS * stages * stream_slot_bytes(bits);
+}
+static int stream_stages_for(int m_pass, int kc, int bits, int t_own) {
+  int st = (kStreamSmemCap - stream_fixed_smem(m_pass, kc, t_own)) / (STREAM_WARPS * stream_slot_bytes(bits));
+  return st > 8 ? 8 : st;
+}
+// CTAs per k chunk.  First choice: two CTAs per SM (32 warps hide the latency of the decode /
+// mma chains best) with a count that divides the column tiles evenly, so that no tile is
+// shared between CTAs and nothing goes through the global scratch; then one CTA per SM with
+// such a count; else one CTA per SM with the left-over tiles shared item-wise.
+static int stream_ctas_per_chunk(int NT, int s, const DeviceInfo& di) {
+  const int full = di.sm_count / s;
+  for (int c = 2 * full; c >= 1 && c * 5 >= full * 8; --c)
+    if (NT % c == 0) return c;
+  for (int c = full; c >= 1 && c * 5 >= full * 4; --c)
+    if (NT % c == 0) return c;
+  return full > NT ? NT : full;
+}
+// K is cut into the fewest chunks S (a divisor of K/512, at most one per SM) that leave room for
+// three ring slots per warp next to the activation chunk [M, K/S]; the grid is S * CPC.
+static int plan_stream(int m_pass, int N, int K, int bits, const DeviceInfo& di, b200q_plan_t* pl) {
+  const int KB = K / BLOCK_K, NT = N / BLOCK_N;
+  int best_s = 0, best_st = 0, best_c = 0;
+  for (int want = 3; want >= 1 && !best_s; --want)
     for (int s = 1; s <= KB && s <= di.sm_count; ++s) {
       if (KB % s) continue;
-      if (pass == 0 && forced && s != forced) continue;
-      const int kbc = KB / s;
-      for (int occ = 2; occ >= 1; --occ) {  // CTAs per SM
-        int P = di.sm_count * occ / s;
-        if (P < 1) continue;
-        if (P > NT) P = NT;
-        const int tiles_max = (NT + P - 1) / P;
-        const int fixed = skinny_smem(m_pass, kbc * 512, bits, 0, tiles_max);
-        const int cap = (di.max_smem + 1024) / occ - 1024 - (occ == 2 ? 1024 : 0);
-        int stages = (cap - fixed) / (kSkinnyWarps * skinny_item_bytes(bits));
-        if (stages > 8) stages = 8;
-        if (stages < 2) continue;
-        const int cta_items = tiles_max * kbc * ipb;
-        const int warp_items = (cta_items + kSkinnyWarps - 1) / kSkinnyWarps;
-        const int gs = s / skinny_cluster(s);
-        // time ~ the busiest SM's longest warp, staging the activation chunk, reduction traffic
-        const double cost = (double)warp_items * kSkinnyWarps * occ / ipb + 0.05 * m_pass * kbc * occ + 0.3 * s +
-                            2.0 * (s > 1) + 3.0 * (gs > 1) + (stages < 3 ? 2.0 : 0.0) + (occ == 1 ? 1.0 : 0.0);
-        if (cost < best_cost) { best_cost = cost; best_s = s; best_p = P; best_st = stages; }
-      }
+      const int cpc = stream_ctas_per_chunk(NT, s, di);
+      const int st = stream_stages_for(m_pass, (KB / s) * 512, bits, stream_tiles_owned(m_pass, NT, cpc));
+      if (st >= want) { best_s = s; best_st = st; best_c = cpc; break; }
     }
-  }
   if (!best_s) return ST_UNSUPPORTED;
-  const int kbc = KB / best_s;
-  // enough bytes in flight per CTA to cover the memory latency; more only costs shared memory
-  while (best_st > 3 && kSkinnyWarps * (best_st - 1) * skinny_item_bytes(bits) >= 64 * 1024) --best_st;
-  pl->kernel = 0;
-  pl->m_tiles = mt;
+  pl->kernel = 2;
+  pl->m_tiles = (m_pass + 7) / 8;
   pl->splits = best_s;
-  pl->cluster = skinny_cluster(best_s);
-  pl->ctas_per_split = best_p;
-  pl->warps = kSkinnyWarps;
+  pl->cluster = 1;
+  pl->ctas_per_split = best_c;
+  pl->warps = STREAM_WARPS;
   pl->stages = best_st;
-  pl->smem_bytes = skinny_smem(m_pass, kbc * 512, bits, best_st, (NT + best_p - 1) / best_p);
+  pl->smem_bytes = stream_smem(m_pass, (KB / best_s) * 512, bits, best_st, stream_tiles_owned(m_pass, NT, best_c));
   pl->tile_m = 0;
   pl->pdl = 1;
   pl->debug = 0;
@@ -212,7 +209,7 @@ static int gshift_of(int group, int K) {
 }
 
 // tcgen05 kernel: tile rows, tiles and split-K so that the grid fills the SMs
-static void plan_umma(int M, int N, int K, const DeviceInfo& di, b200q_plan_t* pl) {
+static void plan_umma(int M, int N, int K, int bits, const DeviceInfo& di, b200q_plan_t* pl) {
   const int tm = M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
   const int m_tiles = (M + tm - 1) / tm, n_tiles = (N + 127) / 128;
   const int ctas = m_tiles * n_tiles;
@@ -220,17 +217,17 @@ static void plan_umma(int M, int N, int K, const DeviceInfo& di, b200q_plan_t* p
   int splits = 1;
   if (ctas * 2 <= di.sm_count && ctas <= N / BLOCK_N) {
     for (int s = 2; s <= 16; ++s)
-      if (kblocks % s == 0 && kblocks / s >= 8 && ctas * s <= di.sm_count + di.sm_count / 8) splits = s;
+      if (kblocks % (2 * s) == 0 && kblocks / s >= 8 && ctas * s <= di.sm_count + di.sm_count / 8) splits = s;
   }
   pl->kernel = 1;
   pl->m_tiles = m_tiles;
   pl->splits = splits;
   pl->cluster = 1;
   pl->ctas_per_split = ctas;
-  pl->smem_bytes = umma_smem_bytes(tm);
+  pl->stages = umma_a_stages(tm, bits, di.max_smem);
+  pl->smem_bytes = umma_smem_bytes(tm, bits, pl->stages);
   pl->tile_m = tm;
-  pl->stages = 4;
-  pl->warps = 10;
+  pl->warps = 15;
   pl->passes = 1;
   pl->pdl = 0;
   pl->debug = 0;
@@ -241,18 +238,20 @@ static int make_plan(int M, int N, int K, int var, b200q_plan_t* pl) {
   std::memset(pl, 0, sizeof(*pl));
   const int bits = var_bits(var);
   if (M > 16) {
-    plan_umma(M, N, K, di, pl);
+    plan_umma(M, N, K, bits, di, pl);
     const size_t part = pl->splits > 1 ? (size_t)M * N * sizeof(float) : 0;
     pl->workspace_bytes = WS_HEADER_BYTES + ws_counter_bytes(N) + part;
     return ST_OK;
   }
   const int m_pass = M < 16 ? M : 16;
-  int st = plan_skinny(m_pass, N, K, bits, di, pl);
+  int st = plan_stream(m_pass, N, K, bits, di, pl);
   if (st != ST_OK) return st;
   pl->passes = (M + 15) / 16;
-  pl->workspace_bytes = WS_HEADER_BYTES + ws_counter_bytes(N) + (size_t)m_pass * N * sizeof(float);
+  // fp32 scratch [N][8 or 16]
+  pl->workspace_bytes = WS_HEADER_BYTES + ws_counter_bytes(N) + (size_t)16 * N * sizeof(float);
   return ST_OK;
 }
+
 
 static int run_umma(const void* a, int lda, const void* bq, const void* scales, void* c, int ldc, int M, int N, int K,
                     int var, int group, void* workspace, size_t ws_bytes, cudaStream_t stream,
@@ -261,8 +260,11 @@ static int run_umma(const void* a, int lda, const void* bq, const void* scales, 
   if (tm != 32 && tm != 64 && tm != 128 && tm != 256) return ST_INVALID_ARG;
   const int m_tiles = (M + tm - 1) / tm, n_tiles = (N + 127) / 128;
   const int kblocks = K / 64;
-  if (pl.splits < 1 || kblocks % pl.splits != 0) return ST_INVALID_ARG;
+  if (pl.splits < 1 || kblocks % (2 * pl.splits) != 0) return ST_INVALID_ARG;  // whole 128-row groups per split
   if (pl.splits > 1 && m_tiles * n_tiles > N / BLOCK_N) return ST_INVALID_ARG;  // counters region
+  if ((ldc & 1) || (((uintptr_t)scales) & 15)) return ST_INVALID_ARG;  // paired stores, bulk-copied scale rows
+  const int bits = var_bits(var);
+  const int a_stages = umma_a_stages(tm, bits, device_info().max_smem);
   const size_t need = WS_HEADER_BYTES + ws_counter_bytes(N) + (pl.splits > 1 ? (size_t)M * N * sizeof(float) : 0);
   if (!workspace || ws_bytes < need || ((uintptr_t)workspace & 255)) return ST_WORKSPACE;
   EncodeTiledFn enc = encode_tiled_fn();
@@ -287,10 +289,62 @@ static int run_umma(const void* a, int lda, const void* bq, const void* scales, 
   p.gshift = gshift_of(group, K);
   p.tm = tm; p.m_tiles = m_tiles; p.n_tiles = n_tiles;
   p.splits = pl.splits; p.kblocks_per_split = kblocks / pl.splits;
-  const int smem = umma_smem_bytes(tm);
+  p.a_stages = a_stages;
+  p.debug = pl.debug;
+  p.tl = nullptr;
+#ifdef B200Q_TIMELINE
+  p.tl = g_tl_buf;
+#endif
+  const int tiles = pl.splits * m_tiles * n_tiles;
+  p.grid = tiles < device_info().sm_count ? tiles : device_info().sm_count;
+  const int smem = umma_smem_bytes(tm, bits, a_stages);
   if (smem > device_info().max_smem) return ST_UNSUPPORTED;
   cudaError_t e = umma_launch(var, p, &tmap, smem, stream);
   if (e != cudaSuccess) { g_last_cuda_error = (int)e; return ST_CUDA; }
+  return ST_OK;
+}
+
+static int run_stream(const void* a, int lda, const void* bq, const void* scales, void* c, int ldc, int M, int N,
+                      int K, int var, int group, void* workspace, size_t ws_bytes, cudaStream_t stream,
+                      const b200q_plan_t& pl) {
+  const int bits = var_bits(var);
+  const int KB = K / BLOCK_K;
+  if (pl.splits < 1 || KB % pl.splits != 0 || pl.ctas_per_split < 1) return ST_INVALID_ARG;
+  if (pl.stages < 1 || pl.stages > 8) return ST_INVALID_ARG;
+  if (((uintptr_t)scales) & 15) return ST_INVALID_ARG;  // scale rows are fetched with 32-byte bulk copies
+  const size_t need = WS_HEADER_BYTES + ws_counter_bytes(N) + (size_t)16 * N * sizeof(float);
+  if (!workspace || ws_bytes < need || ((uintptr_t)workspace & 255)) return ST_WORKSPACE;
+  StreamParams p;
+  p.bq = bq;
+  p.scales = reinterpret_cast<const __half*>(scales);
+  p.status = reinterpret_cast<int*>(workspace);
+  p.counters = reinterpret_cast<int*>(reinterpret_cast<char*>(workspace) + WS_HEADER_BYTES);
+  p.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + WS_HEADER_BYTES + ws_counter_bytes(N));
+  p.N = N; p.K = K; p.lda = lda; p.ldc = ldc; p.KB = KB; p.NT = N / BLOCK_N;
+  p.gshift = gshift_of(group, K);
+  p.S = pl.splits; p.KBc = KB / pl.splits; p.CPC = pl.ctas_per_split;
+  if (p.S * p.CPC > 4 * device_info().sm_count) return ST_INVALID_ARG;
+  p.pitch = stream_pitch(p.KBc * 512);
+  p.stages = pl.stages;
+  p.debug_skip = pl.debug;
+  p.pdl = pl.pdl;
+  p.tl = nullptr;
+  p.tl_slot = -1;
+  for (int m0 = 0; m0 < M; m0 += 16) {
+    const int mc = (M - m0) < 16 ? (M - m0) : 16;
+    p.a = reinterpret_cast<const __half*>(a) + (size_t)m0 * lda;
+    p.c = reinterpret_cast<__half*>(c) + (size_t)m0 * ldc;
+    p.M = mc;
+    p.T_own = stream_tiles_owned(mc, p.NT, p.CPC);
+    const int smem = stream_smem(mc, p.KBc * 512, bits, pl.stages, p.T_own);
+    if (smem > device_info().max_smem) return ST_UNSUPPORTED;
+#ifdef B200Q_TIMELINE
+    p.tl = g_tl_buf;
+    p.tl_slot = (g_tl_buf && g_tl_next < g_tl_slots) ? g_tl_next++ : -1;
+#endif
+    cudaError_t e = stream_launch(var, p, (mc + 7) / 8, smem, stream);
+    if (e != cudaSuccess) { g_last_cuda_error = (int)e; return ST_CUDA; }
+  }
   return ST_OK;
 }
 
@@ -303,41 +357,9 @@ static int run_gemm(const void* a, int lda, const void* bq, const void* scales, 
   if (lda < K || ldc < N || (lda % 8) != 0) return ST_INVALID_ARG;
   if (pl.kernel == 1)
     return run_umma(a, lda, bq, scales, c, ldc, M, N, K, var, group, workspace, ws_bytes, stream, pl);
-  if (pl.kernel != 0) return ST_UNSUPPORTED;
-  if (pl.splits < 1 || (K / BLOCK_K) % pl.splits != 0 || pl.ctas_per_split < 1) return ST_INVALID_ARG;
-  const int bits = var_bits(var);
-  if (pl.stages < 1 || pl.stages > 8) return ST_INVALID_ARG;
-  if (pl.cluster < 1 || pl.cluster > 8 || pl.splits % pl.cluster != 0) return ST_INVALID_ARG;
-  if (pl.ctas_per_split > N / BLOCK_N) return ST_INVALID_ARG;
-  const int m_pass = M < 16 ? M : 16;
-  const size_t need = WS_HEADER_BYTES + ws_counter_bytes(N) + (size_t)m_pass * N * sizeof(float);
-  if (!workspace || ws_bytes < need || ((uintptr_t)workspace & 255)) return ST_WORKSPACE;
-
-  SkinnyParams p;
-  p.bq = reinterpret_cast<const uint4*>(bq);
-  p.scales = reinterpret_cast<const __half*>(scales);
-  p.counters = reinterpret_cast<int*>(reinterpret_cast<char*>(workspace) + WS_HEADER_BYTES);
-  p.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + WS_HEADER_BYTES + ws_counter_bytes(N));
-  p.N = N; p.K = K; p.group = group; p.gshift = gshift_of(group, K); p.lda = lda; p.ldc = ldc;
-  p.KB = K / BLOCK_K; p.NT = N / BLOCK_N;
-  p.CS = pl.cluster; p.GS = pl.splits / pl.cluster; p.P = pl.ctas_per_split; p.KBc = p.KB / pl.splits;
-  p.tiles_max = (p.NT + p.P - 1) / p.P;
-  p.pitch = skinny_pitch(p.KBc * 512);
-  p.stages = pl.stages;
-  p.status = reinterpret_cast<int*>(workspace);
-  p.debug_skip = pl.debug;
-  p.pdl = pl.pdl;
-  for (int m0 = 0; m0 < M; m0 += 16) {
-    const int mc = (M - m0) < 16 ? (M - m0) : 16;
-    p.a = reinterpret_cast<const __half*>(a) + (size_t)m0 * lda;
-    p.c = reinterpret_cast<__half*>(c) + (size_t)m0 * ldc;
-    p.M = mc;
-    const int smem = skinny_smem(mc, p.KBc * 512, bits, pl.stages, p.tiles_max);
-    if (smem > device_info().max_smem) return ST_UNSUPPORTED;
-    cudaError_t e = skinny_launch(var, p, (mc + 7) / 8, smem, stream);
-    if (e != cudaSuccess) { g_last_cuda_error = (int)e; return ST_CUDA; }
-  }
-  return ST_OK;
+  if (pl.kernel == 2)
+    return run_stream(a, lda, bq, scales, c, ldc, M, N, K, var, group, workspace, ws_bytes, stream, pl);
+  return ST_UNSUPPORTED;
 }
 
 }  // namespace b200q

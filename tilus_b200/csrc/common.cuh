@@ -32,26 +32,31 @@ constexpr int BLOCK_K = 512;
 constexpr size_t WS_HEADER_BYTES = 256;
 inline size_t ws_counter_bytes(int N) { return (((size_t)(N / BLOCK_N) * 4) + 255) / 256 * 256; }
 
-// ---- skinny (M <= 16 per launch) split-K kernel ---------------------------------------------
-struct SkinnyParams {
+// ---- stream kernel (M <= 16 per launch): one CTA per SM, item-balanced, ring-fed ---------------
+constexpr int STREAM_WARPS = 16;
+constexpr int STREAM_SC_GROUPS = 16;  // groups per warp in the shared-memory scale cache (32 bytes each)
+// 128-row groups per ring item: items of 1..2 KB for every bit width
+constexpr int stream_gi(int bits) { return bits <= 2 ? 4 : bits <= 5 ? 2 : 1; }
+struct StreamParams {
   const __half* a;       // [M, K] row-major, leading dimension lda
-  const uint4* bq;       // b200 layout
-  const __half* scales;  // [K/group, N]
+  const void* bq;        // b200 layout
+  const __half* scales;  // [K/group, N], 16-byte aligned
   __half* c;             // [M, N], leading dimension ldc
-  float* partial;        // [M, N] fp32, zero on entry, zero on exit
-  int* counters;         // [N/16], zero on entry, zero on exit
-  int M, N, K, group;
-  int gshift;            // log2(group / 128), or -1 when there is one group per column (group == K)
+  float* partial;        // [N][8*MT] fp32, zero on entry, zero on exit
+  int* counters;         // [N/16] arrived items per column tile, zero on entry, zero on exit
+  int* status;           // workspace status header
+  int M, N, K;
   int lda, ldc;
   int KB, NT;            // K/512, N/16
-  int GS, CS, P, KBc;    // global k splits, cluster size (k splits inside a cluster), column ranges,
-                         // k-blocks per CTA (K/512 / (GS*CS))
-  int tiles_max;         // most column tiles any cluster owns: ceil(NT / P)
+  int gshift;            // log2(group / 128), or -1 when there is one group per column (group == K)
+  int S, KBc, CPC;       // k chunks, k blocks per chunk, CTAs per chunk; grid = S * CPC
+  int T_own;             // whole column tiles per CTA (<= NT / CPC); the rest is shared item-wise
   int pitch;             // shared-memory row pitch of the activation chunk, in halfs
-  int stages;            // items in flight per warp (<= 8)
-  int* status;           // workspace status header
+  int stages;            // ring slots per warp (<= 8)
   int debug_skip;        // diagnosis: 1 stream the weights but skip the math, 2 skip the loop, 3 and the staging
   int pdl;               // launch with programmatic stream serialization
+  unsigned long long* tl;  // timeline experiments (side builds with B200Q_TIMELINE only), else null
+  int tl_slot;
 };
 
 // ---- tcgen05 kernel (any M; used for M > 16) ---------------------------------------------------
@@ -68,7 +73,11 @@ struct UmmaParams {
   int tm;                // activation rows per CTA tile = N extent of the MMA (32, 64, 128 or 256)
   int m_tiles, n_tiles;  // ceil(M / tm), ceil(N / 128)
   int splits;            // split-K factor
-  int kblocks_per_split; // 64-row k blocks per CTA
+  int kblocks_per_split; // 64-row k blocks per tile (even)
+  int a_stages;          // activation stages in shared memory
+  int grid;              // persistent CTAs: min(tiles, SMs)
+  int debug;             // timing experiments: 1 no decode, 2 no activation copies, 4 no stores, 8 no tcgen05.st
+  unsigned long long* tl;  // wait accounting (side builds with B200Q_TIMELINE only), else null
 };
 
 // ---- dequantize kernel -----------------------------------------------------------------------
@@ -93,7 +102,7 @@ __device__ __forceinline__ uint32_t u4_comp(const uint4& v, int c) {
 
 __device__ __forceinline__ void mma_m16n8k16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                              uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
@@ -102,10 +111,64 @@ __device__ __forceinline__ void mma_m16n8k16(float (&d)[4], uint32_t a0, uint32_
 // same, first step of a chain: the accumulator input is zero
 __device__ __forceinline__ void mma_m16n8k16_init(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                   uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
       : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+}
+
+__device__ __forceinline__ void red_add_v2(float* addr, float x, float y) {
+  asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(addr), "f"(x), "f"(y) : "memory");
+}
+
+// ---- shared-memory and mbarrier helpers of the mma.sync kernels ----------------------------------
+// Waits on an mbarrier phase for at most about a quarter of a second; false when that ran out.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+  uint64_t t0 = 0;
+  for (int it = 0;; ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, 0x100000;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    uint64_t now;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+    if (it == 0) t0 = now;
+    else if (now - t0 > 250000000ull) return false;
+  }
+}
+
+__device__ __forceinline__ uint4 lds_u4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ float2 lds_f2(uint32_t addr) {
+  float2 v;
+  asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
+  return v;
+}
+// the B words of one unit, from a shared-memory byte address
+template <int B>
+__device__ __forceinline__ void lds_unit_words(uint32_t addr, uint32_t (&w)[B]) {
+  if constexpr (B % 4 == 0) {
+#pragma unroll
+    for (int q = 0; q < B / 4; ++q) {
+      const uint4 v = lds_u4(addr + q * 16);
+      w[4 * q] = v.x; w[4 * q + 1] = v.y; w[4 * q + 2] = v.z; w[4 * q + 3] = v.w;
+    }
+  } else if constexpr (B % 2 == 0) {
+#pragma unroll
+    for (int q = 0; q < B / 2; ++q)
+      asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(w[2 * q]), "=r"(w[2 * q + 1]) : "r"(addr + q * 8));
+  } else {
+#pragma unroll
+    for (int q = 0; q < B; ++q) asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w[q]) : "r"(addr + q * 4));
+  }
 }
 
 }  // namespace b200q

@@ -1,0 +1,577 @@
+// Decode path: C[M<=16, N] = A[M, K] x dequant(Bq[K, N]) - the memory-bound GEMV / skinny GEMM.
+//
+// Data movement.  The (column tile, k block) items of the weight matrix - GI consecutive
+// 128-row groups of a 16-column x 512-row block, 1..2 KB contiguous - are cut into equal
+// contiguous runs, one per warp, and every CTA gets the same number of items whatever the
+// shape.  Lane 0 of a warp keeps the warp's own shared-memory ring full with TMA bulk copies
+// (cp.async.bulk, completion on an mbarrier per slot).  Weights and scales are constants, so
+// the ring is filled and the warp's scales are cached in shared memory before the kernel
+// waits for its predecessor in the stream (programmatic dependent launch): the memory
+// system always has the next layer's requests queued behind the current layer's.  A CTA
+// takes at most half of an SM (16 warps at <= 64 registers, <= 113 KB of shared memory): two
+// CTAs of one launch share an SM, or - when a launch has one CTA per SM - the next launch
+// of the stream becomes resident beside it and prefetches while it computes.  K is cut into S
+// chunks when the activation chunk [M, K/S] would not fit next to the rings; a CTA works
+// inside one chunk.
+//
+// Compute.  One 128-row group at a time.  A lane reads its two units (columns r and r+8, 32
+// rows each) with one vector load per unit, turns them into tensor-core operands with the
+// unit decoder's "linear" patterns (decode.cuh, pair_lin: one mask per pair of codes, no
+// floating-point work per weight) and issues mma.sync.m16n8k16 with the weight tile as the
+// 16-row operand and the (up to 8-row) activation slice as the 8-column operand.  An integer
+// code q lands in the mantissa of an fp16 subnormal (value q * 2^(T-24)), a float code in
+// its own exponent / mantissa bits; the tensor core multiplies these exactly by activations
+// that were pre-multiplied by 2^-T when the CTA staged them into shared memory.  The
+// accumulator of a group starts from the zero-point term -zero_point * sum_k(a_k) / F (group
+// sums computed during staging, stored in accumulator-fragment order), and once per group
+// and column it is scaled:   C += (s * F) * acc_group,   F = 2^24 (integers) or 2^(15 - bias).
+// Products are exact, sums fp32; the weights are never rounded to fp16 here, so the result
+// is at least as close to the real-valued product as the reference's cast-scale-dot; the
+// bit-exact weight values are what the dequantize kernel returns.  The k index of the mma is
+// a private permutation (a dot product does not care about the order of its terms): lane
+// (r, j) owns rows j*32 .. j*32+31 of the group, so its weights are one contiguous unit per
+// column and its activations contiguous 16-byte pieces.
+//
+// Output.  Every CTA owns T_own whole column tiles, whose partial 16 x M sums its warps add
+// into a tile buffer in shared memory (red.shared) and which the CTA writes to C at the end
+// without any traffic to other CTAs.  The tiles that do not divide among the CTAs are cut
+// into equal item runs, one per CTA, which are worked through first: such a partial tile is
+// added into an fp32 scratch array [N][8*MT] with vector red.global, then the warp adds its
+// item count to the tile's arrival counter; whoever completes the count converts the sums
+// to fp16, writes C and puts scratch and counter back to zero - long before the CTA's own
+// tiles are done, so these round trips stay off the tail.  When K is cut in chunks the own
+// tiles meet in the same scratch at the end of the kernel.  Nobody waits for anybody: the only
+// waits are on the mbarriers of the warp's own bulk copies (bounded).
+//
+// Reference: QuantizedMatmul.__call__, examples/quantization/matmul_a16wx.py:231-405 (cast,
+// scale multiply, fp32 dot, fp16 store; its serial fp16 split-K, :375-398, is replaced by the
+// fp32 reduction).
+#include "common.cuh"
+
+#ifndef B200Q_PART
+#define B200Q_PART 0
+#endif
+#ifndef B200Q_NPARTS
+#define B200Q_NPARTS 1
+#endif
+
+namespace b200q {
+
+#ifndef B200Q_DIAG_MODE
+#define B200Q_DIAG_MODE 0  // side builds: 4 no tensor-core work, 5 no decode, 6 normal numbers for subnormals
+#endif
+
+#ifdef B200Q_TIMELINE
+// Side builds only: per-launch, per-CTA %globaltimer stamps for timeline experiments.
+#define TL_STAMP(k)                                                                   \
+  do {                                                                                \
+    if (tl_base && lane == 0 && warp == 0) {                                          \
+      unsigned long long t_;                                                          \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                          \
+      tl_base[k] = t_;                                                                \
+    }                                                                                 \
+  } while (0)
+#else
+#define TL_STAMP(k) do { } while (0)
+#endif
+
+// the B words of one unit, from shared memory (plain loads: the compiler may predicate and schedule them)
+template <int B>
+__device__ __forceinline__ void ld_unit_words(const unsigned char* ptr, uint32_t (&w)[B]) {
+  if constexpr (B % 4 == 0) {
+#pragma unroll
+    for (int q = 0; q < B / 4; ++q) {
+      const uint4 v = reinterpret_cast<const uint4*>(ptr)[q];
+      w[4 * q] = v.x; w[4 * q + 1] = v.y; w[4 * q + 2] = v.z; w[4 * q + 3] = v.w;
+    }
+  } else if constexpr (B % 2 == 0) {
+#pragma unroll
+    for (int q = 0; q < B / 2; ++q) {
+      const uint2 v = reinterpret_cast<const uint2*>(ptr)[q];
+      w[2 * q] = v.x; w[2 * q + 1] = v.y;
+    }
+  } else {
+#pragma unroll
+    for (int q = 0; q < B; ++q) w[q] = reinterpret_cast<const uint32_t*>(ptr)[q];
+  }
+}
+// one non-blocking look at an mbarrier phase
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Shared-memory layout (byte offsets from the dynamic smem base):
+//   [0, 1024)    mbarriers [warp][stage]   (16 warps x up to 8 stages)
+//   [1024, ...)  rings [warp][stage][ITEM_BYTES] of packed weights
+//   then         scale caches [warp][STREAM_SC_GROUPS][16] halfs: the scales of the warp's next groups
+//   then         tile sums of the CTA's own column tiles [T_own][16 columns][8*MT rows] floats
+//   then         activation chunk [M][pitch] halfs, then group sums [groups][8*MT] floats
+template <int VAR, int MT>
+__global__ void __launch_bounds__(STREAM_WARPS * 32, 2) stream_kernel(const StreamParams p) {
+  constexpr int B = var_bits(VAR);
+  constexpr int MP = 8 * MT;
+  constexpr int BIAS = var_bias(VAR);
+  constexpr int GI = stream_gi(B);
+  constexpr int NI = 4 / GI;  // items per block
+  constexpr int ITEM_BYTES = GI * 256 * B;
+  constexpr int SLOT_BYTES = ITEM_BYTES;
+  constexpr int NWARPS = STREAM_WARPS;
+  constexpr int SCG = STREAM_SC_GROUPS;
+  constexpr float F = (float)(1u << lin_factor_log2(VAR));
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  const int NST = p.stages;
+  const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem_raw);
+  unsigned char* sScale = smem_raw + 1024 + (size_t)NWARPS * NST * SLOT_BYTES;
+  float* sAcc = reinterpret_cast<float*>(sScale + (size_t)NWARPS * SCG * 32);
+  __half* sA = reinterpret_cast<__half*>(sAcc + (size_t)p.T_own * 16 * MP);
+  // 64 zero bytes after the activation chunk: what the lanes of rows that do not exist read
+  // -zero_point * sum of the activations of each 128-row group, divided by F, laid out as the
+  // accumulator fragment of the first MMA of a group: [group][MT][j = 0..3] x {row 2j, row 2j+1, row 2j, row 2j+1}
+  float* sNb = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(sA) + (size_t)p.M * p.pitch * 2 + 64);
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int r = lane >> 2, j = lane & 3;
+  const int chunk = blockIdx.x % p.S, ci = blockIdx.x / p.S;
+  const int kb_base = chunk * p.KBc;
+  const int IPT = p.KBc * NI;  // items per column tile inside a k chunk
+  // The CTA owns T_own whole column tiles; the NT - CPC * T_own tiles left over are cut into
+  // equal item runs, one per CTA.  A CTA works through its left-over run first.
+  const int own_tile0 = ci * p.T_own;
+  const int left_tile0 = p.CPC * p.T_own;
+  const long long left_items = (long long)(p.NT - left_tile0) * IPT;
+  const int l0 = (int)(left_items * ci / p.CPC), l1 = (int)(left_items * (ci + 1) / p.CPC);
+  const int n_left = l1 - l0, n_total = n_left + p.T_own * IPT;
+  const int v0 = (int)((long long)n_total * warp / NWARPS), v1 = (int)((long long)n_total * (warp + 1) / NWARPS);
+  // this warp's two item runs: cA items of left-over tiles, then cB items of the CTA's own tiles
+  const int cA = v0 < n_left ? min(v1, n_left) - v0 : 0;
+  const int tileA = left_tile0 + (l0 + v0) / IPT, qA = (l0 + v0) % IPT;
+  const int oB = max(v0, n_left) - n_left;
+  const int cB = max(v1 - max(v0, n_left), 0);
+  const int tileB = own_tile0 + oB / IPT, qB = oB % IPT;
+  const int n_items = cA + cB;
+
+#ifdef B200Q_TIMELINE
+  unsigned long long* tl_base = nullptr;
+  if (p.tl && p.tl_slot >= 0) tl_base = p.tl + ((size_t)p.tl_slot * gridDim.x + blockIdx.x) * 32;
+#endif
+  TL_STAMP(0);
+  // the next kernel of the stream may become resident as soon as there is room for it
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+  const uint32_t bar0 = smem_base + warp * 64;
+  const uint32_t ring_s = smem_base + 1024 + warp * NST * SLOT_BYTES;
+  const uint32_t ring_end = ring_s + NST * SLOT_BYTES;
+
+  // ---- producer: lane 0 requests the items of the warp, in order, into the warp's ring ----
+  int pc_q, issued = 0;
+  const unsigned char* pc_src;
+  const size_t tile_skip = (size_t)(p.KB - p.KBc) * (1024 * B);  // from the end of a chunk to the next tile's
+  auto cursor_set = [&](int tile, int q) {
+    pc_q = q;
+    pc_src = reinterpret_cast<const unsigned char*>(p.bq) + ((size_t)tile * p.KB + kb_base) * (size_t)(1024 * B) +
+             (size_t)q * ITEM_BYTES;
+  };
+  if (cA > 0) cursor_set(tileA, qA); else cursor_set(tileB, qB);
+  auto issue_next = [&](uint32_t bar, uint32_t dst) {  // lane 0
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(ITEM_BYTES) : "memory");
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+        "l"(pc_src), "r"(ITEM_BYTES), "r"(bar)
+        : "memory");
+    if (++issued == cA) {
+      cursor_set(tileB, qB);
+    } else {
+      pc_src += ITEM_BYTES;
+      if (++pc_q == IPT) { pc_q = 0; pc_src += tile_skip; }
+    }
+  };
+  // ---- scale cache: entry i % SCG holds the 16 scales of the warp's i-th group; a lane fetches
+  // half a row (16 bytes) of one of 16 consecutive groups.  Scales are constants: the first
+  // fill runs ahead of the wait on the previous kernel. ----
+  unsigned char* sc_warp = sScale + (size_t)warp * SCG * 32;
+  auto fill_scales = [&](int first) {
+    const int gidx = first + (lane >> 1);
+    if (gidx < n_items * GI) {
+      const int itx = gidx / GI, gi = gidx - itx * GI;
+      int tile, q;
+      if (itx < cA) {
+        const int gg = l0 + v0 + itx;
+        tile = left_tile0 + gg / IPT; q = gg % IPT;
+      } else {
+        const int o = oB + itx - cA;
+        tile = own_tile0 + o / IPT; q = o % IPT;
+      }
+      const int row = p.gshift >= 0 ? ((kb_base * 4 + q * GI + gi) >> p.gshift) : 0;
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(p.scales + (size_t)row * p.N + tile * 16) + (lane & 1));
+      *reinterpret_cast<uint4*>(sc_warp + (gidx % SCG) * 32 + (lane & 1) * 16) = v;
+    }
+  };
+  if (lane == 0) {
+    for (int s = 0; s < NST; ++s) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar0 + s * 8) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncwarp();
+  if (lane == 0 && p.debug_skip < 2)
+    for (int s = 0; s < NST && issued < n_items; ++s) issue_next(bar0 + s * 8, ring_s + s * SLOT_BYTES);
+  if (p.debug_skip < 2) fill_scales(0);
+  __syncwarp();
+  for (int idx = tid; idx < p.T_own * 16 * MP; idx += NWARPS * 32) sAcc[idx] = 0.f;
+
+  TL_STAMP(1);
+  // everything below may read what the previous kernel of the stream wrote
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  TL_STAMP(2);
+
+  // ---- stage the activation chunk A[0:M, kb_base*512 : +KBc*512], pre-scaled ----
+  if (p.debug_skip < 3) {
+    const int kc = p.KBc * 512;
+    const int vec_per_row = kc / 8;  // multiple of 64
+    const int total = p.M * vec_per_row;
+    if constexpr (BIAS != 0) {  // rows that do not exist contribute exact zeros
+      for (int idx = tid; idx < p.KBc * 4 * MP * 2; idx += NWARPS * 32) {
+        const int m = ((idx >> 4) % MT) * 8 + ((idx >> 2) & 3) * 2 + (idx & 1);
+        if (m >= p.M) sNb[idx] = 0.f;
+      }
+    }
+    if (tid < 16) reinterpret_cast<uint32_t*>(reinterpret_cast<unsigned char*>(sA) + (size_t)p.M * p.pitch * 2)[tid] = 0u;
+    // a thread always lands on the same 8-column slot of a 32-column unit: pairs h0 .. h0+3
+    const int h0 = (tid & 3) * 4;
+    __half2 mult[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int e = lin_prescale_shift(VAR, h0 + q);
+      mult[q] = h2_from_bits(dup16((uint32_t)(15 - e) << 10));  // 2^-e
+    }
+    int m = 0, vv = tid;  // idx = m * vec_per_row + vv
+    for (int idx = tid; idx < total; idx += NWARPS * 32) {
+      while (vv >= vec_per_row) { vv -= vec_per_row; ++m; }
+      const int kk = vv * 8;
+      vv += NWARPS * 32;
+      uint4 v = __ldg(reinterpret_cast<const uint4*>(p.a + (size_t)m * p.lda + (size_t)kb_base * 512 + kk));
+      __half2 x0 = h2_from_bits(v.x), x1 = h2_from_bits(v.y), x2 = h2_from_bits(v.z), x3 = h2_from_bits(v.w);
+      if constexpr (BIAS != 0) {
+        const float2 f0 = __half22float2(x0), f1 = __half22float2(x1), f2 = __half22float2(x2),
+                     f3 = __half22float2(x3);
+        float sum = ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y));
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 8);
+        if ((lane & 15) == 0) {
+          const float v = -(float)BIAS * sum * (1.0f / F);
+          float* q4 = sNb + (((kk >> 7) * MT + (m >> 3)) * 4 + ((m & 7) >> 1)) * 4 + (m & 1);
+          q4[0] = v;
+          q4[2] = v;
+        }
+      }
+      if constexpr (!var_is_float(VAR)) {
+        x0 = __hmul2(x0, mult[0]); x1 = __hmul2(x1, mult[1]);
+        x2 = __hmul2(x2, mult[2]); x3 = __hmul2(x3, mult[3]);
+      }
+      v.x = bits_from_h2(x0); v.y = bits_from_h2(x1); v.z = bits_from_h2(x2); v.w = bits_from_h2(x3);
+      *reinterpret_cast<uint4*>(sA + (size_t)m * p.pitch + kk + (kk >> 5) * 8) = v;
+    }
+  }
+  __syncthreads();  // activations staged, tile sums cleared
+  TL_STAMP(3);
+
+  const int items_per_tile_total = p.KB * NI;
+  bool ok = true;
+  if (n_items > 0 && p.debug_skip < 2) {
+    float acc[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) acc[mt][q] = 0.f;
+
+    // Activation fragments: lane (r, j) reads row mt*8 + r, columns j*32 .. of each group (32
+    // columns + 8 of padding per unit, 4 units per group).  Lanes whose row does not exist
+    // read the 64 zero bytes behind the chunk instead (kmask clears their group offset).
+    const unsigned char* a_ptr[MT];
+    uint32_t kmask[MT];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+      const int m = mt * 8 + r;
+      const bool valid = m < p.M;
+      a_ptr[mt] = reinterpret_cast<const unsigned char*>(sA) +
+                  (valid ? 2u * (uint32_t)(m * p.pitch + j * 40) : 2u * (uint32_t)(p.M * p.pitch));
+      kmask[mt] = valid ? 0xffffffffu : 0u;
+    }
+    const float4* nb4 = reinterpret_cast<const float4*>(sNb) + j;
+    const unsigned char* ring_g = smem_raw + (ring_s - smem_base);  // this warp's ring, generic pointer
+    const uint32_t w_lane = (uint32_t)(lane * B * 4);
+
+    int seg = cA > 0 ? 0 : 1;          // 0: left-over tiles (shared with other CTAs), 1: own tiles
+    int seg_left = cA > 0 ? cA : cB;
+    int cur_tile = cA > 0 ? tileA : tileB;
+    int q = cA > 0 ? qA : qB;  // item index inside the tile chunk: k block q / NI, groups (q % NI) * GI ...
+    uint32_t slot_off = 0, bar = bar0;
+    uint32_t parity = 0;
+    int it = 0;
+    while (it < n_items && ok) {
+      const int run = min(IPT - q, seg_left);  // items of this column tile
+      for (int e = 0; e < run; ++e, ++it, ++q) {
+        const int g0 = q * GI;  // first 128-row group of the item, counted inside the chunk
+#ifdef B200Q_TIMELINE
+        if (it < 6) TL_STAMP(8 + 4 * it);
+#endif
+        if (!__all_sync(0xffffffffu, mbar_test(bar, parity) ? 1 : 0)) {  // not there yet: bounded wait
+          if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar, parity) ? 1 : 0)) { ok = false; break; }
+        }
+#ifdef B200Q_TIMELINE
+        if (it == 0) TL_STAMP(4);
+        if (it == n_items - 1) TL_STAMP(5);
+        if (it < 6) TL_STAMP(9 + 4 * it);
+#endif
+        const unsigned char* slot = ring_g + slot_off;
+        if (it != 0 && (it * GI) % SCG == 0) {  // the cache has been used up: next SCG groups
+          __syncwarp();
+          fill_scales(it * GI);
+          __syncwarp();
+        }
+        // this item's scales: columns r and r+8 of each group
+        float sf0[GI], sf1[GI];
+#pragma unroll
+        for (int gi = 0; gi < GI; ++gi) {
+          const __half* sp = reinterpret_cast<const __half*>(sc_warp + ((it * GI + gi) % SCG) * 32) + r;
+          sf0[gi] = __half2float(sp[0]);
+          sf1[gi] = __half2float(sp[8]);
+        }
+#pragma unroll
+        for (int gi = 0; gi < GI; ++gi) {
+          uint32_t w0[B], w1[B];
+          ld_unit_words<B>(slot + w_lane + gi * (256 * B), w0);
+          ld_unit_words<B>(slot + w_lane + gi * (256 * B) + 128 * B, w1);
+          uint32_t W0[16], W1[16];
+          if (B200Q_DIAG_MODE == 5) {  // diagnosis: no decode
+#pragma unroll
+            for (int h = 0; h < 16; ++h) { W0[h] = w0[h % B] & 0x03ff03ffu; W1[h] = w1[h % B] & 0x03ff03ffu; }
+          } else {
+            unit_decode_linear<VAR>(w0, W0);
+            unit_decode_linear<VAR>(w1, W1);
+          }
+          if (gi == GI - 1) {
+            // every lane has turned its copy of the last group into operands: refill the slot
+            __syncwarp();
+#ifdef B200Q_TIMELINE
+            if (it < 6) TL_STAMP(10 + 4 * it);
+#endif
+            if (lane == 0 && issued < n_items) {
+              asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+              issue_next(bar, ring_s + slot_off);
+            }
+#ifdef B200Q_TIMELINE
+            if (it < 6) TL_STAMP(11 + 4 * it);
+#endif
+          }
+          const uint32_t koff = (uint32_t)((g0 + gi) * 320);  // bytes: 128 columns + 4 x 8 of padding per group
+          // two accumulation chains per 8-row tile; the first starts from the zero-point term of the group
+          float d[MT][2][4];
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            float4 nb = make_float4(0.f, 0.f, 0.f, 0.f);
+            if constexpr (BIAS != 0) nb = nb4[((g0 + gi) * MT + mt) * 4];
+            d[mt][0][0] = nb.x; d[mt][0][1] = nb.y; d[mt][0][2] = nb.z; d[mt][0][3] = nb.w;
+          }
+          if (B200Q_DIAG_MODE != 4) {
+#pragma unroll
+            for (int sp = 0; sp < 4; ++sp) {
+#pragma unroll
+              for (int mt = 0; mt < MT; ++mt) {
+                const uint4 av = *reinterpret_cast<const uint4*>(a_ptr[mt] + (koff & kmask[mt]) + sp * 16);
+                mma_m16n8k16(d[mt][0], W0[4 * sp], W1[4 * sp], W0[4 * sp + 1], W1[4 * sp + 1], av.x, av.y);
+                if (sp == 0)
+                  mma_m16n8k16_init(d[mt][1], W0[2], W1[2], W0[3], W1[3], av.z, av.w);
+                else
+                  mma_m16n8k16(d[mt][1], W0[4 * sp + 2], W1[4 * sp + 2], W0[4 * sp + 3], W1[4 * sp + 3], av.z, av.w);
+              }
+            }
+          } else {  // diagnosis: no tensor-core work
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+              for (int e2 = 0; e2 < 4; ++e2) {
+                d[mt][0][e2] += __uint_as_float((W0[e2] ^ W1[e2 + 4]) & 0x007fffffu);
+                d[mt][1][e2] = __uint_as_float((W0[e2 + 8] ^ W1[e2 + 12]) & 0x007fffffu);
+              }
+          }
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            acc[mt][0] = fmaf(sf0[gi], d[mt][0][0] + d[mt][1][0], acc[mt][0]);
+            acc[mt][1] = fmaf(sf0[gi], d[mt][0][1] + d[mt][1][1], acc[mt][1]);
+            acc[mt][2] = fmaf(sf1[gi], d[mt][0][2] + d[mt][1][2], acc[mt][2]);
+            acc[mt][3] = fmaf(sf1[gi], d[mt][0][3] + d[mt][1][3], acc[mt][3]);
+          }
+        }
+        slot_off += SLOT_BYTES; bar += 8;
+        if (slot_off == (uint32_t)NST * SLOT_BYTES) { slot_off = 0; bar = bar0; parity ^= 1u; }
+      }
+      if (!ok) break;
+      // ---- this warp's share of column tile cur_tile is complete: hand it over ----
+      // lane (r, j) holds rows 2j, 2j+1 (of each 8-row tile) of columns r and r+8
+      if (seg == 1) {
+        // one of the CTA's own tiles: add into its tile sums in shared memory
+        float* dst = sAcc + (size_t)(cur_tile - own_tile0) * 16 * MP;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+          for (int qq = 0; qq < 4; ++qq) {
+            const int m = mt * 8 + 2 * j + (qq & 1);
+            if (m < p.M) atomicAdd(dst + (r + (qq >> 1) * 8) * MP + m, acc[mt][qq] * F);
+            acc[mt][qq] = 0.f;
+          }
+      } else {
+        // a tile shared with other CTAs: add into the global scratch, count the items in
+        float* dst = p.partial + (size_t)cur_tile * 16 * MP;  // [column][MP]
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          const int m0 = mt * 8 + 2 * j;
+          if (m0 < p.M) {
+            red_add_v2(dst + r * MP + m0, acc[mt][0] * F, acc[mt][1] * F);
+            red_add_v2(dst + (r + 8) * MP + m0, acc[mt][2] * F, acc[mt][3] * F);
+          }
+#pragma unroll
+          for (int qq = 0; qq < 4; ++qq) acc[mt][qq] = 0.f;
+        }
+        __syncwarp();
+        int last = 0;
+        if (lane == 0) {
+          __threadfence();  // cumulative over the warp's additions (ordered by the barrier above)
+          const int old = atomicAdd(p.counters + cur_tile, run);
+          last = (old + run == items_per_tile_total) ? 1 : 0;
+        }
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (last) {  // every share has arrived: convert, write C, put the scratch back to zero
+          __threadfence();
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            const int m0 = mt * 8 + 2 * j;
+            if (m0 < p.M) {
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                float2* src = reinterpret_cast<float2*>(dst + (r + h * 8) * MP + m0);
+                const float2 v = __ldcg(src);
+                __stcg(src, make_float2(0.f, 0.f));
+                const int n = cur_tile * 16 + r + h * 8;
+                p.c[(size_t)m0 * p.ldc + n] = __float2half_rn(v.x);
+                if (m0 + 1 < p.M) p.c[(size_t)(m0 + 1) * p.ldc + n] = __float2half_rn(v.y);
+              }
+            }
+          }
+          if (lane == 0) p.counters[cur_tile] = 0;
+        }
+      }
+      seg_left -= run;
+      if (seg == 0 && seg_left == 0) {
+        seg = 1; seg_left = cB; cur_tile = tileB; q = qB;
+      } else {
+        q = 0;
+        ++cur_tile;
+      }
+    }
+  }
+  TL_STAMP(6);
+  if (!ok) {
+    // a bulk copy never completed: report it and give the copies still in flight a bounded
+    // chance to land (the CTA must not retire under them)
+    if (lane == 0) {
+      atomicExch(p.status, ST_DEVICE_TIMEOUT);
+      p.status[1] = 3;  // where: stream kernel weight ring
+      p.status[2] = blockIdx.x;
+      p.status[3] = warp;
+    }
+    for (int s = 0; s < NST; ++s) mbar_wait_bounded(bar0 + s * 8, 0);
+  }
+
+  // ---- the CTA's own tiles ----
+  if (p.T_own == 0) return;
+  __syncthreads();
+  const int n0 = own_tile0 * 16, ncols = p.T_own * 16;
+  if (p.S == 1) {  // all of K was here: write C
+    for (int m = 0; m < p.M; ++m)
+      for (int n = tid; n < ncols; n += NWARPS * 32) p.c[(size_t)m * p.ldc + n0 + n] = __float2half_rn(sAcc[n * MP + m]);
+    return;
+  }
+  // other k chunks hold the rest: meet in the global scratch; the last chunk to arrive converts
+  for (int idx = tid; idx < ncols * MP; idx += NWARPS * 32)
+    if ((idx % MP) < p.M) atomicAdd(p.partial + (size_t)n0 * MP + idx, sAcc[idx]);
+  __syncthreads();
+  int* s_last = reinterpret_cast<int*>(sAcc);  // the tile sums are no longer needed
+  if (tid == 0) __threadfence();  // cumulative over the CTA's additions (ordered by the barrier above)
+  __syncthreads();
+  for (int t = tid; t < p.T_own; t += NWARPS * 32) {
+    const int old = atomicAdd(p.counters + own_tile0 + t, IPT);
+    s_last[t] = (old + IPT == items_per_tile_total) ? 1 : 0;
+  }
+  __syncthreads();
+  for (int idx = tid; idx < ncols * MP; idx += NWARPS * 32) {
+    const int t = idx / (16 * MP);
+    if (!s_last[t]) continue;
+    __threadfence();
+    const int m = idx % MP, n = n0 + idx / MP;
+    if (m < p.M) {
+      float* src = p.partial + (size_t)n0 * MP + idx;
+      p.c[(size_t)m * p.ldc + n] = __float2half_rn(__ldcg(src));
+      __stcg(src, 0.f);
+    }
+    if ((idx % (16 * MP)) == 0) p.counters[own_tile0 + t] = 0;
+  }
+}
+
+template <int VAR, int MT>
+static cudaError_t launch_one(const StreamParams& p, int smem_bytes, cudaStream_t stream) {
+  auto kern = stream_kernel<VAR, MT>;
+  static int configured_smem[16] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (smem_bytes > 48 * 1024 && (dev < 0 || dev >= 16 || configured_smem[dev] < smem_bytes)) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < 16) configured_smem[dev] = smem_bytes;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(p.S * p.CPC), 1, 1);
+  cfg.blockDim = dim3(STREAM_WARPS * 32, 1, 1);
+  cfg.dynamicSmemBytes = (size_t)smem_bytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  // programmatic dependent launch: this kernel may become resident while the previous kernel
+  // of the stream still runs; it waits (griddepcontrol.wait) before it reads anything but
+  // the weights and scales
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = p.pdl ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, p);
+}
+
+template <int VAR>
+static cudaError_t launch_var(int var, const StreamParams& p, int mt, int smem_bytes, cudaStream_t stream) {
+  if constexpr (VAR % B200Q_NPARTS == B200Q_PART) {
+    if (var == VAR) {
+      return mt == 1 ? launch_one<VAR, 1>(p, smem_bytes, stream) : launch_one<VAR, 2>(p, smem_bytes, stream);
+    }
+  }
+  if constexpr (VAR + 1 < VAR_COUNT) return launch_var<VAR + 1>(var, p, mt, smem_bytes, stream);
+  else return cudaErrorInvalidValue;
+}
+
+#define B200Q_CAT2(a, b) a##b
+#define B200Q_CAT(a, b) B200Q_CAT2(a, b)
+
+// One of these per compiled part; api.cu picks the part as var % B200Q_NPARTS.
+cudaError_t B200Q_CAT(stream_launch_part, B200Q_PART)(int var, const StreamParams& p, int mt, int smem_bytes,
+                                                       cudaStream_t stream) {
+  return launch_var<0>(var, p, mt, smem_bytes, stream);
+}
+
+}  // namespace b200q

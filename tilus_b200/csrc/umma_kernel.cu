@@ -2,27 +2,32 @@
 //
 // The product is computed transposed, D[n, m] = sum_k W[k, n] * A[m, k], so that the
 // dequantized weights are the operand that lives in tensor memory and the activations are
-// the operand that TMA brings to shared memory:
+// the operand that TMA brings to shared memory.  A CTA is persistent: it walks over output
+// tiles of 128 weight columns x TM activation rows (TM = 32 .. 256, the N extent of the MMA),
+// each over all of K (or one of S splits of it), with the pipelines running across tile
+// boundaries.  Warp roles:
 //
-//   * the 128 lanes of tensor memory are 128 weight columns n; a CTA owns a tile of
-//     128 columns x TM activation rows (TM = 32 .. 256, the N extent of the MMA) and all of
-//     K (or one of S splits of it);
-//   * warps 0-7 dequantize.  Thread t of warp w is lane n = 32 * (w % 4) + t.  For a block
-//     of 64 k it reads its column's 2 units (64 codes, 16*b contiguous bytes) from global
-//     memory, decodes and scales them in registers with the unit decoder (decode.cuh; the
-//     weights are fp16_rn(value * scale), exactly the values the reference multiplies by,
-//     examples/quantization/matmul_a16wx.py:316-320) and writes the 32 half2 results to 32
-//     columns of tensor memory with one tcgen05.st.  Warps 0-3 take the even 64-blocks,
-//     warps 4-7 the odd ones;
-//   * warp 8 is the TMA producer: one 2-D tiled copy (128-byte swizzle) per 64-block brings
-//     A[m0 : m0+TM, k : k+64] into a 4-deep shared-memory ring; rows past M read as zero;
-//   * warp 9 owns tensor memory (alloc / dealloc) and issues the MMAs: per 64-block four
+//   * warp 13, weight producer: per 128-row group it brings the packed weights of the tile's
+//     128 columns (eight 16-column pieces of 256*b contiguous bytes, cp.async.bulk) and their
+//     128 fp16 scales into a 4-deep shared-memory ring;
+//   * warps 0-7 dequantize.  Thread t of warp w is lane n = 32 * (w % 4) + t of tensor
+//     memory.  For a block of 64 k it reads its column's 2 units (64 codes, 16*b contiguous
+//     bytes) from the ring, decodes and scales them in registers with the unit decoder
+//     (decode.cuh; the weights are fp16_rn(value * scale), exactly the values the reference
+//     multiplies by, examples/quantization/matmul_a16wx.py:316-320) and writes the 32 half2
+//     results to 32 columns of tensor memory with one tcgen05.st.  Warps 0-3 take the even
+//     64-blocks, warps 4-7 the odd ones;
+//   * warp 12, activation producer: one 2-D tiled TMA copy (128-byte swizzle) per 64-block
+//     brings A[m0 : m0+TM, k : k+64] into a shared-memory ring; rows past M read as zero;
+//   * warp 14 owns tensor memory (alloc / dealloc) and issues the MMAs: per 64-block four
 //     tcgen05.mma.cta_group::1.kind::f16 (K = 16 each) with the weight operand in tensor
 //     memory, the activation operand through a shared-memory descriptor and the fp32
 //     accumulator D (128 lanes x TM columns) in tensor memory; tcgen05.commit releases the
 //     activation stage and the weight stage when the MMAs have read them;
-//   * after the last block warps 0-3 read D with tcgen05.ld, convert to fp16 and store
-//     C[m, n] (64-byte row segments), or add into the fp32 split-K scratch.
+//   * warps 8-11, epilogue: when a tile's last MMA has completed they read D with
+//     tcgen05.ld, convert to fp16 and store C[m, n] (or add into the fp32 split-K scratch),
+//     then hand D back.  Meanwhile the producers and the dequantizers are already working on
+//     the next tile, so the tensor pipe restarts as soon as D is free.
 //
 // Every mbarrier wait is bounded in time; a wait that runs out raises a CTA-wide abort flag,
 // all loops leave, tensor memory is still freed and the status word of the workspace reports
@@ -30,6 +35,7 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "umma_common.cuh"
 
 #ifndef B200Q_PART
 #define B200Q_PART 0
@@ -40,98 +46,63 @@
 
 namespace b200q {
 
-constexpr int UMMA_THREADS = 320;   // 8 dequant warps + TMA warp + MMA warp
-constexpr int UMMA_SA = 4;          // activation stages
-constexpr int UMMA_SW = 8;          // weight stages (32 tensor-memory columns each)
+constexpr int UMMA_THREADS = 480;   // 8 dequant warps, 4 epilogue warps, 2 producers, MMA warp
+constexpr int UMMA_SA_MAX = 6;      // activation stages (most)
+constexpr int UMMA_SW = 8;          // weight stages in tensor memory (32 columns each)
+constexpr int UMMA_WG = 4;          // 128-row weight groups in the shared-memory ring
 constexpr int UMMA_WCOL0 = 256;     // first tensor-memory column of the weight stages
 constexpr int UMMA_TMEM_COLS = 512;
 
 struct UmmaBarriers {
-  uint64_t a_full[UMMA_SA], a_empty[UMMA_SA];
+  uint64_t a_full[UMMA_SA_MAX], a_empty[UMMA_SA_MAX];
   uint64_t w_full[UMMA_SW], w_empty[UMMA_SW];
-  uint64_t d_full;
+  uint64_t g_full[UMMA_WG], g_empty[UMMA_WG];
+  uint64_t d_full, d_empty;
   uint32_t tmem_base;
   volatile int abort_flag;
+  int last_flag;
 };
 
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-// bounded wait (about two seconds); also gives up as soon as another thread raised the abort flag
-__device__ __forceinline__ bool mbar_wait_abortable(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  uint64_t t0 = 0;
-  for (int it = 0;; ++it) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, 0x10000;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    if (ok) return true;
-    if (*abort_flag) return false;
-    uint64_t now;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-    if (it == 0) t0 = now;
-    else if (now - t0 > 2000000000ull) { *abort_flag = 1; return false; }
-  }
-}
-
-// shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 64 fp16
-// (128 bytes), 8-row groups 1024 bytes apart (stride byte offset), descriptor version 1
-__device__ __forceinline__ uint64_t umma_smem_desc(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);  // start address
-  d |= (uint64_t)1 << 16;                        // leading byte offset (unused for swizzled K-major)
-  d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset
-  d |= (uint64_t)1 << 46;                        // version
-  d |= (uint64_t)2 << 61;                        // SWIZZLE_128B
-  return d;
-}
-// instruction descriptor: D fp32, A/B fp16, both K-major, M = 128, N = tm
-__device__ __forceinline__ uint32_t umma_idesc(int tm) {
-  return (1u << 4) | ((uint32_t)(tm >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-}
+__host__ __device__ constexpr int umma_wstage_bytes(int bits) { return 2048 * bits + 256; }
 
 template <int VAR>
 __global__ void __launch_bounds__(UMMA_THREADS, 1)
 umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
   constexpr int B = var_bits(VAR);
+  constexpr uint32_t WSTAGE = (uint32_t)umma_wstage_bytes(B);
   extern __shared__ __align__(1024) unsigned char smem_raw[];
-  // [0, SA * TM * 128): activation stages (1024-byte aligned), then the barriers
-  // (the 128-byte swizzle wants the stages on 1024-byte boundaries: align by hand)
+  // [0, SA * TM * 128): activation stages (1024-byte aligned for the 128-byte swizzle: aligned
+  // by hand), then the weight ring, then the barriers
   const uint32_t smem_unaligned = (uint32_t)__cvta_generic_to_shared(smem_raw);
   const uint32_t smem_base = (smem_unaligned + 1023u) & ~1023u;
   unsigned char* smem_al = smem_raw + (smem_base - smem_unaligned);
   const int TM = p.tm;
+  const int SA = p.a_stages;
   const uint32_t stage_bytes = (uint32_t)TM * 128u;
-  UmmaBarriers* bars = reinterpret_cast<UmmaBarriers*>(smem_al + (size_t)UMMA_SA * stage_bytes);
-  const uint32_t bars_s = smem_base + UMMA_SA * stage_bytes;
+  const uint32_t wring_s = smem_base + (uint32_t)SA * stage_bytes;
+  const uint32_t bars_off = (uint32_t)SA * stage_bytes + UMMA_WG * WSTAGE;
+  UmmaBarriers* bars = reinterpret_cast<UmmaBarriers*>(smem_al + bars_off);
+  const uint32_t bars_s = smem_base + bars_off;
 #define BAR_ADDR(field, i) (bars_s + (uint32_t)offsetof(UmmaBarriers, field) + (uint32_t)(i) * 8u)
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  // blockIdx.x = (split * n_tiles + n_tile) * m_tiles + m_tile: CTAs that run together share weights
-  const int m_tile = blockIdx.x % p.m_tiles;
-  const int n_tile = (blockIdx.x / p.m_tiles) % p.n_tiles;
-  const int split = blockIdx.x / (p.m_tiles * p.n_tiles);
-  const int kk0 = split * p.kblocks_per_split;  // first 64-block of this CTA
-  const int nkk = p.kblocks_per_split;
-  const int m0 = m_tile * TM;
+  const int total_tiles = p.splits * p.n_tiles * p.m_tiles;
+  const int nkk = p.kblocks_per_split;  // 64-blocks per tile (even)
+  const int ngrp = nkk >> 1;            // 128-row groups per tile
   volatile int* abort_flag = &bars->abort_flag;
 
   if (tid == 0) {
-    for (int i = 0; i < UMMA_SA; ++i) { mbar_init(BAR_ADDR(a_full, i), 1); mbar_init(BAR_ADDR(a_empty, i), 1); }
+    for (int i = 0; i < UMMA_SA_MAX; ++i) { mbar_init(BAR_ADDR(a_full, i), 1); mbar_init(BAR_ADDR(a_empty, i), 1); }
     for (int i = 0; i < UMMA_SW; ++i) { mbar_init(BAR_ADDR(w_full, i), 4); mbar_init(BAR_ADDR(w_empty, i), 1); }
+    for (int i = 0; i < UMMA_WG; ++i) { mbar_init(BAR_ADDR(g_full, i), 1); mbar_init(BAR_ADDR(g_empty, i), 8); }
     mbar_init(BAR_ADDR(d_full, 0), 1);
+    mbar_init(BAR_ADDR(d_empty, 0), 4);
     bars->abort_flag = 0;
+    bars->last_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  if (warp == 9) {
+  if (warp == 14) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      bars_s + (uint32_t)offsetof(UmmaBarriers, tmem_base)),
                  "r"(UMMA_TMEM_COLS)
@@ -143,166 +114,293 @@ umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = bars->tmem_base;
 
+  // tile t -> (split, n_tile, m_tile), m fastest: CTAs that run together share weight columns
+#define TILE_COORDS(t)                                        \
+  const int m_tile = (t) % p.m_tiles;                         \
+  const int n_tile = ((t) / p.m_tiles) % p.n_tiles;           \
+  const int split = (t) / (p.m_tiles * p.n_tiles);            \
+  const int kk0 = split * nkk;                                \
+  const int m0 = m_tile * TM;                                 \
+  (void)m_tile; (void)n_tile; (void)split; (void)kk0; (void)m0;
+
   if (warp < 8) {
-    // ================= dequantize: global -> registers -> tensor memory =================
-    const int grp = warp >> 2;                      // 0: even 64-blocks, 1: odd ones
-    const int nl = (warp & 3) * 32 + lane;          // lane of tensor memory = column inside the tile
-    const int n = n_tile * 128 + nl;
-    const bool nvalid = n < p.N;
-    const int nt = n >> 4, half = (n >> 3) & 1, r = n & 7;
-    // words of this column inside a block: group c, units j: ((c*2 + half)*32 + r*4 + j) * B
-    const uint32_t* col_words = reinterpret_cast<const uint32_t*>(p.bq) + (size_t)nt * p.KB * (256 * B) +
-                                (size_t)(half * 32 + r * 4) * B;
+    // ================= dequantize: shared-memory ring -> registers -> tensor memory =================
+    const int grp = warp >> 2;              // 0: even 64-blocks, 1: odd ones
+    const int nl = (warp & 3) * 32 + lane;  // lane of tensor memory = column inside the tile
+    // this column inside a ring stage: 16-column piece nl / 16, then unit (half*32 + r*4 + j)
+    const uint32_t lane_off = (uint32_t)((nl >> 4) * (256 * B) + (((nl >> 3) & 1) * 32 + (nl & 7) * 4 + grp * 2) * (B * 4));
     const uint32_t taddr_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16) + UMMA_WCOL0;
-
-    uint32_t wcur[2 * B], wnxt[2 * B];
-    __half scur = __float2half(0.f), snxt = __float2half(0.f);
-    auto load_block = [&](int kk, uint32_t (&w)[2 * B], __half& s) {
-      // 64-block kk: block kk / 8, group (kk % 8) / 2, units (kk % 2) * 2 + {0, 1}
-      const int kb = kk >> 3, c = (kk >> 1) & 3, j0 = (kk & 1) * 2;
-      if (nvalid) {
-        const uint32_t* src = col_words + (size_t)kb * (256 * B) + (size_t)(c * 64 + j0) * B;
-        if constexpr ((2 * B) % 4 == 0) {
+    int g_run = 0;  // groups consumed so far (all tiles)
+    bool good = true;
+    TL_DECL(acc_g); TL_DECL(acc_w);
+#ifdef B200Q_TIMELINE
+    const long long t_begin = clock64();
+#endif
+    for (int t = blockIdx.x; t < total_tiles && good; t += gridDim.x) {
+      TILE_COORDS(t)
+      const bool nvalid = n_tile * 128 + nl < p.N;
+      for (int g = 0; g < ngrp; ++g, ++g_run) {
+        const int gs = g_run % UMMA_WG;
+        if (!WAIT_ACC(acc_g, mbar_wait_abortable(BAR_ADDR(g_full, gs), (uint32_t)(g_run / UMMA_WG) & 1u, abort_flag))) { good = false; break; }
+        uint32_t w[2 * B];
+        const uint32_t st = wring_s + (uint32_t)gs * WSTAGE;
+        lds_two_units<B>(st + lane_off, w);
+        unsigned short sbits;
+        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sbits) : "r"(st + 2048u * B + (uint32_t)nl * 2u));
+        if (!nvalid) {
 #pragma unroll
-          for (int q = 0; q < 2 * B / 4; ++q) {
-            const uint4 v = __ldg(reinterpret_cast<const uint4*>(src) + q);
-            w[4 * q] = v.x; w[4 * q + 1] = v.y; w[4 * q + 2] = v.z; w[4 * q + 3] = v.w;
-          }
-        } else {
-#pragma unroll
-          for (int q = 0; q < B; ++q) {
-            const uint2 v = __ldg(reinterpret_cast<const uint2*>(src) + q);
-            w[2 * q] = v.x; w[2 * q + 1] = v.y;
-          }
+          for (int q = 0; q < 2 * B; ++q) w[q] = 0u;
+          sbits = 0;
         }
-        const int row = p.gshift >= 0 ? ((kk >> 1) >> p.gshift) : 0;
-        s = __ldg(p.scales + (size_t)row * p.N + n);
-      } else {
+        uint32_t out[32];
+        const __half2 s2 = __half2half2(__ushort_as_half(sbits));
+        if (p.debug & 1) {  // timing experiments: no decode
 #pragma unroll
-        for (int q = 0; q < 2 * B; ++q) w[q] = 0u;
-        s = __float2half(0.f);
+          for (int q = 0; q < 32; ++q) out[q] = w[q % (2 * B)];
+        } else {
+          unit_decode_scaled<VAR>(w, s2, out);
+          unit_decode_scaled<VAR>(w + B, s2, out + 16);
+        }
+        // the ring stage has been read (its values fed the arithmetic above)
+        __syncwarp();
+        if (lane == 0) mbar_arrive(BAR_ADDR(g_empty, gs));
+        const int wi = 2 * g_run + grp;  // running 64-block index
+        const int sw = wi % UMMA_SW;
+        if (!WAIT_ACC(acc_w, mbar_wait_abortable(BAR_ADDR(w_empty, sw), ((uint32_t)(wi / UMMA_SW) & 1u) ^ 1u, abort_flag))) { good = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t taddr = taddr_lane + (uint32_t)(sw * 32);
+        if (!(p.debug & 8))
+        asm volatile(
+            "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, "
+            "%14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(
+                taddr),
+            "r"(out[0]), "r"(out[1]), "r"(out[2]), "r"(out[3]), "r"(out[4]), "r"(out[5]), "r"(out[6]), "r"(out[7]),
+            "r"(out[8]), "r"(out[9]), "r"(out[10]), "r"(out[11]), "r"(out[12]), "r"(out[13]), "r"(out[14]),
+            "r"(out[15]), "r"(out[16]), "r"(out[17]), "r"(out[18]), "r"(out[19]), "r"(out[20]), "r"(out[21]),
+            "r"(out[22]), "r"(out[23]), "r"(out[24]), "r"(out[25]), "r"(out[26]), "r"(out[27]), "r"(out[28]),
+            "r"(out[29]), "r"(out[30]), "r"(out[31])
+            : "memory");
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(BAR_ADDR(w_full, sw));
       }
-    };
-
-    int kk = kk0 + grp;
-    if (kk < kk0 + nkk) load_block(kk, wcur, scur);
-    for (int i = grp; i < nkk; i += 2, kk += 2) {
-      if (i + 2 < nkk) load_block(kk + 2, wnxt, snxt);
-      const int sw = i % UMMA_SW;
-      const uint32_t par = ((uint32_t)(i / UMMA_SW) & 1u) ^ 1u;
-      if (!mbar_wait_abortable(BAR_ADDR(w_empty, sw), par, abort_flag)) break;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      uint32_t out[32];
-      const __half2 s2 = __half2half2(scur);
-      unit_decode_scaled<VAR>(wcur, s2, out);
-      unit_decode_scaled<VAR>(wcur + B, s2, out + 16);
-      const uint32_t taddr = taddr_lane + (uint32_t)(sw * 32);
-      asm volatile(
-          "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, "
-          "%14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(
-              taddr),
-          "r"(out[0]), "r"(out[1]), "r"(out[2]), "r"(out[3]), "r"(out[4]), "r"(out[5]), "r"(out[6]), "r"(out[7]),
-          "r"(out[8]), "r"(out[9]), "r"(out[10]), "r"(out[11]), "r"(out[12]), "r"(out[13]), "r"(out[14]),
-          "r"(out[15]), "r"(out[16]), "r"(out[17]), "r"(out[18]), "r"(out[19]), "r"(out[20]), "r"(out[21]),
-          "r"(out[22]), "r"(out[23]), "r"(out[24]), "r"(out[25]), "r"(out[26]), "r"(out[27]), "r"(out[28]),
-          "r"(out[29]), "r"(out[30]), "r"(out[31])
-          : "memory");
-      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) mbar_arrive(BAR_ADDR(w_full, sw));
-#pragma unroll
-      for (int q = 0; q < 2 * B; ++q) wcur[q] = wnxt[q];
-      scur = snxt;
     }
-
-    // ================= epilogue: warps 0-3 read D and write C =================
-    if (warp < 4) {
-      const bool got = mbar_wait_abortable(BAR_ADDR(d_full, 0), 0, abort_flag);
+#ifdef B200Q_TIMELINE
+    if (lane == 0 && (warp == 0 || warp == 4)) {
+      TL_WRITE(warp == 0 ? 0 : 3, clock64() - t_begin);
+      TL_WRITE(warp == 0 ? 1 : 4, acc_g);
+      TL_WRITE(warp == 0 ? 2 : 5, acc_w);
+    }
+#endif
+  } else if (warp < 12) {
+    // ================= epilogue: read D, write C (or add into the split-K scratch) =================
+    const int ew = warp - 8;  // lane quadrant of tensor memory this warp may read
+    const int nl = ew * 32 + lane;
+    const uint32_t daddr = tmem + ((uint32_t)(ew * 32) << 16);
+    int tile_it = 0;
+    bool good = true;
+    TL_DECL(acc_d); TL_DECL(acc_epi);
+    for (int t = blockIdx.x; t < total_tiles && good; t += gridDim.x, ++tile_it) {
+      TILE_COORDS(t)
+      const int n = n_tile * 128 + nl;
+      const bool nvalid = n < p.N;
+      if (!WAIT_ACC(acc_d, mbar_wait_abortable(BAR_ADDR(d_full, 0), (uint32_t)tile_it & 1u, abort_flag))) { good = false; break; }
+#ifdef B200Q_TIMELINE
+      const long long t_epi = clock64();
+#endif
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      if (got) {
-        const uint32_t daddr = tmem + ((uint32_t)(warp * 32) << 16);
-        for (int c0 = 0; c0 < TM; c0 += 32) {
-          uint32_t v[32];
-          asm volatile(
-              "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, "
-              "%14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-              : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-                "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]),
-                "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]),
-                "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]),
-                "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-              : "r"(daddr + (uint32_t)c0)
-              : "memory");
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-          if (nvalid) {
+      for (int c0 = 0; c0 < TM; c0 += 32) {
+        uint32_t v[32];
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, "
+            "%14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+            : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+              "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]),
+              "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]),
+              "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]),
+              "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+            : "r"(daddr + (uint32_t)c0)
+            : "memory");
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (c0 + 32 >= TM) {
+          // D is in registers: the next tile's MMAs may overwrite it
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive(BAR_ADDR(d_empty, 0));
+        }
+        if (m0 + c0 < p.M && !(p.debug & 4)) {
+          // lanes 2i and 2i+1 hold columns n, n+1 of the same 32 rows: exchange so that the even
+          // lane stores the even rows and the odd lane the odd rows, two columns (4 bytes) at a time
+          const bool odd = lane & 1;
 #pragma unroll
-            for (int q = 0; q < 32; ++q) {
-              const int m = m0 + c0 + q;
-              if (m < p.M) {
-                const float x = __uint_as_float(v[q]);
-                if (p.splits == 1) p.c[(size_t)m * p.ldc + n] = __float2half_rn(x);
-                else atomicAdd(p.partial + (size_t)m * p.N + n, x);
+          for (int q = 0; q < 32; q += 2) {
+            const uint32_t mine = odd ? v[q + 1] : v[q];      // row q + odd, own column
+            const uint32_t give = odd ? v[q] : v[q + 1];      // row q + !odd, own column
+            const uint32_t got = __shfl_xor_sync(0xffffffffu, give, 1);  // row q + odd, the other column
+            const float lo = __uint_as_float(odd ? got : mine), hi = __uint_as_float(odd ? mine : got);
+            const int m = m0 + c0 + q + (odd ? 1 : 0);
+            const int ne = n & ~1;
+            if (m < p.M && ne < p.N) {
+              if (p.splits == 1) {
+                *reinterpret_cast<__half2*>(p.c + (size_t)m * p.ldc + ne) = __floats2half2_rn(lo, hi);
+              } else {
+                red_add_v2(p.partial + (size_t)m * p.N + ne, lo, hi);
               }
             }
           }
         }
       }
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      (void)nvalid;
+      if (p.splits > 1) {
+        // the last split to arrive converts the fp32 sums and restores the zeros
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (warp == 8 && lane == 0) {
+          __threadfence();
+          const int old = atomicAdd(p.counters + n_tile * p.m_tiles + m_tile, 1);
+          const int last = (old + 1 == p.splits) ? 1 : 0;
+          if (last) __threadfence();
+          bars->last_flag = last;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (bars->last_flag) {
+          for (int idx = tid - 256; idx < 64 * TM; idx += 128) {
+            const int nn = n_tile * 128 + (idx & 63) * 2, m = m0 + (idx >> 6);
+            if (nn < p.N && m < p.M) {
+              float2* src = reinterpret_cast<float2*>(p.partial + (size_t)m * p.N + nn);
+              const float2 x = __ldcg(src);
+              *reinterpret_cast<__half2*>(p.c + (size_t)m * p.ldc + nn) = __floats2half2_rn(x.x, x.y);
+              __stcg(src, make_float2(0.f, 0.f));
+            }
+          }
+          if (warp == 8 && lane == 0) p.counters[n_tile * p.m_tiles + m_tile] = 0;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // last_flag may be rewritten by the next tile
+      }
+#ifdef B200Q_TIMELINE
+      acc_epi += clock64() - t_epi;
+#endif
     }
-  } else if (warp == 8) {
+#ifdef B200Q_TIMELINE
+    if (warp == 8 && lane == 0) { TL_WRITE(6, acc_d); TL_WRITE(7, acc_epi); }
+#endif
+  } else if (warp == 12) {
     // ================= TMA producer: activations =================
     if (lane == 0) {
-      for (int i = 0; i < nkk; ++i) {
-        const int sa = i % UMMA_SA;
-        const uint32_t par = ((uint32_t)(i / UMMA_SA) & 1u) ^ 1u;
-        if (!mbar_wait_abortable(BAR_ADDR(a_empty, sa), par, abort_flag)) break;
-        const uint32_t bar = BAR_ADDR(a_full, sa);
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(stage_bytes)
-                     : "memory");
-        const int kx = (kk0 + i) * 64;
-        asm volatile(
-            "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-            ::"r"(smem_base + (uint32_t)sa * stage_bytes), "l"(&tmap_a), "r"(bar), "r"(kx), "r"(m0)
-            : "memory");
+      int ai = 0;
+      bool good = true;
+      TL_DECL(acc_ae);
+      for (int t = blockIdx.x; t < total_tiles && good; t += gridDim.x) {
+        TILE_COORDS(t)
+        for (int i = 0; i < nkk; ++i, ++ai) {
+          const int sa = ai % SA;
+          if (!WAIT_ACC(acc_ae, mbar_wait_abortable(BAR_ADDR(a_empty, sa), ((uint32_t)(ai / SA) & 1u) ^ 1u, abort_flag))) { good = false; break; }
+          const uint32_t bar = BAR_ADDR(a_full, sa);
+          if (p.debug & 2) { mbar_arrive(bar); continue; }  // timing experiments: no activation traffic
+          asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(stage_bytes)
+                       : "memory");
+          const int kx = (kk0 + i) * 64;
+          asm volatile(
+              "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+              ::"r"(smem_base + (uint32_t)sa * stage_bytes), "l"(&tmap_a), "r"(bar), "r"(kx), "r"(m0)
+              : "memory");
+        }
+      }
+      TL_WRITE(8, acc_ae);
+    }
+  } else if (warp == 13) {
+    // ================= bulk-copy producer: packed weights and scales =================
+    int g_run = 0;
+    bool good = true;
+    TL_DECL(acc_ge);
+    const unsigned char* bq = reinterpret_cast<const unsigned char*>(p.bq);
+    for (int t = blockIdx.x; t < total_tiles && good; t += gridDim.x) {
+      TILE_COORDS(t)
+      const int nt0 = n_tile * 8;
+      const int pieces = min(8, p.N / BLOCK_N - nt0);  // 16-column pieces of this tile that exist
+      for (int g = 0; g < ngrp; ++g, ++g_run) {
+        const int gs = g_run % UMMA_WG;
+        int ok = 1;
+        if (lane == 0) ok = WAIT_ACC(acc_ge, mbar_wait_abortable(BAR_ADDR(g_empty, gs), ((uint32_t)(g_run / UMMA_WG) & 1u) ^ 1u, abort_flag)) ? 1 : 0;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) { good = false; break; }
+        const uint32_t bar = BAR_ADDR(g_full, gs);
+        const uint32_t dst = wring_s + (uint32_t)gs * WSTAGE;
+        if (lane == 0)
+          asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar),
+                       "r"((uint32_t)pieces * (256u * B + 32u))
+                       : "memory");
+        __syncwarp();
+        const int G = (kk0 >> 1) + g;  // 128-row group of K
+        if (lane < pieces) {
+          const unsigned char* src = bq + ((size_t)(nt0 + lane) * p.KB + (G >> 2)) * (size_t)(1024 * B) +
+                                     (size_t)(G & 3) * (256 * B);
+          asm volatile(
+              "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                  dst + (uint32_t)lane * (256u * B)),
+              "l"(src), "r"(256u * B), "r"(bar)
+              : "memory");
+        } else if (lane == 8) {
+          const int row = p.gshift >= 0 ? (G >> p.gshift) : 0;
+          const __half* src = p.scales + (size_t)row * p.N + n_tile * 128;
+          asm volatile(
+              "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                  dst + 2048u * B),
+              "l"(src), "r"((uint32_t)pieces * 32u), "r"(bar)
+              : "memory");
+        }
       }
     }
+    if (lane == 0) TL_WRITE(9, acc_ge);
   } else {
     // ================= MMA issuer =================
     if (lane == 0) {
       const uint32_t idesc = umma_idesc(TM);
       bool good = true;
-      for (int i = 0; i < nkk && good; ++i) {
-        const int sa = i % UMMA_SA, sw = i % UMMA_SW;
-        good = mbar_wait_abortable(BAR_ADDR(a_full, sa), (uint32_t)(i / UMMA_SA) & 1u, abort_flag) &&
-               mbar_wait_abortable(BAR_ADDR(w_full, sw), (uint32_t)(i / UMMA_SW) & 1u, abort_flag);
-        if (!good) break;
+      int ai = 0, tile_it = 0;
+      TL_DECL(acc_de); TL_DECL(acc_af); TL_DECL(acc_wf);
+#ifdef B200Q_TIMELINE
+      const long long t_begin = clock64();
+#endif
+      for (int t = blockIdx.x; t < total_tiles && good; t += gridDim.x, ++tile_it) {
+        // D must have been read out by the epilogue of the previous tile
+        if (!WAIT_ACC(acc_de, mbar_wait_abortable(BAR_ADDR(d_empty, 0), ((uint32_t)tile_it & 1u) ^ 1u, abort_flag))) { good = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint64_t bdesc = umma_smem_desc(smem_base + (uint32_t)sa * stage_bytes);
-        const uint32_t a_tmem = tmem + UMMA_WCOL0 + (uint32_t)(sw * 32);
+        for (int i = 0; i < nkk; ++i, ++ai) {
+          const int sa = ai % SA, sw = ai % UMMA_SW;
+          good = WAIT_ACC(acc_af, mbar_wait_abortable(BAR_ADDR(a_full, sa), (uint32_t)(ai / SA) & 1u, abort_flag)) &&
+                 WAIT_ACC(acc_wf, mbar_wait_abortable(BAR_ADDR(w_full, sw), (uint32_t)(ai / UMMA_SW) & 1u, abort_flag));
+          if (!good) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint64_t bdesc = umma_smem_desc(smem_base + (uint32_t)sa * stage_bytes);
+          const uint32_t a_tmem = tmem + UMMA_WCOL0 + (uint32_t)(sw * 32);
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-          const uint32_t accumulate = (i > 0 || ks > 0) ? 1u : 0u;
-          asm volatile(
-              "{\n\t.reg .pred p;\n\t"
-              "setp.ne.b32 p, %4, 0;\n\t"
-              "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-              ::"r"(tmem), "r"(a_tmem + (uint32_t)(ks * 8)), "l"(bdesc + (uint64_t)(ks * 2)), "r"(idesc),
-              "r"(accumulate)
-              : "memory");
+          for (int ks = 0; ks < 4; ++ks) {
+            const uint32_t accumulate = (i > 0 || ks > 0) ? 1u : 0u;
+            asm volatile(
+                "{\n\t.reg .pred p;\n\t"
+                "setp.ne.b32 p, %4, 0;\n\t"
+                "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                ::"r"(tmem), "r"(a_tmem + (uint32_t)(ks * 8)), "l"(bdesc + (uint64_t)(ks * 2)), "r"(idesc),
+                "r"(accumulate)
+                : "memory");
+          }
+          // the stages may be overwritten once these MMAs have read them
+          asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                           BAR_ADDR(a_empty, sa))
+                       : "memory");
+          asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                           BAR_ADDR(w_empty, sw))
+                       : "memory");
         }
-        // the stages may be overwritten once these MMAs have read them
-        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                         BAR_ADDR(a_empty, sa))
-                     : "memory");
-        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                         BAR_ADDR(w_empty, sw))
-                     : "memory");
+        if (good)
+          asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                           BAR_ADDR(d_full, 0))
+                       : "memory");
       }
-      if (good)
-        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                         BAR_ADDR(d_full, 0))
-                     : "memory");
+#ifdef B200Q_TIMELINE
+      TL_WRITE(10, clock64() - t_begin); TL_WRITE(11, acc_de); TL_WRITE(12, acc_af); TL_WRITE(13, acc_wf);
+#endif
     }
   }
 
@@ -316,35 +414,12 @@ umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
     p.status[2] = blockIdx.x;
     p.status[3] = 0;
   }
-  if (warp == 9) {
+  if (warp == 14) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(UMMA_TMEM_COLS) : "memory");
   }
-
-  // ---- split-K: the last CTA of a tile converts the fp32 sums and restores the zeros ----
-  if (p.splits > 1 && !*abort_flag) {
-    __shared__ int s_last;
-    __syncthreads();
-    if (tid == 0) {
-      __threadfence();
-      const int old = atomicAdd(p.counters + n_tile * p.m_tiles + m_tile, 1);
-      s_last = (old + 1 == p.splits) ? 1 : 0;
-      if (s_last) __threadfence();
-    }
-    __syncthreads();
-    if (s_last) {
-      for (int idx = tid; idx < 128 * TM; idx += UMMA_THREADS) {
-        const int n = n_tile * 128 + (idx & 127), m = m0 + (idx >> 7);
-        if (n < p.N && m < p.M) {
-          float* src = p.partial + (size_t)m * p.N + n;
-          p.c[(size_t)m * p.ldc + n] = __float2half_rn(__ldcg(src));
-          __stcg(src, 0.f);
-        }
-      }
-      if (tid == 0) p.counters[n_tile * p.m_tiles + m_tile] = 0;
-    }
-  }
 #undef BAR_ADDR
+#undef TILE_COORDS
 }
 
 template <int VAR>
@@ -359,7 +434,7 @@ static cudaError_t umma_launch_one(const UmmaParams& p, const CUtensorMap& tmap,
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 16) configured_smem[dev] = smem_bytes;
   }
-  kern<<<p.splits * p.n_tiles * p.m_tiles, UMMA_THREADS, smem_bytes, stream>>>(p, tmap);
+  kern<<<p.grid, UMMA_THREADS, smem_bytes, stream>>>(p, tmap);
   return cudaGetLastError();
 }
 
@@ -383,7 +458,16 @@ cudaError_t B200Q_CAT(umma_launch_part, B200Q_PART)(int var, const UmmaParams& p
 }
 
 #if B200Q_PART == 0
-int umma_smem_bytes(int tm) { return 1024 + UMMA_SA * tm * 128 + (int)sizeof(UmmaBarriers) + 64; }
+// dynamic shared memory: alignment slack + activation stages + weight ring + barriers
+int umma_smem_bytes(int tm, int bits, int a_stages) {
+  return 1024 + a_stages * tm * 128 + UMMA_WG * umma_wstage_bytes(bits) + (int)sizeof(UmmaBarriers) + 64;
+}
+// most activation stages (<= UMMA_SA_MAX) that fit next to the weight ring
+int umma_a_stages(int tm, int bits, int max_smem) {
+  int sa = UMMA_SA_MAX;
+  while (sa > 2 && umma_smem_bytes(tm, bits, sa) > max_smem) --sa;
+  return sa;
+}
 #endif
 
 }  // namespace b200q
