@@ -1,7 +1,7 @@
 """Benchmark of the weight-only quantized matmul hot path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
-                    [--no-sweep] [--no-prefill] [--profile-case decode|prefill|batch16]
+                    [--no-sweep] [--no-prefill] [--stack] [--profile-case decode|prefill|batch16]
 
 Headline workload (one GPU): decode GEMV, M=1, K=N=8192, uint4 codes with zero point 8,
 group 128, fp16 scales - the "u4 g128" decode configuration the metric is quoted on.
@@ -22,6 +22,9 @@ and the M=4096 prefill GEMM in TFLOP/s.
 
 `--impl reference` times the CPU dequantize + matmul path alone (the reference operator's
 semantics on the host cores), on the same workload and metric.
+
+`--stack` times the Llama-3-8B-shaped decode linear stack, N-sharded over the ranks with an
+NCCL all-gather of every layer's output (strong scaling), for M in {1, 8, 32, 64}.
 
 `--profile-case X` runs a few plain launches of one kernel on a problem larger than L2 and
 prints its CUDA-event time: the command line used for the ncu captures under profiles/.
@@ -49,7 +52,7 @@ R_LAYERS = 10   # distinct layers per pass: 10 x 33.5 MB of weights = 335 MB > 1
 ROUNDS = 10     # passes per graph: 100 launches per replay
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the headline kernel, from the
 # ncu capture summarised in profiles/stream_kernel_u4_m1_k8192_n8192.md
-DECODE_DRAM_TRAFFIC_BYTES = 34_700_000
+DECODE_DRAM_TRAFFIC_BYTES = 34_660_864
 
 
 def _peaks():
@@ -265,6 +268,109 @@ def run_profile_case(args) -> None:
                       "us_per_launch_plain_stream": us}))
 
 
+def run_stack(args) -> None:
+    """Llama-3-8B-shaped decode linear stack, N-sharded over the ranks, all-gather of every layer's
+    output: 32 x {qkv 4096->6144, o 4096->4096, gate_up 4096->28672, down 14336->4096}, uint4 g128
+    weights, batch M in {1, 8, 32, 64}.  Strong scaling: the model is fixed, the shards shrink with N.
+    A step = one pass over the 128 linears (+ 128 all-gathers), replayed from one CUDA graph when the
+    collectives can be captured, else launched eagerly."""
+    import torch.distributed as dist
+
+    from tilus_b200 import dtypes, float16, packing, sharded, synth
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    dt = dtypes.uint4b
+    shapes = [("qkv", 4096, 6144), ("o", 4096, 4096), ("gate_up", 4096, 28672), ("down", 14336, 4096)]
+    n_layers = 32
+    protos = {}
+    for name, k_in, n_out in shapes:  # one synthetic weight per shape, one device copy per layer
+        prob = synth.make_problem(1, n_out, k_in, dt, GROUP, seed=7)
+        n0, n1 = sharded.shard_range(n_out, world, rank)
+        protos[name] = (packing.interleave(prob["codes"][:, n0:n1].contiguous().to(dev), dt),
+                        prob["scales"][:, n0:n1].contiguous().to(dev), prob["zero_point"])
+    layers = []
+    for _ in range(n_layers):
+        block = []
+        for name, k_in, n_out in shapes:
+            bq, sc, zp = protos[name]
+            lin = sharded.ShardedQuantizedLinear(float16, dt, GROUP, k_in, n_out, zero_point=zp).to(dev)
+            lin.local.load_packed(bq, sc, layout="b200")
+            block.append(lin)
+        layers.append(block)
+    del protos
+    weight_bytes = sum(k * n // 2 + (k // GROUP) * n * 2 for _, k, n in shapes) * n_layers // world
+
+    def step(x):
+        for qkv, o, gate_up, down in layers:
+            h = qkv(x)
+            h = o(h[:, :4096])
+            h = gate_up(h)
+            x = down(h[:, :14336])
+        return x
+
+    results = {}
+    graphs = []
+    for m in (1, 8, 32, 64):
+        x = (torch.randn(m, 4096, generator=torch.Generator().manual_seed(m)) * 0.05).to(torch.float16).to(dev)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                step(x)
+        torch.cuda.synchronize()
+        mode = "cuda graph"
+        try:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                out = step(x)  # noqa: F841
+            run = g.replay
+            graphs.append(g)
+        except Exception:  # collectives that cannot be captured: launch eagerly
+            torch.cuda.synchronize()
+            mode = "eager"
+            run = lambda: step(x)  # noqa: E731
+        for _ in range(max(args.warmup, 3)):
+            run()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            run()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / args.steps], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        results[f"M{m}"] = {"ms_per_step": round(ms, 4), "tokens_per_s": round(m / (ms * 1e-3), 1),
+                            "us_per_linear": round(ms * 1e3 / (4 * n_layers), 2),
+                            "per_gpu_weight_gbs": round(weight_bytes / (ms * 1e-3) / 1e9, 1), "launch": mode}
+    if rank == 0:
+        print(json.dumps({"metric": "Llama-3-8B-shaped decode linear stack, N-sharded, all-gather per layer",
+                          "unit": "ms per 128-linear step", "n_gpus": world, "steps": args.steps,
+                          "scaling": "strong", "dtype": "f16", "data": "synthetic",
+                          "config": {"workload": "llama3_8b_linear_stack_u4_g128", "layers": n_layers,
+                                     "per_gpu_weight_bytes": weight_bytes},
+                          "results": results}), flush=True)
+    if world > 1:
+        # graphs that captured NCCL kernels must be gone before the communicator is; tearing the
+        # communicator down under them has been seen to block, so the ranks leave without it
+        del run, graphs
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        os._exit(0)
+
+
 def run_b200(args) -> None:
     import torch.distributed as dist
 
@@ -298,7 +404,9 @@ def run_b200(args) -> None:
     # a step = `inner` graph replays, long enough for a few clock samples over the timed region
     inner = max(1, int(0.5 / (R_LAYERS * ROUNDS * 8e-6 * args.steps)))
     barrier()
+    torch.cuda.profiler.start()  # no-op unless a profiler is attached (ncu --profile-from-start off)
     ms = _time_graph(graph, args.steps * inner)
+    torch.cuda.profiler.stop()
     barrier()
     clocks = sampler.stop() if rank == 0 else None
     t = torch.tensor([ms], dtype=torch.float64, device=dev)
@@ -426,6 +534,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-sweep", action="store_true", help="skip the extra dtype / shape sweep")
     ap.add_argument("--no-prefill", action="store_true", help="skip the M=4096 prefill entry of the sweep")
+    ap.add_argument("--stack", action="store_true",
+                    help="time the N-sharded Llama-3-8B-shaped decode linear stack (all-gather per layer) instead")
     ap.add_argument("--profile-case", default=None, choices=["decode", "batch16", "prefill"],
                     help="run a few plain launches of one kernel (for ncu) instead of the benchmark")
     args = ap.parse_args()
@@ -433,6 +543,8 @@ def main():
         run_reference(args)
     elif args.profile_case:
         run_profile_case(args)
+    elif args.stack:
+        run_stack(args)
     else:
         run_b200(args)
 
