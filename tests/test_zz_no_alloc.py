@@ -45,10 +45,11 @@ def _gemm_both(M, N, K, dt, group, seed):
     return c_ref.float().cpu().numpy(), [o.float().cpu().numpy() for o in outs]
 
 
-@pytest.mark.parametrize("M,N,K", [(40, 256, 2048), (3, 272, 2048)])
+@pytest.mark.parametrize("M,N,K", [(200, 256, 2048), (40, 256, 2048), (3, 272, 2048)])
 def test_static_workspace_matches_gemm_twice(M, N, K):
-    # (40, 256, 2048) runs the tcgen05 kernel with split-K: the fp32 partial sums and the
-    # arrival counters live in the built-in scratch
+    # (200, 256, 2048) runs the tcgen05 kernel with split-K, the other two the mma.sync kernel with
+    # K cut in chunks / tiles shared between CTAs: in all of them fp32 partial sums and arrival
+    # counters live in the built-in scratch
     ref, outs = _gemm_both(M, N, K, D.int4b, 128, seed=21)
     scale = np.abs(ref).max()
     for got in outs:

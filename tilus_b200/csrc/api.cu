@@ -131,14 +131,19 @@ static int stream_pitch(int kc) {
 // CTA may use half of the SM's shared memory: (228 KB - 2 x 1 KB reserved) / 2.
 static const int kStreamSmemCap = 113 * 1024;
 static int stream_slot_bytes(int bits) { return stream_gi(bits) * 256 * bits; }
+// 8-row activation tiles per launch: 1 or 2 (the kernel's MT)
+static int stream_mt(int m_pass) { return m_pass <= 8 ? 1 : 2; }
+// most activation rows one launch of the stream kernel takes
+static int stream_rows_per_pass(int M) { (void)M; return 16; }
+static int stream_smem_cap(int m_pass, const DeviceInfo& di) { (void)m_pass; (void)di; return kStreamSmemCap; }
 // whole column tiles a CTA owns (their sums live in at most 16 KB of shared memory)
 static int stream_tiles_owned(int m_pass, int NT, int cpc) {
-  const int mt = (m_pass + 7) / 8, cap = 32 / mt;
+  const int mt = stream_mt(m_pass), cap = 32 / mt;
   const int t = NT / cpc;
   return t < cap ? t : cap;
 }
 static int stream_fixed_smem(int m_pass, int kc, int t_own) {
-  const int mt = (m_pass + 7) / 8;
+  const int mt = stream_mt(m_pass);
   // barriers, own-tile sums, activation chunk (+ 64 zero bytes), group sums as accumulator quads
   return 1024 + STREAM_WARPS * STREAM_SC_GROUPS * 32 + t_own * 16 * 8 * mt * 4 + m_pass * stream_pitch(kc) * 2 + 64 +
          (kc / 128) * 16 * mt * 4;
@@ -146,22 +151,25 @@ static int stream_fixed_smem(int m_pass, int kc, int t_own) {
 static int stream_smem(int m_pass, int kc, int bits, int stages, int t_own) {
   return stream_fixed_smem(m_pass, kc, t_own) + STREAM_WARPS * stages * stream_slot_bytes(bits);
 }
-static int stream_stages_for(int m_pass, int kc, int bits, int t_own) {
-  int st = (kStreamSmemCap - stream_fixed_smem(m_pass, kc, t_own)) / (STREAM_WARPS * stream_slot_bytes(bits));
+static int stream_stages_for(int m_pass, int kc, int bits, int t_own, const DeviceInfo& di) {
+  int st = (stream_smem_cap(m_pass, di) - stream_fixed_smem(m_pass, kc, t_own)) / (STREAM_WARPS * stream_slot_bytes(bits));
   return st > 8 ? 8 : st;
 }
 // CTAs per k chunk.  First choice: two CTAs per SM (32 warps hide the latency of the decode /
 // mma chains best) with a count that divides the column tiles evenly, so that no tile is
 // shared between CTAs and nothing goes through the global scratch; then one CTA per SM with
 // such a count; else one CTA per SM with the left-over tiles shared item-wise.
-static int stream_ctas_per_chunk(int NT, int s, const DeviceInfo& di) {
+static int stream_ctas_per_chunk(int NT, int s, int per_sm, const DeviceInfo& di) {
   const int full = di.sm_count / s;
-  for (int c = 2 * full; c >= 1 && c * 5 >= full * 8; --c)
+  if (full < 1) return 0;
+  for (int c = 2 * full; per_sm == 2 && c >= 1 && c * 5 >= full * 8; --c)
     if (NT % c == 0) return c;
   for (int c = full; c >= 1 && c * 5 >= full * 4; --c)
     if (NT % c == 0) return c;
   return full > NT ? NT : full;
 }
+static const int kStreamMaxRows = 16;
+static size_t stream_workspace_bytes(int N) { return WS_HEADER_BYTES + ws_counter_bytes(N) + (size_t)16 * N * sizeof(float); }
 // K is cut into the fewest chunks S (a divisor of K/512, at most one per SM) that leave room for
 // three ring slots per warp next to the activation chunk [M, K/S]; the grid is S * CPC.
 static int plan_stream(int m_pass, int N, int K, int bits, const DeviceInfo& di, b200q_plan_t* pl) {
@@ -170,13 +178,14 @@ static int plan_stream(int m_pass, int N, int K, int bits, const DeviceInfo& di,
   for (int want = 3; want >= 1 && !best_s; --want)
     for (int s = 1; s <= KB && s <= di.sm_count; ++s) {
       if (KB % s) continue;
-      const int cpc = stream_ctas_per_chunk(NT, s, di);
-      const int st = stream_stages_for(m_pass, (KB / s) * 512, bits, stream_tiles_owned(m_pass, NT, cpc));
+      const int cpc = stream_ctas_per_chunk(NT, s, 2, di);
+      if (cpc < 1) continue;
+      const int st = stream_stages_for(m_pass, (KB / s) * 512, bits, stream_tiles_owned(m_pass, NT, cpc), di);
       if (st >= want) { best_s = s; best_st = st; best_c = cpc; break; }
     }
   if (!best_s) return ST_UNSUPPORTED;
   pl->kernel = 2;
-  pl->m_tiles = (m_pass + 7) / 8;
+  pl->m_tiles = stream_mt(m_pass);
   pl->splits = best_s;
   pl->cluster = 1;
   pl->ctas_per_split = best_c;
@@ -227,7 +236,7 @@ static void plan_umma(int M, int N, int K, int bits, const DeviceInfo& di, b200q
   pl->stages = umma_a_stages(tm, bits, di.max_smem);
   pl->smem_bytes = umma_smem_bytes(tm, bits, pl->stages);
   pl->tile_m = tm;
-  pl->warps = 15;
+  pl->warps = 19;
   pl->passes = 1;
   pl->pdl = 0;
   pl->debug = 0;
@@ -237,18 +246,22 @@ static int make_plan(int M, int N, int K, int var, b200q_plan_t* pl) {
   const DeviceInfo di = device_info();
   std::memset(pl, 0, sizeof(*pl));
   const int bits = var_bits(var);
-  if (M > 16) {
-    plan_umma(M, N, K, bits, di, pl);
-    const size_t part = pl->splits > 1 ? (size_t)M * N * sizeof(float) : 0;
-    pl->workspace_bytes = WS_HEADER_BYTES + ws_counter_bytes(N) + part;
-    return ST_OK;
+  // up to 16 rows: the mma.sync stream kernel; above, the tcgen05 kernel.  (The stream kernel was
+  // also tried with 32 rows per launch for M <= 64: 45 us for M = 32, K = N = 8192 against ~40 us of the
+  // tcgen05 kernel - with K cut in 16 chunks its fp32 partial sums cost more than the decode saves.)
+  if (M <= kStreamMaxRows) {
+    const int rows = stream_rows_per_pass(M);
+    const int m_pass = M < rows ? M : rows;
+    if (plan_stream(m_pass, N, K, bits, di, pl) == ST_OK) {
+      pl->passes = (M + rows - 1) / rows;
+      pl->workspace_bytes = stream_workspace_bytes(N);  // fp32 scratch [N][8 or 16]
+      return ST_OK;
+    }
+    if (M <= 16) return ST_UNSUPPORTED;
   }
-  const int m_pass = M < 16 ? M : 16;
-  int st = plan_stream(m_pass, N, K, bits, di, pl);
-  if (st != ST_OK) return st;
-  pl->passes = (M + 15) / 16;
-  // fp32 scratch [N][8 or 16]
-  pl->workspace_bytes = WS_HEADER_BYTES + ws_counter_bytes(N) + (size_t)16 * N * sizeof(float);
+  plan_umma(M, N, K, bits, di, pl);
+  const size_t part = pl->splits > 1 ? (size_t)M * N * sizeof(float) : 0;
+  pl->workspace_bytes = WS_HEADER_BYTES + ws_counter_bytes(N) + part;
   return ST_OK;
 }
 
@@ -312,7 +325,7 @@ static int run_stream(const void* a, int lda, const void* bq, const void* scales
   if (pl.splits < 1 || KB % pl.splits != 0 || pl.ctas_per_split < 1) return ST_INVALID_ARG;
   if (pl.stages < 1 || pl.stages > 8) return ST_INVALID_ARG;
   if (((uintptr_t)scales) & 15) return ST_INVALID_ARG;  // scale rows are fetched with 32-byte bulk copies
-  const size_t need = WS_HEADER_BYTES + ws_counter_bytes(N) + (size_t)16 * N * sizeof(float);
+  const size_t need = stream_workspace_bytes(N);
   if (!workspace || ws_bytes < need || ((uintptr_t)workspace & 255)) return ST_WORKSPACE;
   StreamParams p;
   p.bq = bq;
@@ -330,8 +343,9 @@ static int run_stream(const void* a, int lda, const void* bq, const void* scales
   p.pdl = pl.pdl;
   p.tl = nullptr;
   p.tl_slot = -1;
-  for (int m0 = 0; m0 < M; m0 += 16) {
-    const int mc = (M - m0) < 16 ? (M - m0) : 16;
+  const int rows = stream_rows_per_pass(M);
+  for (int m0 = 0; m0 < M; m0 += rows) {
+    const int mc = (M - m0) < rows ? (M - m0) : rows;
     p.a = reinterpret_cast<const __half*>(a) + (size_t)m0 * lda;
     p.c = reinterpret_cast<__half*>(c) + (size_t)m0 * ldc;
     p.M = mc;
@@ -342,7 +356,7 @@ static int run_stream(const void* a, int lda, const void* bq, const void* scales
     p.tl = g_tl_buf;
     p.tl_slot = (g_tl_buf && g_tl_next < g_tl_slots) ? g_tl_next++ : -1;
 #endif
-    cudaError_t e = stream_launch(var, p, (mc + 7) / 8, smem, stream);
+    cudaError_t e = stream_launch(var, p, stream_mt(mc), smem, stream);
     if (e != cudaSuccess) { g_last_cuda_error = (int)e; return ST_CUDA; }
   }
   return ST_OK;

@@ -502,8 +502,13 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, 2) stream_kernel(const Stre
     return;
   }
   // other k chunks hold the rest: meet in the global scratch; the last chunk to arrive converts
-  for (int idx = tid; idx < ncols * MP; idx += NWARPS * 32)
-    if ((idx % MP) < p.M) atomicAdd(p.partial + (size_t)n0 * MP + idx, sAcc[idx]);
+  for (int idx = tid * 4; idx < ncols * MP; idx += NWARPS * 32 * 4)
+    if ((idx % MP) < p.M) {  // four rows of one column at a time; rows past M hold exact zeros
+      const float4 v = *reinterpret_cast<const float4*>(sAcc + idx);
+      asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p.partial + (size_t)n0 * MP + idx), "f"(v.x),
+                   "f"(v.y), "f"(v.z), "f"(v.w)
+                   : "memory");
+    }
   __syncthreads();
   int* s_last = reinterpret_cast<int*>(sAcc);  // the tile sums are no longer needed
   if (tid == 0) __threadfence();  // cumulative over the CTA's additions (ordered by the barrier above)

@@ -7,7 +7,7 @@
 // each over all of K (or one of S splits of it), with the pipelines running across tile
 // boundaries.  Warp roles:
 //
-//   * warp 13, weight producer: per 128-row group it brings the packed weights of the tile's
+//   * warp 17, weight producer: per 128-row group it brings the packed weights of the tile's
 //     128 columns (eight 16-column pieces of 256*b contiguous bytes, cp.async.bulk) and their
 //     128 fp16 scales into a 4-deep shared-memory ring;
 //   * warps 0-7 dequantize.  Thread t of warp w is lane n = 32 * (w % 4) + t of tensor
@@ -17,14 +17,15 @@
 //     multiplies by, examples/quantization/matmul_a16wx.py:316-320) and writes the 32 half2
 //     results to 32 columns of tensor memory with one tcgen05.st.  Warps 0-3 take the even
 //     64-blocks, warps 4-7 the odd ones;
-//   * warp 12, activation producer: one 2-D tiled TMA copy (128-byte swizzle) per 64-block
+//   * warp 16, activation producer: one 2-D tiled TMA copy (128-byte swizzle) per 64-block
 //     brings A[m0 : m0+TM, k : k+64] into a shared-memory ring; rows past M read as zero;
-//   * warp 14 owns tensor memory (alloc / dealloc) and issues the MMAs: per 64-block four
+//   * warp 18 owns tensor memory (alloc / dealloc) and issues the MMAs: per 64-block four
 //     tcgen05.mma.cta_group::1.kind::f16 (K = 16 each) with the weight operand in tensor
 //     memory, the activation operand through a shared-memory descriptor and the fp32
 //     accumulator D (128 lanes x TM columns) in tensor memory; tcgen05.commit releases the
 //     activation stage and the weight stage when the MMAs have read them;
-//   * warps 8-11, epilogue: when a tile's last MMA has completed they read D with
+//   * warps 8-15, epilogue (two per lane quadrant, alternate 32-column chunks): when a tile's last
+//     MMA has completed they read D with
 //     tcgen05.ld, convert to fp16 and store C[m, n] (or add into the fp32 split-K scratch),
 //     then hand D back.  Meanwhile the producers and the dequantizers are already working on
 //     the next tile, so the tensor pipe restarts as soon as D is free.
@@ -46,7 +47,7 @@
 
 namespace b200q {
 
-constexpr int UMMA_THREADS = 480;   // 8 dequant warps, 4 epilogue warps, 2 producers, MMA warp
+constexpr int UMMA_THREADS = 608;   // 8 dequant warps, 8 epilogue warps, 2 producers, MMA warp
 constexpr int UMMA_SA_MAX = 6;      // activation stages (most)
 constexpr int UMMA_SW = 8;          // weight stages in tensor memory (32 columns each)
 constexpr int UMMA_WG = 4;          // 128-row weight groups in the shared-memory ring
@@ -96,13 +97,13 @@ umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
     for (int i = 0; i < UMMA_SW; ++i) { mbar_init(BAR_ADDR(w_full, i), 4); mbar_init(BAR_ADDR(w_empty, i), 1); }
     for (int i = 0; i < UMMA_WG; ++i) { mbar_init(BAR_ADDR(g_full, i), 1); mbar_init(BAR_ADDR(g_empty, i), 8); }
     mbar_init(BAR_ADDR(d_full, 0), 1);
-    mbar_init(BAR_ADDR(d_empty, 0), 4);
+    mbar_init(BAR_ADDR(d_empty, 0), 8);
     bars->abort_flag = 0;
     bars->last_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  if (warp == 14) {
+  if (warp == 18) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      bars_s + (uint32_t)offsetof(UmmaBarriers, tmem_base)),
                  "r"(UMMA_TMEM_COLS)
@@ -193,9 +194,11 @@ umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
       TL_WRITE(warp == 0 ? 2 : 5, acc_w);
     }
 #endif
-  } else if (warp < 12) {
+  } else if (warp < 16) {
     // ================= epilogue: read D, write C (or add into the split-K scratch) =================
-    const int ew = warp - 8;  // lane quadrant of tensor memory this warp may read
+    // two warps per lane quadrant of tensor memory; they take alternate 32-column chunks of D
+    const int ew = warp & 3;            // lane quadrant this warp may read
+    const int chunk0 = (warp - 8) >> 2; // first chunk of this warp
     const int nl = ew * 32 + lane;
     const uint32_t daddr = tmem + ((uint32_t)(ew * 32) << 16);
     int tile_it = 0;
@@ -210,7 +213,12 @@ umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
       const long long t_epi = clock64();
 #endif
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      for (int c0 = 0; c0 < TM; c0 += 32) {
+      if (chunk0 * 32 >= TM) {  // nothing of this tile is this warp's (TM = 32): hand D back at once
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(BAR_ADDR(d_empty, 0));
+      }
+      for (int c0 = chunk0 * 32; c0 < TM; c0 += 64) {
         uint32_t v[32];
         asm volatile(
             "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, "
@@ -223,8 +231,8 @@ umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
             : "r"(daddr + (uint32_t)c0)
             : "memory");
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (c0 + 32 >= TM) {
-          // D is in registers: the next tile's MMAs may overwrite it
+        if (c0 + 64 >= TM) {
+          // this warp's last chunk of D is in registers: the next tile's MMAs may overwrite it
           asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
           __syncwarp();
           if (lane == 0) mbar_arrive(BAR_ADDR(d_empty, 0));
@@ -254,7 +262,7 @@ umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
       (void)nvalid;
       if (p.splits > 1) {
         // the last split to arrive converts the fp32 sums and restores the zeros
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        asm volatile("bar.sync 1, 256;" ::: "memory");
         if (warp == 8 && lane == 0) {
           __threadfence();
           const int old = atomicAdd(p.counters + n_tile * p.m_tiles + m_tile, 1);
@@ -262,9 +270,9 @@ umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
           if (last) __threadfence();
           bars->last_flag = last;
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        asm volatile("bar.sync 1, 256;" ::: "memory");
         if (bars->last_flag) {
-          for (int idx = tid - 256; idx < 64 * TM; idx += 128) {
+          for (int idx = tid - 256; idx < 64 * TM; idx += 256) {
             const int nn = n_tile * 128 + (idx & 63) * 2, m = m0 + (idx >> 6);
             if (nn < p.N && m < p.M) {
               float2* src = reinterpret_cast<float2*>(p.partial + (size_t)m * p.N + nn);
@@ -275,7 +283,7 @@ umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
           }
           if (warp == 8 && lane == 0) p.counters[n_tile * p.m_tiles + m_tile] = 0;
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");  // last_flag may be rewritten by the next tile
+        asm volatile("bar.sync 1, 256;" ::: "memory");  // last_flag may be rewritten by the next tile
       }
 #ifdef B200Q_TIMELINE
       acc_epi += clock64() - t_epi;
@@ -284,7 +292,7 @@ umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
 #ifdef B200Q_TIMELINE
     if (warp == 8 && lane == 0) { TL_WRITE(6, acc_d); TL_WRITE(7, acc_epi); }
 #endif
-  } else if (warp == 12) {
+  } else if (warp == 16) {
     // ================= TMA producer: activations =================
     if (lane == 0) {
       int ai = 0;
@@ -308,7 +316,7 @@ umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
       }
       TL_WRITE(8, acc_ae);
     }
-  } else if (warp == 13) {
+  } else if (warp == 17) {
     // ================= bulk-copy producer: packed weights and scales =================
     int g_run = 0;
     bool good = true;
@@ -414,7 +422,7 @@ umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
     p.status[2] = blockIdx.x;
     p.status[3] = 0;
   }
-  if (warp == 14) {
+  if (warp == 18) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(UMMA_TMEM_COLS) : "memory");
   }

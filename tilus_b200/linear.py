@@ -57,6 +57,7 @@ class QuantizedLinear(nn.Module):
             torch.empty(in_features // group_size, out_features, dtype=torch.float16), requires_grad=False
         )
         self.register_buffer("layout_version", torch.tensor(packing.LAYOUT_VERSION, dtype=torch.int32))
+        self._ws_need = {}  # workspace bytes per batch size M (filled on first use)
 
     # -- loading ---------------------------------------------------------------------
     def load_and_quantize(self, weight: torch.Tensor):
@@ -108,11 +109,12 @@ class QuantizedLinear(nn.Module):
 
     # -- compute ---------------------------------------------------------------------
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        lead = x.shape[:-1]
-        x2 = x.reshape(-1, self.in_features)
-        out = ops.quantized_matmul(x2, self.quantized_weight.data, self.scales.data, self.w_dtype, self.group_size,
-                                   self.zero_point)
-        return out.reshape(*lead, self.out_features)
+        x2 = x if x.dim() == 2 else x.reshape(-1, self.in_features)
+        if x2.shape[1] != self.in_features:
+            raise ValueError(f"expected {self.in_features} input features, got {x2.shape[1]}")
+        out = ops.linear_forward(x2, self.quantized_weight.data, self.scales.data, self.w_dtype.code, self.zero_point,
+                                 self.group_size, self.in_features, self.out_features, self._ws_need)
+        return out if x.dim() == 2 else out.reshape(*x.shape[:-1], self.out_features)
 
     def extra_repr(self) -> str:
         return (f"in_features={self.in_features}, out_features={self.out_features}, w_dtype={self.w_dtype.name}, "

@@ -90,6 +90,48 @@ def quantized_matmul(a: torch.Tensor, bq: torch.Tensor, scales: torch.Tensor, w_
     return out
 
 
+def linear_forward(x2: torch.Tensor, bq: torch.Tensor, scales: torch.Tensor, code: int, zero_point: int,
+                   group_size: int, K: int, N: int, ws_need: dict) -> torch.Tensor:
+    """The call QuantizedLinear.forward makes: same kernel launch as quantized_matmul, with the
+    layer's constants already validated at construction and the workspace size cached per M
+    (``ws_need``), so that a decode step spends its host time in the launch, not in checks."""
+    if not x2.is_cuda:
+        raise ValueError("QuantizedLinear needs CUDA tensors (there is no CPU path)")
+    if x2.dtype != torch.float16 or x2.stride(1) != 1:
+        raise TypeError("activations must be float16 with unit inner stride")
+    lib = _lib.load()
+    M = x2.shape[0]
+    out = torch.empty(M, N, dtype=torch.float16, device=x2.device)
+    if M == 0:
+        return out
+    dev = x2.device
+    need = ws_need.get(M)
+    if need is None:
+        need = lib.b200q_workspace_bytes(M, N, K, code, zero_point, group_size)
+        if need == 0:
+            raise _lib.B200QError(_lib.ST_UNSUPPORTED, f"no kernel for M={M} N={N} K={K}")
+        ws_need[M] = need
+    switch = torch.cuda.current_device() != dev.index
+    if switch:
+        prev = torch.cuda.current_device()
+        torch.cuda.set_device(dev)
+    try:
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        key = (dev.index, stream)
+        ws = _workspaces.get(key)
+        if ws is None or ws.numel() < need:
+            ws = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=dev)
+            _workspaces[key] = ws
+        st = lib.b200q_gemm(x2.data_ptr(), x2.stride(0), bq.data_ptr(), scales.data_ptr(), out.data_ptr(), N, M, N, K,
+                            code, zero_point, group_size, _lib.ACT_F16, ws.data_ptr(), ws.numel(), stream)
+    finally:
+        if switch:
+            torch.cuda.set_device(prev)
+    if st != 0:
+        _lib.check(st)
+    return out
+
+
 def dequantize(bq: torch.Tensor, scales: torch.Tensor, w_dtype, group_size: int, zero_point: int = 0) -> torch.Tensor:
     """W[K, N] fp16, the weights the GEMM multiplies by (bit-exact with the reference's
     cast-then-scale)."""
