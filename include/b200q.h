@@ -51,18 +51,18 @@ enum { B200Q_F16 = 0 };
  * python/tilus/lang/instantiated_script.py:700-801).  Filled by b200q_plan; may be edited
  * and passed to b200q_gemm_planned for experiments. */
 typedef struct b200q_plan {
-  int32_t kernel;        /* 0 = split-K mma.sync path (M <= 16 per pass), 1 = tcgen05 path */
-  int32_t m_tiles;       /* kernel 0: 8-row activation tiles per pass (1 or 2) */
-  int32_t splits;        /* split-K factor S */
-  int32_t cluster;       /* kernel 0: CTAs per cluster; that many of the S splits reduce in shared memory */
-  int32_t ctas_per_split;/* kernel 0: column ranges P; grid = S * P */
+  int32_t kernel;        /* 2 = mma.sync stream kernel (M <= 16 per pass), 1 = tcgen05 kernel */
+  int32_t m_tiles;       /* kernel 2: 8-row activation tiles per pass (1 or 2); kernel 1: tiles along M */
+  int32_t splits;        /* k chunks (kernel 2) / split-K factor (kernel 1) */
+  int32_t cluster;       /* 1 (no kernel launches clusters) */
+  int32_t ctas_per_split;/* kernel 2: CTAs per k chunk, grid = splits * ctas_per_split; kernel 1: output tiles */
   int32_t smem_bytes;    /* dynamic shared memory per CTA */
-  int32_t tile_m;        /* kernel 1: activation rows per CTA tile (multiple of 16, <= 256) */
-  int32_t stages;        /* pipeline depth (kernel 0: weight items in flight per warp) */
-  int32_t warps;         /* kernel 0: warps per CTA (output only) */
+  int32_t tile_m;        /* kernel 1: activation rows per CTA tile (32, 64, 128 or 256) */
+  int32_t stages;        /* pipeline depth (kernel 2: ring slots per warp; kernel 1: activation stages) */
+  int32_t warps;         /* warps per CTA (output only) */
   int32_t passes;        /* launches needed to cover M */
   int32_t pdl;           /* 1: launch with programmatic stream serialization (overlap with the previous kernel) */
-  int32_t debug;         /* 0; non-zero values switch parts of kernel 0 off for timing experiments */
+  int32_t debug;         /* 0; non-zero values switch parts of the kernels off for timing experiments */
   uint64_t workspace_bytes;
 } b200q_plan_t;
 
@@ -120,6 +120,15 @@ size_t b200q_static_workspace_limit(void);
  * python/tilus/kernels/cast.py:27-55). */
 int b200q_dequantize(const void* bq, const void* scales, void* w, int N, int K, int wtype, int zero_point, int group,
                      void* stream);
+
+/* QuantizedLinear.load_and_quantize on the GPU (examples/quantization/matmul_a16wx.py:470-528):
+ * weight [N, K] (row = output feature; weight_dtype 0 = fp16, 1 = fp32; row stride ldw elements) ->
+ * scales fp16 [K/group, N] = max(absmax / max_value, 1e-6) per (group, column) and the packed
+ * weights bq (b200 layout, K*N*nbits/8 bytes): q = clamp(w / scale, min, max), integers rounded
+ * half to even, floats encoded as python/tilus/hidet/ir/primitives/cuda/cast.py:44-100.  The
+ * reference does this with PyTorch ops followed by its change-layout kernel (:520-525). */
+int b200q_quantize(const void* weight, int weight_dtype, int ldw, void* bq, void* scales, int N, int K, int wtype,
+                   int group, void* stream);
 
 /* Reads the device status header of a workspace (synchronises `stream`): status[0] is 0 or
  * B200Q_ERR_DEVICE_TIMEOUT, status[1..3] say which wait gave up.  Clears the header. */

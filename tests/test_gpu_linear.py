@@ -69,3 +69,24 @@ def test_state_dict_round_trip():
     other.load_state_dict(sd)
     x = torch.randn(2, k, dtype=torch.float16, device="cuda")
     assert torch.equal(layer(x), other(x))
+
+
+@pytest.mark.parametrize("dt", [D.int4b, D.int5b, D.int2b, D.float6_e2m3, D.float5_e2m2, D.float8_e5m2, D.uint4b],
+                         ids=lambda d: d.name)
+@pytest.mark.parametrize("group,wdtype", [(32, torch.float32), (128, torch.float16), (512, torch.float32)])
+def test_gpu_quantize_and_pack_bit_exact(dt, group, wdtype):
+    """b200q_quantize (absmax scales, clamp, round / float encode, packing in one library call)
+    against the oracle's load_and_quantize arithmetic and the host re-packer, bit for bit."""
+    from tilus_b200 import quantize
+
+    torch.manual_seed(3)
+    k, n = 1024, 64
+    w = (torch.randn(n, k) * 0.3).to(wdtype)
+    w[0, :group] = 0  # an all-zero group: the scale floor 1e-6
+    w[1, 5] = 1e4     # an outlier: saturation of everything else to tiny codes
+    packed, scales = quantize.quantize_and_pack(w.cuda(), dt, group)
+    torch.cuda.synchronize()
+    codes_ref, scales_ref = qo.quantize_weight(w.float().numpy(), dt, group)
+    np.testing.assert_array_equal(scales.cpu().numpy().view(np.uint16), scales_ref.view(np.uint16))
+    want = packing.interleave(torch.from_numpy(codes_ref), dt)
+    assert torch.equal(packed.cpu(), want)

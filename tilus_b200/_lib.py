@@ -57,6 +57,7 @@ SYMBOLS = {
     "b200q_gemm_static_ws": (_i, [_vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "b200q_static_workspace_limit": (_sz, []),
     "b200q_dequantize": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "b200q_quantize": (_i, [_vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _vp]),
     "b200q_device_status": (_i, [_vp, ctypes.POINTER(ctypes.c_int32 * 4), _vp]),
 }
 

@@ -1,5 +1,6 @@
 // C ABI of libb200q (declared in include/b200q.h): argument validation, the static
 // shape -> tile table, and kernel dispatch.  No torch types, no allocation.
+#include <cmath>
 #include <cstdio>
 #include <cstring>
 #include <mutex>
@@ -20,6 +21,8 @@ namespace b200q {
 B200Q_DECL_SPART(0) B200Q_DECL_SPART(1) B200Q_DECL_SPART(2) B200Q_DECL_SPART(3)
 B200Q_DECL_SPART(4) B200Q_DECL_SPART(5) B200Q_DECL_SPART(6) B200Q_DECL_SPART(7)
 cudaError_t dequant_launch(int var, const DequantParams& p, cudaStream_t stream);
+cudaError_t quantize_launch(const void* w, int w_is_f32, int ldw, void* bq, void* scales, int N, int K, int group,
+                            int kind, int nbits, int ebits, int mbits, float minv, float maxv, cudaStream_t stream);
 #define B200Q_DECL_UPART(i) \
   cudaError_t umma_launch_part##i(int, const UmmaParams&, const void*, int, cudaStream_t);
 B200Q_DECL_UPART(0) B200Q_DECL_UPART(1) B200Q_DECL_UPART(2) B200Q_DECL_UPART(3)
@@ -502,6 +505,30 @@ int b200q_dequantize(const void* bq, const void* scales, void* w, int N, int K, 
   p.N = N; p.K = K; p.group = group; p.KB = K / BLOCK_K; p.NT = N / BLOCK_N;
   cudaError_t e = dequant_launch(var, p, reinterpret_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) { g_last_cuda_error = (int)e; return ST_CUDA; }
+  return ST_OK;
+}
+
+int b200q_quantize(const void* weight, int weight_dtype, int ldw, void* bq, void* scales, int N, int K, int wtype,
+                   int group, void* stream) {
+  if (!weight || !bq || !scales) return ST_INVALID_ARG;
+  if (N < 1 || K < 1 || group < 1 || ldw < K) return ST_INVALID_ARG;
+  if (weight_dtype != 0 && weight_dtype != 1) return ST_UNSUPPORTED;
+  const int kind = (wtype >> 16) & 0xff, nbits = (wtype >> 8) & 0xff, e = (wtype >> 4) & 0xf, m = wtype & 0xf;
+  if (kind > 2 || nbits < 1 || nbits > 8) return ST_UNSUPPORTED;
+  if (kind == 2 && (nbits != 1 + e + m || e < 1 || m < 1)) return ST_UNSUPPORTED;
+  if (K % BLOCK_K != 0 || N % BLOCK_N != 0 || group % 32 != 0 || K % group != 0) return ST_UNSUPPORTED;
+  if (((uintptr_t)bq & 15) || ((uintptr_t)scales & 1) || ((uintptr_t)weight & 3)) return ST_INVALID_ARG;
+  float minv, maxv;
+  if (kind == 0) { minv = 0.f; maxv = (float)((1 << nbits) - 1); }
+  else if (kind == 1) { minv = -(float)(1 << (nbits - 1)); maxv = (float)((1 << (nbits - 1)) - 1); }
+  else {
+    const int bias = (1 << (e - 1)) - 1, top = (1 << e) - 1 - (e == 5 ? 1 : 0);
+    maxv = ldexpf(2.0f - ldexpf(1.0f, -m), top - bias);
+    minv = -maxv;
+  }
+  cudaError_t err = quantize_launch(weight, weight_dtype, ldw, bq, scales, N, K, group, kind, nbits, e, m, minv, maxv,
+                                    reinterpret_cast<cudaStream_t>(stream));
+  if (err != cudaSuccess) { g_last_cuda_error = (int)err; return ST_CUDA; }
   return ST_OK;
 }
 

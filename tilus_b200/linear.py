@@ -67,6 +67,10 @@ class QuantizedLinear(nn.Module):
             raise ValueError("load_and_quantize is symmetric: use a signed or float weight type "
                              "(unsigned codes come in through load_codes / load_packed)")
         dev = self.quantized_weight.device
+        if dev.type == "cuda":  # one fused pass on the GPU: scales, codes, packing
+            packed, scales = quantize.quantize_and_pack(weight.to(dev), self.w_dtype, self.group_size)
+            self.load_packed(packed, scales, layout="b200")
+            return
         codes, scales = quantize.quantize_weight(weight.to(dev), self.w_dtype, self.group_size)
         self.load_codes(codes, scales)
 

@@ -1,4 +1,4 @@
-"""Weight quantization on the host (PyTorch): the arithmetic of
+"""Weight quantization: on the GPU through the library (quantize_and_pack), and on the host (PyTorch): the arithmetic of
 QuantizedLinear.load_and_quantize (examples/quantization/matmul_a16wx.py:470-528 of the
 reference) - per-group absmax scales, clamp, round - producing integer codes.
 
@@ -65,3 +65,26 @@ def quantize_weight(weight: torch.Tensor, w_dtype, group_size: int):
     else:
         codes = (torch.round(q).to(torch.int64) & ((1 << dt.nbits) - 1)).to(torch.uint8)
     return codes.view(in_f, out_f), scales.view(in_f // group_size, out_f)
+
+
+def quantize_and_pack(weight: torch.Tensor, w_dtype, group_size: int):
+    """weight[out, in] on a CUDA device (fp16 or fp32) -> (packed b200 bytes uint8[K*N*b/8],
+    scales fp16[K/group, N]) in one library call (two kernels): the same arithmetic as
+    quantize_weight followed by packing.interleave, bit for bit."""
+    from . import _lib
+
+    dt = weight_dtype(w_dtype)
+    if not weight.is_cuda:
+        raise ValueError("quantize_and_pack needs a CUDA tensor (use quantize_weight + packing.interleave on the host)")
+    if weight.dtype not in (torch.float16, torch.float32):
+        weight = weight.float()
+    weight = weight.contiguous()
+    out_f, in_f = weight.shape
+    bq = torch.empty(in_f * out_f * dt.nbits // 8, dtype=torch.uint8, device=weight.device)
+    scales = torch.empty(in_f // group_size, out_f, dtype=torch.float16, device=weight.device)
+    with torch.cuda.device(weight.device):
+        st = _lib.load().b200q_quantize(weight.data_ptr(), 1 if weight.dtype == torch.float32 else 0, in_f,
+                                        bq.data_ptr(), scales.data_ptr(), out_f, in_f, dt.code, group_size,
+                                        torch.cuda.current_stream(weight.device).cuda_stream)
+    _lib.check(st)
+    return bq, scales
