@@ -314,27 +314,43 @@ def run_stack(args) -> None:
             x = down(h[:, :14336])
         return x
 
+    # --fused: the all-gather is done by the GEMV kernel itself (stores into every rank's row buffer
+    # over NVLink, flags instead of a collective); covers M <= 16, wider batches use the NCCL path
+    ctx = sharded.PeerGather.create(16, 28672, dev) if args.fused else None
+
+    def step_fused(x):
+        row = x
+        for qkv, o, gate_up, down in layers:
+            row = ctx.gemm(row, qkv)
+            row = ctx.gemm(row.cols(0, 4096), o)
+            row = ctx.gemm(row, gate_up)
+            row = ctx.gemm(row.cols(0, 14336), down)
+        return row
+
     results = {}
     graphs = []
     for m in (1, 8, 32, 64):
         x = (torch.randn(m, 4096, generator=torch.Generator().manual_seed(m)) * 0.05).to(torch.float16).to(dev)
+        fn = step_fused if (ctx is not None and m <= 16) else step
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
             for _ in range(2):
-                step(x)
+                fn(x)
         torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
         mode = "cuda graph"
         try:
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, stream=side):
-                out = step(x)  # noqa: F841
+                out = fn(x)  # noqa: F841
             run = g.replay
             graphs.append(g)
         except Exception:  # collectives that cannot be captured: launch eagerly
             torch.cuda.synchronize()
             mode = "eager"
-            run = lambda: step(x)  # noqa: E731
+            run = lambda: fn(x)  # noqa: E731
         for _ in range(max(args.warmup, 3)):
             run()
         if world > 1:
@@ -352,7 +368,8 @@ def run_stack(args) -> None:
         ms = float(t.item())
         results[f"M{m}"] = {"ms_per_step": round(ms, 4), "tokens_per_s": round(m / (ms * 1e-3), 1),
                             "us_per_linear": round(ms * 1e3 / (4 * n_layers), 2),
-                            "per_gpu_weight_gbs": round(weight_bytes / (ms * 1e-3) / 1e9, 1), "launch": mode}
+                            "per_gpu_weight_gbs": round(weight_bytes / (ms * 1e-3) / 1e9, 1), "launch": mode,
+                            "gather": "fused in the GEMV kernel" if fn is step_fused else ("nccl all-gather" if world > 1 else "none")}
     if rank == 0:
         print(json.dumps({"metric": "Llama-3-8B-shaped decode linear stack, N-sharded, all-gather per layer",
                           "unit": "ms per 128-linear step", "n_gpus": world, "steps": args.steps,
@@ -536,6 +553,8 @@ def main():
     ap.add_argument("--no-prefill", action="store_true", help="skip the M=4096 prefill entry of the sweep")
     ap.add_argument("--stack", action="store_true",
                     help="time the N-sharded Llama-3-8B-shaped decode linear stack (all-gather per layer) instead")
+    ap.add_argument("--fused", action="store_true",
+                    help="with --stack: all-gather fused into the GEMV kernel (peer stores + flags) for M <= 16")
     ap.add_argument("--profile-case", default=None, choices=["decode", "batch16", "prefill"],
                     help="run a few plain launches of one kernel (for ncu) instead of the benchmark")
     args = ap.parse_args()

@@ -115,6 +115,51 @@ int b200q_gemm_static_ws(const void* a, int lda, const void* bq, const void* sca
                          int K, int wtype, int zero_point, int group, int act_dtype, void* stream);
 size_t b200q_static_workspace_limit(void);
 
+/* ---- column-sharded GEMV with the all-gather fused into the kernel -------------------------------
+ * The reference is single-GPU (no collective anywhere in its tree), so these have no counterpart
+ * there; they serve the N-sharded decode stack: rank r holds columns [col_offset, col_offset + N)
+ * of a layer and every rank needs the full output row as the next layer's activations.
+ *
+ * b200q_gemm_gather computes this rank's columns like b200q_gemm (M <= 16) and stores them straight
+ * into the full output row [M, ldc] of every rank (peer-mapped device pointers; stores only, no
+ * loads from peers), then raises this rank's flag on every rank.  Every rank owns two row
+ * buffers used alternately (`out[g]` = buffer 0 of rank g, buffer 1 is `buffer_elems` elements
+ * further), `world` 32-bit flags and a call counter `epoch_local`, all zero at the start.  A
+ * launch is fused call number E + 1 of its rank, with E read from `epoch_local` on the device:
+ * it waits - bounded, 0.25 s, else B200Q_ERR_DEVICE_TIMEOUT in the status word - until all
+ * `world` slots of `flags_local` have reached E (every rank has finished call E, so the
+ * activations are complete and nobody still reads the buffer about to be overwritten), writes
+ * buffer (E + 1) % 2 of every rank, sets `flag_slot[g]` (= this rank's slot in rank g's flags) to
+ * E + 1 and stores E + 1 to `epoch_local`.  With `a_prev_offset >= 0` the activations are this
+ * rank's previous gathered output (buffer E % 2, from that element on, row stride lda) and `a`
+ * is ignored.  No per-call state is passed from the host, so the same call sequence can be
+ * captured once and replayed from a CUDA graph.  All ranks must make the same sequence of calls.
+ * Word 8 of the workspace header counts the CTAs of the launch. */
+typedef struct b200q_gather {
+  int32_t world, rank;
+  int32_t ldc;            /* elements per full output row */
+  int32_t col_offset;     /* first column of this rank's shard */
+  void* out[8];           /* row buffer 0 of every rank, fp16 [M, ldc] */
+  void* flag_slot[8];     /* this rank's slot in every rank's flag array */
+  const void* flags_local;/* this rank's flag array, uint32[world] */
+  void* epoch_local;      /* this rank's call counter, uint32 */
+  int64_t buffer_elems;   /* elements between a rank's two row buffers */
+  int64_t a_prev_offset;  /* >= 0: activations = this rank's previous gathered output from this element on */
+} b200q_gather_t;
+
+int b200q_gemm_gather(const void* a, int lda, const void* bq, const void* scales, int M, int N, int K, int wtype,
+                      int zero_point, int group, int act_dtype, void* workspace, size_t workspace_bytes, void* stream,
+                      const b200q_gather_t* gather);
+
+/* Device memory that other processes of the node can map (cudaMalloc + CUDA IPC): allocate,
+ * export a 64-byte handle, open a peer's handle (enables peer access), close, free.  These five
+ * are the only functions of the library that allocate or free device memory. */
+int b200q_peer_alloc(size_t bytes, void** ptr);
+int b200q_peer_export(void* ptr, unsigned char handle[64]);
+int b200q_peer_open(const unsigned char handle[64], void** ptr);
+int b200q_peer_close(void* ptr);
+int b200q_peer_free(void* ptr);
+
 /* W[K, N] (fp16, row-major) = dequantized weights, bit-exact with the reference's
  * cast-then-scale (examples/quantization/matmul_a16wx.py:316-320; cast kernel
  * python/tilus/kernels/cast.py:27-55). */

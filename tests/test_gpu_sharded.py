@@ -1,0 +1,106 @@
+"""Column-sharded layers with the all-gather fused into the GEMV kernel (b200q_gemm_gather).
+
+One GPU is enough: the ranks of a two-rank group are played one after the other on one stream, with
+both ranks' row buffers and flags in this process's memory, so the kernel's addressing (column
+offsets, every rank's buffer, buffer alternation) and its flag protocol (wait for the previous
+epoch, raise the own slot everywhere) run exactly as they do across GPUs - only the transport
+(peer-mapped pointers over NVLink) is not exercised here."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import quant_oracle as qo
+from tilus_b200 import float16, sharded, synth
+from tilus_b200 import dtypes as D
+
+pytestmark = pytest.mark.gpu
+
+
+def _virtual_group(world, max_rows, max_cols, dev):
+    regions = [torch.zeros(sharded.PeerGather.region_bytes(max_rows, max_cols), dtype=torch.uint8, device=dev)
+               for _ in range(world)]
+    ptrs = [r.data_ptr() for r in regions]
+    return regions, [sharded.PeerGather(world, r, ptrs, max_rows, max_cols, dev) for r in range(world)]
+
+
+@pytest.mark.parametrize("M", [1, 5, 16])
+@pytest.mark.parametrize("world", [2, 4])
+def test_fused_gather_chain_matches_unsharded(M, world):
+    dev = torch.device("cuda:0")
+    dt, g = D.uint4b, 128
+    dims = [(1024, 2048), (2048, 1024), (1024, 512)]  # a chain of three layers
+    probs = [synth.make_problem(M, n, k, dt, g, seed=10 + i) for i, (k, n) in enumerate(dims)]
+    regions, ctxs = _virtual_group(world, 16, 2048, dev)
+    shards = []
+    for (k, n), prob in zip(dims, probs):
+        per_rank = []
+        for r in range(world):
+            lin = sharded.ShardedQuantizedLinear(float16, dt, g, k, n, zero_point=prob["zero_point"],
+                                                 shard=(world, r)).to(dev)
+            lin.load_codes(prob["codes"], prob["scales"])
+            per_rank.append(lin)
+        shards.append(per_rank)
+    x0 = (probs[0]["a"] * 0.25).to(torch.float16).to(dev)
+    xs = [x0 for _ in range(world)]
+    for per_rank in shards:  # one fused call per layer; the ranks take their turns on one stream
+        xs = [ctxs[r].gemm(xs[r], per_rank[r]) for r in range(world)]
+    outs = [ctxs[r].fetch(xs[r]) for r in range(world)]
+    # reference: the same chain through the oracle, fp16 between layers
+    ref = x0.cpu().numpy()
+    for (k, n), prob in zip(dims, probs):
+        ref = qo.quantized_matmul(ref, prob["codes"].numpy(), prob["scales"].numpy(), dt, g, prob["zero_point"])
+    for r in range(world):
+        got = outs[r].float().cpu().numpy()
+        assert got.shape == (M, dims[-1][1])
+        err = np.abs(got - ref.astype(np.float32)).max() / np.abs(ref.astype(np.float32)).max()
+        assert err <= 2e-2, (r, err)  # three layers deep: tolerance of the single GEMM, doubled
+    # every rank saw every rank finish the last call, and counted its own calls
+    for r in range(world):
+        flags = regions[r][: 4 * world].view(torch.int32).cpu().numpy()
+        assert (flags == len(dims)).all()
+        assert ctxs[r].calls_completed() == len(dims)
+
+
+def test_fused_gather_replays_from_a_cuda_graph():
+    """The calls carry no per-call state: a captured chain can be replayed and keeps counting."""
+    dev = torch.device("cuda:0")
+    dt, g, M, world = D.int4b, 128, 2, 2
+    prob = synth.make_problem(M, 1024, 1024, dt, g, seed=3)
+    regions, ctxs = _virtual_group(world, 16, 1024, dev)
+    lins = []
+    for r in range(world):
+        lin = sharded.ShardedQuantizedLinear(float16, dt, g, 1024, 1024, shard=(world, r)).to(dev)
+        lin.load_codes(prob["codes"], prob["scales"])
+        lins.append(lin)
+    x = (prob["a"] * 0.25).to(torch.float16).to(dev)
+
+    def chain():
+        rows = [ctxs[r].gemm(x, lins[r]) for r in range(world)]          # call 1: external activations
+        return [ctxs[r].gemm(rows[r], lins[r]) for r in range(world)]     # call 2: previous output
+
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        rows = chain()  # warm-up (sets kernel attributes, allocates the workspace)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            rows = chain()
+        for _ in range(3):
+            graph.replay()
+        want1 = qo.quantized_matmul(x.cpu().numpy(), prob["codes"].numpy(), prob["scales"].numpy(), dt, g, 0)
+        want2 = qo.quantized_matmul(want1, prob["codes"].numpy(), prob["scales"].numpy(), dt, g, 0)
+        for r in range(world):
+            assert ctxs[r].calls_completed() == 2 + 3 * 2
+            got = ctxs[r].fetch(rows[r]).float().cpu().numpy()
+            err = np.abs(got - want2.astype(np.float32)).max() / np.abs(want2.astype(np.float32)).max()
+            assert err <= 2e-2
+
+
+def test_fused_gather_rejects_wide_batches():
+    dev = torch.device("cuda:0")
+    regions, ctxs = _virtual_group(2, 16, 512, dev)
+    lin = sharded.ShardedQuantizedLinear(float16, D.int4b, 128, 512, 512, shard=(2, 0)).to(dev)
+    prob = synth.make_problem(1, 512, 512, D.int4b, 128, seed=1)
+    lin.load_codes(prob["codes"], prob["scales"])
+    with pytest.raises(ValueError):
+        ctxs[0].gemm(torch.zeros(17, 512, dtype=torch.float16, device=dev), lin)

@@ -21,6 +21,22 @@ class B200QError(RuntimeError):
         self.status = status
 
 
+class Gather(ctypes.Structure):
+    """b200q_gather_t of include/b200q.h."""
+    _fields_ = [
+        ("world", ctypes.c_int32),
+        ("rank", ctypes.c_int32),
+        ("ldc", ctypes.c_int32),
+        ("col_offset", ctypes.c_int32),
+        ("out", ctypes.c_void_p * 8),
+        ("flag_slot", ctypes.c_void_p * 8),
+        ("flags_local", ctypes.c_void_p),
+        ("epoch_local", ctypes.c_void_p),
+        ("buffer_elems", ctypes.c_int64),
+        ("a_prev_offset", ctypes.c_int64),
+    ]
+
+
 class Plan(ctypes.Structure):
     _fields_ = [
         ("kernel", ctypes.c_int32),
@@ -57,6 +73,12 @@ SYMBOLS = {
     "b200q_gemm_static_ws": (_i, [_vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "b200q_static_workspace_limit": (_sz, []),
     "b200q_dequantize": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "b200q_gemm_gather": (_i, [_vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp, ctypes.POINTER(Gather)]),
+    "b200q_peer_alloc": (_i, [_sz, ctypes.POINTER(ctypes.c_void_p)]),
+    "b200q_peer_export": (_i, [_vp, ctypes.c_char_p]),
+    "b200q_peer_open": (_i, [ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p)]),
+    "b200q_peer_close": (_i, [_vp]),
+    "b200q_peer_free": (_i, [_vp]),
     "b200q_quantize": (_i, [_vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _vp]),
     "b200q_device_status": (_i, [_vp, ctypes.POINTER(ctypes.c_int32 * 4), _vp]),
 }

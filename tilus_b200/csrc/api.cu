@@ -322,7 +322,7 @@ static int run_umma(const void* a, int lda, const void* bq, const void* scales, 
 
 static int run_stream(const void* a, int lda, const void* bq, const void* scales, void* c, int ldc, int M, int N,
                       int K, int var, int group, void* workspace, size_t ws_bytes, cudaStream_t stream,
-                      const b200q_plan_t& pl) {
+                      const b200q_plan_t& pl, const b200q_gather_t* gather = nullptr) {
   const int bits = var_bits(var);
   const int KB = K / BLOCK_K;
   if (pl.splits < 1 || KB % pl.splits != 0 || pl.ctas_per_split < 1) return ST_INVALID_ARG;
@@ -346,6 +346,28 @@ static int run_stream(const void* a, int lda, const void* bq, const void* scales
   p.pdl = pl.pdl;
   p.tl = nullptr;
   p.tl_slot = -1;
+  std::memset(&p.ga, 0, sizeof(p.ga));
+  if (gather) {
+    if (M > 16 || gather->world < 1 || gather->world > 8 || gather->rank < 0 || gather->rank >= gather->world)
+      return ST_INVALID_ARG;
+    if (gather->ldc < gather->col_offset + N || gather->col_offset < 0 || !gather->flags_local ||
+        !gather->epoch_local || gather->buffer_elems < (int64_t)M * gather->ldc)
+      return ST_INVALID_ARG;
+    p.ga.G = gather->world;
+    p.ga.rank = gather->rank;
+    p.ga.col_off = gather->col_offset;
+    for (int g = 0; g < gather->world; ++g) {
+      if (!gather->out[g] || !gather->flag_slot[g]) return ST_INVALID_ARG;
+      p.ga.out[g] = reinterpret_cast<__half*>(gather->out[g]);
+      p.ga.flag_slot[g] = reinterpret_cast<unsigned*>(gather->flag_slot[g]);
+    }
+    p.ga.flags = reinterpret_cast<const unsigned*>(gather->flags_local);
+    p.ga.epoch = reinterpret_cast<unsigned*>(gather->epoch_local);
+    p.ga.buf_elems = gather->buffer_elems;
+    p.ga.a_prev_off = gather->a_prev_offset;
+    p.ga.done = reinterpret_cast<unsigned*>(workspace) + 8;  // word 8 of the status header
+    p.ldc = gather->ldc;
+  }
   const int rows = stream_rows_per_pass(M);
   for (int m0 = 0; m0 < M; m0 += rows) {
     const int mc = (M - m0) < rows ? (M - m0) : rows;
@@ -426,6 +448,64 @@ int b200q_gemm_planned(const void* a, int lda, const void* bq, const void* scale
   if (st != ST_OK) return st;
   return run_gemm(a, lda, bq, scales, c, ldc, M, N, K, var, group, workspace, workspace_bytes,
                   reinterpret_cast<cudaStream_t>(stream), *plan);
+}
+
+int b200q_gemm_gather(const void* a, int lda, const void* bq, const void* scales, int M, int N, int K, int wtype,
+                      int zero_point, int group, int act_dtype, void* workspace, size_t workspace_bytes, void* stream,
+                      const b200q_gather_t* gather) {
+  if (act_dtype != B200Q_F16) return ST_UNSUPPORTED;
+  if (!gather || !bq || !scales) return ST_INVALID_ARG;
+  if (M > 16) return ST_UNSUPPORTED;  // the tcgen05 kernel has no fused gather: use b200q_gemm + a collective
+  if (gather->a_prev_offset < 0 && (!a || ((uintptr_t)a & 15))) return ST_INVALID_ARG;
+  if (gather->a_prev_offset >= 0 && (gather->a_prev_offset % 8) != 0) return ST_INVALID_ARG;
+  if (((uintptr_t)bq) & 15) return ST_INVALID_ARG;
+  if (lda < K || (lda % 8) != 0) return ST_INVALID_ARG;
+  int var;
+  int st = check_problem(M, N, K, wtype, zero_point, group, 128, &var);
+  if (st != ST_OK) return st;
+  b200q_plan_t pl;
+  st = make_plan(M, N, K, var, &pl);
+  if (st != ST_OK) return st;
+  if (pl.kernel != 2) return ST_UNSUPPORTED;
+  return run_stream(a, lda, bq, scales, nullptr, gather->ldc, M, N, K, var, group, workspace, workspace_bytes,
+                    reinterpret_cast<cudaStream_t>(stream), pl, gather);
+}
+
+int b200q_peer_alloc(size_t bytes, void** ptr) {
+  if (!ptr || bytes == 0) return ST_INVALID_ARG;
+  cudaError_t e = cudaMalloc(ptr, bytes);
+  if (e == cudaSuccess) e = cudaMemset(*ptr, 0, bytes);
+  if (e != cudaSuccess) { g_last_cuda_error = (int)e; return ST_CUDA; }
+  return ST_OK;
+}
+int b200q_peer_export(void* ptr, unsigned char handle[64]) {
+  if (!ptr || !handle) return ST_INVALID_ARG;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, ptr);
+  if (e != cudaSuccess) { g_last_cuda_error = (int)e; return ST_CUDA; }
+  std::memcpy(handle, &h, 64);
+  return ST_OK;
+}
+int b200q_peer_open(const unsigned char handle[64], void** ptr) {
+  if (!ptr || !handle) return ST_INVALID_ARG;
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle, 64);
+  cudaError_t e = cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) { g_last_cuda_error = (int)e; return ST_CUDA; }
+  return ST_OK;
+}
+int b200q_peer_close(void* ptr) {
+  if (!ptr) return ST_INVALID_ARG;
+  cudaError_t e = cudaIpcCloseMemHandle(ptr);
+  if (e != cudaSuccess) { g_last_cuda_error = (int)e; return ST_CUDA; }
+  return ST_OK;
+}
+int b200q_peer_free(void* ptr) {
+  if (!ptr) return ST_INVALID_ARG;
+  cudaError_t e = cudaFree(ptr);
+  if (e != cudaSuccess) { g_last_cuda_error = (int)e; return ST_CUDA; }
+  return ST_OK;
 }
 
 int b200q_gemm(const void* a, int lda, const void* bq, const void* scales, void* c, int ldc, int M, int N, int K,

@@ -37,6 +37,22 @@ constexpr int STREAM_WARPS = 16;
 constexpr int STREAM_SC_GROUPS = 16;  // groups per warp in the shared-memory scale cache (32 bytes each)
 // 128-row groups per ring item: items of 1..2 KB for every bit width
 constexpr int stream_gi(int bits) { return bits <= 2 ? 4 : bits <= 5 ? 2 : 1; }
+// Fused all-gather of a column-sharded GEMV (G == 0: none).  Every rank's launch stores its
+// columns into the full output row of every rank and then raises its flag on every rank; the
+// next launch waits for all flags before it reads its activations.  The call counter lives on
+// the device (`epoch`), so a launch carries no per-call state and can be replayed from a graph.
+struct GatherArgs {
+  int G, rank;             // ranks, this rank
+  int col_off;             // first column of this rank's shard in the full row
+  __half* out[8];          // row buffer 0 of every rank (peer-mapped); buffer 1 is buf_elems further
+  unsigned* flag_slot[8];  // this rank's slot in every rank's flag array (peer-mapped)
+  const unsigned* flags;   // this rank's own flag array [G]
+  unsigned* epoch;         // this rank's count of completed fused calls
+  unsigned* done;          // arrival counter of this launch's CTAs (zero on entry, zero on exit)
+  long long buf_elems;     // elements between a rank's two row buffers
+  long long a_prev_off;    // >= 0: the activations are this rank's previous gathered output, from this element on
+};
+
 struct StreamParams {
   const __half* a;       // [M, K] row-major, leading dimension lda
   const void* bq;        // b200 layout
@@ -57,6 +73,7 @@ struct StreamParams {
   int pdl;               // launch with programmatic stream serialization
   unsigned long long* tl;  // timeline experiments (side builds with B200Q_TIMELINE only), else null
   int tl_slot;
+  GatherArgs ga;
 };
 
 // ---- tcgen05 kernel (any M; used for M > 16) ---------------------------------------------------

@@ -95,6 +95,19 @@ __device__ __forceinline__ void ld_unit_words(const unsigned char* ptr, uint32_t
     for (int q = 0; q < B; ++q) w[q] = reinterpret_cast<const uint32_t*>(ptr)[q];
   }
 }
+// One output value.  Plain launches write C; launches with a fused all-gather write the value
+// into the full output row of every rank (peer-mapped pointers, stores only).
+template <bool GATHER>
+__device__ __forceinline__ void store_out(const StreamParams& p, size_t gather_buf, int m, int n, float v) {
+  const __half h = __float2half_rn(v);
+  if constexpr (!GATHER) {
+    p.c[(size_t)m * p.ldc + n] = h;
+  } else {
+    const size_t off = gather_buf + (size_t)m * p.ldc + p.ga.col_off + n;
+    for (int g = 0; g < p.ga.G; ++g) p.ga.out[g][off] = h;
+  }
+}
+
 // one non-blocking look at an mbarrier phase
 __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
   uint32_t ok;
@@ -114,7 +127,7 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
 //   then         scale caches [warp][STREAM_SC_GROUPS][16] halfs: the scales of the warp's next groups
 //   then         tile sums of the CTA's own column tiles [T_own][16 columns][8*MT rows] floats
 //   then         activation chunk [M][pitch] halfs, then group sums [groups][8*MT] floats
-template <int VAR, int MT>
+template <int VAR, int MT, bool GATHER>
 __global__ void __launch_bounds__(STREAM_WARPS * 32, 2) stream_kernel(const StreamParams p) {
   constexpr int B = var_bits(VAR);
   constexpr int MP = 8 * MT;
@@ -231,6 +244,41 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, 2) stream_kernel(const Stre
   asm volatile("griddepcontrol.wait;" ::: "memory");
   TL_STAMP(2);
 
+  // ---- fused all-gather: this launch is fused call number E + 1 of the rank (E is kept on the
+  // device, so that the same launch can be replayed from a CUDA graph).  It may start once every
+  // rank has finished call E: then the activations - if they are call E's gathered output - are
+  // complete and nobody still reads the row buffer this call overwrites (bounded wait on this
+  // rank's flags, one thread per source rank). ----
+  const __half* a_base = p.a;
+  size_t gather_buf = 0;  // element offset of the row buffer this call writes, inside every rank's region
+  unsigned epoch = 0;
+  if (GATHER) {
+    epoch = *reinterpret_cast<volatile const unsigned*>(p.ga.epoch);
+    gather_buf = ((epoch + 1) & 1u) ? p.ga.buf_elems : 0;
+    if (p.ga.a_prev_off >= 0) a_base = p.ga.out[p.ga.rank] + ((epoch & 1u) ? p.ga.buf_elems : 0) + p.ga.a_prev_off;
+    if (epoch != 0) {
+      if (tid < p.ga.G) {
+        uint64_t t0 = 0;
+        for (int spin = 0;; ++spin) {
+          unsigned v;
+          asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.ga.flags + tid) : "memory");
+          if ((int)(v - epoch) >= 0) break;
+          uint64_t now;
+          asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+          if (spin == 0) t0 = now;
+          else if (now - t0 > 250000000ull) {  // give up: report, carry on with what is there
+            atomicExch(p.status, ST_DEVICE_TIMEOUT);
+            p.status[1] = 5;  // where: wait for a peer's columns
+            p.status[2] = blockIdx.x;
+            p.status[3] = tid;
+            break;
+          }
+        }
+      }
+      __syncthreads();
+    }
+  }
+
   // ---- stage the activation chunk A[0:M, kb_base*512 : +KBc*512], pre-scaled ----
   if (p.debug_skip < 3) {
     const int kc = p.KBc * 512;
@@ -256,7 +304,8 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, 2) stream_kernel(const Stre
       while (vv >= vec_per_row) { vv -= vec_per_row; ++m; }
       const int kk = vv * 8;
       vv += NWARPS * 32;
-      uint4 v = __ldg(reinterpret_cast<const uint4*>(p.a + (size_t)m * p.lda + (size_t)kb_base * 512 + kk));
+      uint4 v = GATHER ? *reinterpret_cast<const uint4*>(a_base + (size_t)m * p.lda + (size_t)kb_base * 512 + kk)
+                       : __ldg(reinterpret_cast<const uint4*>(a_base + (size_t)m * p.lda + (size_t)kb_base * 512 + kk));
       __half2 x0 = h2_from_bits(v.x), x1 = h2_from_bits(v.y), x2 = h2_from_bits(v.z), x3 = h2_from_bits(v.w);
       if constexpr (BIAS != 0) {
         const float2 f0 = __half22float2(x0), f1 = __half22float2(x1), f2 = __half22float2(x2),
@@ -462,8 +511,8 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, 2) stream_kernel(const Stre
                 const float2 v = __ldcg(src);
                 __stcg(src, make_float2(0.f, 0.f));
                 const int n = cur_tile * 16 + r + h * 8;
-                p.c[(size_t)m0 * p.ldc + n] = __float2half_rn(v.x);
-                if (m0 + 1 < p.M) p.c[(size_t)(m0 + 1) * p.ldc + n] = __float2half_rn(v.y);
+                store_out<GATHER>(p, gather_buf, m0, n, v.x);
+                if (m0 + 1 < p.M) store_out<GATHER>(p, gather_buf, m0 + 1, n, v.y);
               }
             }
           }
@@ -493,48 +542,67 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, 2) stream_kernel(const Stre
   }
 
   // ---- the CTA's own tiles ----
-  if (p.T_own == 0) return;
-  __syncthreads();
-  const int n0 = own_tile0 * 16, ncols = p.T_own * 16;
-  if (p.S == 1) {  // all of K was here: write C
-    for (int m = 0; m < p.M; ++m)
-      for (int n = tid; n < ncols; n += NWARPS * 32) p.c[(size_t)m * p.ldc + n0 + n] = __float2half_rn(sAcc[n * MP + m]);
-    return;
-  }
-  // other k chunks hold the rest: meet in the global scratch; the last chunk to arrive converts
-  for (int idx = tid * 4; idx < ncols * MP; idx += NWARPS * 32 * 4)
-    if ((idx % MP) < p.M) {  // four rows of one column at a time; rows past M hold exact zeros
-      const float4 v = *reinterpret_cast<const float4*>(sAcc + idx);
-      asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p.partial + (size_t)n0 * MP + idx), "f"(v.x),
-                   "f"(v.y), "f"(v.z), "f"(v.w)
-                   : "memory");
+  if (p.T_own > 0) {
+    __syncthreads();
+    const int n0 = own_tile0 * 16, ncols = p.T_own * 16;
+    if (p.S == 1) {  // all of K was here: write C
+      for (int m = 0; m < p.M; ++m)
+        for (int n = tid; n < ncols; n += NWARPS * 32) store_out<GATHER>(p, gather_buf, m, n0 + n, sAcc[n * MP + m]);
+    } else {
+      // other k chunks hold the rest: meet in the global scratch; the last chunk to arrive converts
+      for (int idx = tid * 4; idx < ncols * MP; idx += NWARPS * 32 * 4)
+        if ((idx % MP) < p.M) {  // four rows of one column at a time; rows past M hold exact zeros
+          const float4 v = *reinterpret_cast<const float4*>(sAcc + idx);
+          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p.partial + (size_t)n0 * MP + idx),
+                       "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+                       : "memory");
+        }
+      __syncthreads();
+      int* s_last = reinterpret_cast<int*>(sAcc);  // the tile sums are no longer needed
+      if (tid == 0) __threadfence();  // cumulative over the CTA's additions (ordered by the barrier above)
+      __syncthreads();
+      for (int t = tid; t < p.T_own; t += NWARPS * 32) {
+        const int old = atomicAdd(p.counters + own_tile0 + t, IPT);
+        s_last[t] = (old + IPT == items_per_tile_total) ? 1 : 0;
+      }
+      __syncthreads();
+      for (int idx = tid; idx < ncols * MP; idx += NWARPS * 32) {
+        const int t = idx / (16 * MP);
+        if (!s_last[t]) continue;
+        __threadfence();
+        const int m = idx % MP, n = n0 + idx / MP;
+        if (m < p.M) {
+          float* src = p.partial + (size_t)n0 * MP + idx;
+          store_out<GATHER>(p, gather_buf, m, n, __ldcg(src));
+          __stcg(src, 0.f);
+        }
+        if ((idx % (16 * MP)) == 0) p.counters[own_tile0 + t] = 0;
+      }
     }
-  __syncthreads();
-  int* s_last = reinterpret_cast<int*>(sAcc);  // the tile sums are no longer needed
-  if (tid == 0) __threadfence();  // cumulative over the CTA's additions (ordered by the barrier above)
-  __syncthreads();
-  for (int t = tid; t < p.T_own; t += NWARPS * 32) {
-    const int old = atomicAdd(p.counters + own_tile0 + t, IPT);
-    s_last[t] = (old + IPT == items_per_tile_total) ? 1 : 0;
   }
-  __syncthreads();
-  for (int idx = tid; idx < ncols * MP; idx += NWARPS * 32) {
-    const int t = idx / (16 * MP);
-    if (!s_last[t]) continue;
-    __threadfence();
-    const int m = idx % MP, n = n0 + idx / MP;
-    if (m < p.M) {
-      float* src = p.partial + (size_t)n0 * MP + idx;
-      p.c[(size_t)m * p.ldc + n] = __float2half_rn(__ldcg(src));
-      __stcg(src, 0.f);
+
+  // ---- fused all-gather: the last CTA of the launch tells every rank that this rank's columns
+  // of the output row are in place.  Every CTA orders its stores before its arrival at GPU scope;
+  // the last arriver, which has observed all arrivals, releases at system scope: by cumulativity
+  // every CTA's stores are visible to whoever acquires the flag. ----
+  if (GATHER) {
+    __syncthreads();
+    if (tid == 0) {
+      __threadfence();  // cumulative over the CTA's stores to the peers (ordered by the barrier above)
+      if (atomicAdd(p.ga.done, 1u) == gridDim.x - 1) {
+        atomicExch(p.ga.done, 0u);
+        __threadfence_system();
+        for (int g = 0; g < p.ga.G; ++g)
+          asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.ga.flag_slot[g]), "r"(epoch + 1) : "memory");
+        *p.ga.epoch = epoch + 1;  // read by this rank's next fused launch, after it has waited for this one
+      }
     }
-    if ((idx % (16 * MP)) == 0) p.counters[own_tile0 + t] = 0;
   }
 }
 
-template <int VAR, int MT>
+template <int VAR, int MT, bool GATHER>
 static cudaError_t launch_one(const StreamParams& p, int smem_bytes, cudaStream_t stream) {
-  auto kern = stream_kernel<VAR, MT>;
+  auto kern = stream_kernel<VAR, MT, GATHER>;
   static int configured_smem[16] = {0};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -563,7 +631,9 @@ template <int VAR>
 static cudaError_t launch_var(int var, const StreamParams& p, int mt, int smem_bytes, cudaStream_t stream) {
   if constexpr (VAR % B200Q_NPARTS == B200Q_PART) {
     if (var == VAR) {
-      return mt == 1 ? launch_one<VAR, 1>(p, smem_bytes, stream) : launch_one<VAR, 2>(p, smem_bytes, stream);
+      if (p.ga.G > 0)
+        return mt == 1 ? launch_one<VAR, 1, true>(p, smem_bytes, stream) : launch_one<VAR, 2, true>(p, smem_bytes, stream);
+      return mt == 1 ? launch_one<VAR, 1, false>(p, smem_bytes, stream) : launch_one<VAR, 2, false>(p, smem_bytes, stream);
     }
   }
   if constexpr (VAR + 1 < VAR_COUNT) return launch_var<VAR + 1>(var, p, mt, smem_bytes, stream);

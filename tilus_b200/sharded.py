@@ -17,7 +17,9 @@ import torch
 import torch.distributed as dist
 from torch import nn
 
-from . import packing
+import ctypes
+
+from . import _lib, ops, packing
 from .dtypes import weight_dtype
 from .linear import QuantizedLinear
 
@@ -55,11 +57,14 @@ class ShardedQuantizedLinear(nn.Module):
     """QuantizedLinear whose out_features are split over the ranks of a process group."""
 
     def __init__(self, x_dtype, w_dtype, group_size: int, in_features: int, out_features: int, zero_point: int = 0,
-                 process_group=None, gather_output: bool = True):
+                 process_group=None, gather_output: bool = True, shard=None):
         super().__init__()
         self.process_group = process_group
-        self.world = dist.get_world_size(process_group) if dist.is_initialized() else 1
-        self.rank = dist.get_rank(process_group) if dist.is_initialized() else 0
+        if shard is not None:  # explicit (world, rank): shards handled by one process, e.g. in tests
+            self.world, self.rank = shard
+        else:
+            self.world = dist.get_world_size(process_group) if dist.is_initialized() else 1
+            self.rank = dist.get_rank(process_group) if dist.is_initialized() else 0
         self.in_features, self.out_features = in_features, out_features
         self.n0, self.n1 = shard_range(out_features, self.world, self.rank)
         self.gather_output = gather_output
@@ -77,6 +82,135 @@ class ShardedQuantizedLinear(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         y = self.local(x)
-        if self.gather_output and self.world > 1:
+        if self.gather_output and self.world > 1 and dist.is_initialized():
             y = gather_columns(y, self.process_group)
         return y
+
+
+# ---------------------------------------------------------------------------------------------
+# fused all-gather: the GEMV kernel stores its columns straight into every rank's output row
+# ---------------------------------------------------------------------------------------------
+class _RawCudaBuffer:
+    """A device pointer as an object torch.as_tensor understands (CUDA array interface)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+class GatheredRow:
+    """The gathered output of the latest fused call of a PeerGather context, or a column range of
+    it, as the activations of the next call.  Which of the two row buffers holds it is only known
+    on the device; PeerGather.fetch brings it to a tensor."""
+
+    def __init__(self, rows: int, row_stride: int, col_start: int, width: int):
+        self.rows, self.row_stride, self.col_start, self.width = rows, row_stride, col_start, width
+
+    def cols(self, start: int, stop: int) -> "GatheredRow":
+        assert 0 <= start < stop <= self.width and start % 8 == 0
+        return GatheredRow(self.rows, self.row_stride, self.col_start + start, stop - start)
+
+
+class PeerGather:
+    """Peer-mapped output rows and arrival flags for the fused all-gather of a column-sharded
+    decode stack (include/b200q.h, b200q_gemm_gather).
+
+    Every rank owns one region: `world` 32-bit flags, a call counter, and two fp16 row buffers
+    [max_rows, max_cols] used alternately.  `ptrs[g]` is rank g's region as seen from this
+    process.  A fused call waits (on the device) until every rank has finished the previous
+    call, writes its columns into the other row buffer of every rank and raises its flag on
+    every rank; the call counter lives on the device, so the calls carry no per-call state and
+    a sequence of them can be captured in a CUDA graph and replayed.  All ranks must make the
+    same sequence of calls.
+    """
+
+    FLAGS_OFF, EPOCH_OFF, ROWS_OFF = 0, 64, 256
+
+    def __init__(self, world: int, rank: int, ptrs, max_rows: int, max_cols: int, device):
+        assert 1 <= world <= 8 and len(ptrs) == world
+        self.world, self.rank, self.ptrs = world, rank, list(ptrs)
+        self.max_rows, self.max_cols = max_rows, max_cols
+        self.device = torch.device(device)
+        self._owned = None
+
+    @staticmethod
+    def region_bytes(max_rows: int, max_cols: int) -> int:
+        return PeerGather.ROWS_OFF + 2 * max_rows * max_cols * 2
+
+    @classmethod
+    def create(cls, max_rows: int, max_cols: int, device, group=None):
+        """Allocates this rank's region with the library's peer allocator (zeroed) and maps every
+        other rank's region through CUDA IPC (one process per GPU, one node)."""
+        lib = _lib.load()
+        world = dist.get_world_size(group) if dist.is_initialized() else 1
+        rank = dist.get_rank(group) if dist.is_initialized() else 0
+        nbytes = cls.region_bytes(max_rows, max_cols)
+        with torch.cuda.device(device):
+            mine = ctypes.c_void_p()
+            _lib.check(lib.b200q_peer_alloc(nbytes, ctypes.byref(mine)))
+            handle = ctypes.create_string_buffer(64)
+            _lib.check(lib.b200q_peer_export(mine, handle))
+            handles = [None] * world
+            if world > 1:
+                dist.all_gather_object(handles, bytes(handle.raw), group=group)
+            ptrs = []
+            for g in range(world):
+                if g == rank:
+                    ptrs.append(mine.value)
+                else:
+                    peer = ctypes.c_void_p()
+                    _lib.check(lib.b200q_peer_open(ctypes.create_string_buffer(handles[g], 64), ctypes.byref(peer)))
+                    ptrs.append(peer.value)
+        ctx = cls(world, rank, ptrs, max_rows, max_cols, device)
+        ctx._owned = mine.value
+        return ctx
+
+    def _view(self, byte_off: int, nbytes: int) -> torch.Tensor:
+        return torch.as_tensor(_RawCudaBuffer(self.ptrs[self.rank] + byte_off, nbytes), device=self.device)
+
+    def gemm(self, x, layer: "ShardedQuantizedLinear") -> GatheredRow:
+        """One fused call: this rank's columns of layer(x), gathered into every rank's row buffer.
+        x is a tensor [M, K] or the GatheredRow (or a column range of it) of the previous call."""
+        lib = _lib.load()
+        local = layer.local
+        N_full, N_loc, K = layer.out_features, local.out_features, layer.in_features
+        g = _lib.Gather()
+        if isinstance(x, GatheredRow):
+            M, lda, a_ptr = x.rows, x.row_stride, None
+            if x.width != K:
+                raise ValueError(f"expected {K} input features, got {x.width}")
+            g.a_prev_offset = x.col_start
+        else:
+            if x.dtype != torch.float16 or x.stride(1) != 1 or x.shape[1] != K:
+                raise TypeError(f"activations must be float16 [M, {K}] with unit inner stride")
+            M, lda, a_ptr = x.shape[0], x.stride(0), x.data_ptr()
+            g.a_prev_offset = -1
+        if M > self.max_rows or N_full > self.max_cols or M > 16:
+            raise ValueError("fused gather covers M <= 16 rows within the context's buffer size")
+        g.world, g.rank, g.ldc, g.col_offset = self.world, self.rank, N_full, layer.n0
+        for r in range(self.world):
+            g.out[r] = self.ptrs[r] + self.ROWS_OFF
+            g.flag_slot[r] = self.ptrs[r] + self.FLAGS_OFF + 4 * self.rank
+        g.flags_local = self.ptrs[self.rank] + self.FLAGS_OFF
+        g.epoch_local = self.ptrs[self.rank] + self.EPOCH_OFF
+        g.buffer_elems = self.max_rows * self.max_cols
+        dt, zp, grp = local.w_dtype, local.zero_point, local.group_size
+        with torch.cuda.device(self.device):
+            ws = ops.get_workspace(self.device, ops.workspace_bytes(M, N_loc, K, dt, zp, grp))
+            st = lib.b200q_gemm_gather(a_ptr, lda, local.quantized_weight.data_ptr(), local.scales.data_ptr(), M,
+                                       N_loc, K, dt.code, zp, grp, _lib.ACT_F16, ws.data_ptr(), ws.numel(),
+                                       torch.cuda.current_stream(self.device).cuda_stream, ctypes.byref(g))
+        _lib.check(st)
+        return GatheredRow(M, N_full, 0, N_full)
+
+    def calls_completed(self) -> int:
+        """The device-side call counter (synchronises the current stream)."""
+        torch.cuda.current_stream(self.device).synchronize()
+        return int(self._view(self.EPOCH_OFF, 4).view(torch.int32).item())
+
+    def fetch(self, row: GatheredRow) -> torch.Tensor:
+        """The latest call's gathered output (or the column range `row` of it) as a new tensor."""
+        parity = self.calls_completed() & 1
+        nbytes = self.max_rows * self.max_cols * 2
+        buf = self._view(self.ROWS_OFF + parity * nbytes, nbytes).view(torch.float16)
+        full = buf[: row.rows * row.row_stride].view(row.rows, row.row_stride)
+        return full[:, row.col_start : row.col_start + row.width].clone()
