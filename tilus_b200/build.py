@@ -40,6 +40,8 @@ def _jobs():
     for part in range(NPARTS):
         jobs.append(("stream_kernel.cu", f"stream_part{part}.o", [f"-DB200Q_NPARTS={NPARTS}", f"-DB200Q_PART={part}"]))
     for part in range(NPARTS):
+        jobs.append(("wide_kernel.cu", f"wide_part{part}.o", [f"-DB200Q_NPARTS={NPARTS}", f"-DB200Q_PART={part}"]))
+    for part in range(NPARTS):
         jobs.append(("umma_kernel.cu", f"umma_part{part}.o", [f"-DB200Q_NPARTS={NPARTS}", f"-DB200Q_PART={part}"]))
     jobs.append(("dequant_kernel.cu", "dequant.o", []))
     jobs.append(("quantize_kernel.cu", "quantize.o", []))

@@ -27,6 +27,12 @@ cudaError_t quantize_launch(const void* w, int w_is_f32, int ldw, void* bq, void
   cudaError_t umma_launch_part##i(int, const UmmaParams&, const void*, int, cudaStream_t);
 B200Q_DECL_UPART(0) B200Q_DECL_UPART(1) B200Q_DECL_UPART(2) B200Q_DECL_UPART(3)
 B200Q_DECL_UPART(4) B200Q_DECL_UPART(5) B200Q_DECL_UPART(6) B200Q_DECL_UPART(7)
+#define B200Q_DECL_WPART(i) \
+  cudaError_t wide_launch_part##i(int, const WideParams&, const void*, int, cudaStream_t);
+B200Q_DECL_WPART(0) B200Q_DECL_WPART(1) B200Q_DECL_WPART(2) B200Q_DECL_WPART(3)
+B200Q_DECL_WPART(4) B200Q_DECL_WPART(5) B200Q_DECL_WPART(6) B200Q_DECL_WPART(7)
+int wide_smem_bytes(int bits, int wg_stages);
+int wide_wg_stages(int bits, int max_smem);
 int umma_smem_bytes(int tm, int bits, int a_stages);
 int umma_a_stages(int tm, int bits, int max_smem);
 
@@ -42,6 +48,19 @@ static cudaError_t stream_launch(int var, const StreamParams& p, int mt, int sme
     case 5: return stream_launch_part5(var, p, mt, smem, s);
     case 6: return stream_launch_part6(var, p, mt, smem, s);
     default: return stream_launch_part7(var, p, mt, smem, s);
+  }
+}
+
+static cudaError_t wide_launch(int var, const WideParams& p, const void* tmap, int smem, cudaStream_t s) {
+  switch (var % B200Q_NPARTS) {
+    case 0: return wide_launch_part0(var, p, tmap, smem, s);
+    case 1: return wide_launch_part1(var, p, tmap, smem, s);
+    case 2: return wide_launch_part2(var, p, tmap, smem, s);
+    case 3: return wide_launch_part3(var, p, tmap, smem, s);
+    case 4: return wide_launch_part4(var, p, tmap, smem, s);
+    case 5: return wide_launch_part5(var, p, tmap, smem, s);
+    case 6: return wide_launch_part6(var, p, tmap, smem, s);
+    default: return wide_launch_part7(var, p, tmap, smem, s);
   }
 }
 
@@ -245,6 +264,28 @@ static void plan_umma(int M, int N, int K, int bits, const DeviceInfo& di, b200q
   pl->debug = 0;
 }
 
+// wide tcgen05 kernel (kernel 3): 128-row x 256-column tiles, split-K while the tiles do not fill the SMs
+static const int kWideMaxRows = 128;
+static void plan_wide(int M, int N, int K, int bits, const DeviceInfo& di, b200q_plan_t* pl) {
+  const int m_tiles = (M + 127) / 128, n_tiles = (N + 255) / 256;
+  const int tiles = m_tiles * n_tiles, G = K / 128;
+  int splits = 1;
+  for (int s = 2; s <= 32; ++s)
+    if (G % s == 0 && G / s >= 2 && tiles * s <= di.sm_count + di.sm_count / 8) splits = s;
+  pl->kernel = 3;
+  pl->m_tiles = m_tiles;
+  pl->splits = splits;
+  pl->cluster = 1;
+  pl->ctas_per_split = tiles;
+  pl->stages = wide_wg_stages(bits, di.max_smem);
+  pl->smem_bytes = wide_smem_bytes(bits, pl->stages);
+  pl->tile_m = 128;
+  pl->warps = 23;
+  pl->passes = 1;
+  pl->pdl = 0;
+  pl->debug = 0;
+}
+
 static int make_plan(int M, int N, int K, int var, b200q_plan_t* pl) {
   const DeviceInfo di = device_info();
   std::memset(pl, 0, sizeof(*pl));
@@ -262,7 +303,9 @@ static int make_plan(int M, int N, int K, int var, b200q_plan_t* pl) {
     }
     if (M <= 16) return ST_UNSUPPORTED;
   }
-  plan_umma(M, N, K, bits, di, pl);
+  // a few dozen rows: weights on the wide side of the MMA; beyond, the transposed prefill kernel
+  if (M <= kWideMaxRows) plan_wide(M, N, K, bits, di, pl);
+  else plan_umma(M, N, K, bits, di, pl);
   const size_t part = pl->splits > 1 ? (size_t)M * N * sizeof(float) : 0;
   pl->workspace_bytes = WS_HEADER_BYTES + ws_counter_bytes(N) + part;
   return ST_OK;
@@ -316,6 +359,51 @@ static int run_umma(const void* a, int lda, const void* bq, const void* scales, 
   const int smem = umma_smem_bytes(tm, bits, a_stages);
   if (smem > device_info().max_smem) return ST_UNSUPPORTED;
   cudaError_t e = umma_launch(var, p, &tmap, smem, stream);
+  if (e != cudaSuccess) { g_last_cuda_error = (int)e; return ST_CUDA; }
+  return ST_OK;
+}
+
+static int run_wide(const void* a, int lda, const void* bq, const void* scales, void* c, int ldc, int M, int N, int K,
+                    int var, int group, void* workspace, size_t ws_bytes, cudaStream_t stream,
+                    const b200q_plan_t& pl) {
+  const int bits = var_bits(var);
+  const int m_tiles = (M + 127) / 128, n_tiles = (N + 255) / 256, G = K / 128;
+  if (pl.splits < 1 || G % pl.splits != 0) return ST_INVALID_ARG;  // whole 128-row groups per split
+  if ((ldc % 8) != 0 || (((uintptr_t)scales) & 15)) return ST_INVALID_ARG;  // 16-byte stores, bulk-copied scale rows
+  const size_t need = WS_HEADER_BYTES + ws_counter_bytes(N) + (pl.splits > 1 ? (size_t)M * N * sizeof(float) : 0);
+  if (!workspace || ws_bytes < need || ((uintptr_t)workspace & 255)) return ST_WORKSPACE;
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return ST_CUDA;
+  CUtensorMap tmap;
+  const cuuint64_t gdim[2] = {(cuuint64_t)K, (cuuint64_t)M};
+  const cuuint64_t gstride[1] = {(cuuint64_t)lda * 2};
+  const cuuint32_t box[2] = {64u, 128u};
+  const cuuint32_t estr[2] = {1u, 1u};
+  CUresult r = enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(a), gdim, gstride, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { g_last_cuda_error = (int)r; return ST_CUDA; }
+  WideParams p;
+  p.bq = bq;
+  p.scales = reinterpret_cast<const __half*>(scales);
+  p.c = reinterpret_cast<__half*>(c);
+  p.status = reinterpret_cast<int*>(workspace);
+  p.counters = reinterpret_cast<int*>(reinterpret_cast<char*>(workspace) + WS_HEADER_BYTES);
+  p.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + WS_HEADER_BYTES + ws_counter_bytes(N));
+  p.M = M; p.N = N; p.K = K; p.KB = K / BLOCK_K; p.ldc = ldc;
+  p.gshift = gshift_of(group, K);
+  p.m_tiles = m_tiles; p.n_tiles = n_tiles;
+  p.splits = pl.splits; p.kblocks_per_split = 2 * G / pl.splits;
+  p.wg_stages = wide_wg_stages(bits, device_info().max_smem);
+  p.tl = nullptr;
+#ifdef B200Q_TIMELINE
+  p.tl = g_tl_buf;
+#endif
+  const int items = pl.splits * m_tiles * n_tiles;
+  p.grid = items < device_info().sm_count ? items : device_info().sm_count;
+  const int smem = wide_smem_bytes(bits, p.wg_stages);
+  if (smem > device_info().max_smem) return ST_UNSUPPORTED;
+  cudaError_t e = wide_launch(var, p, &tmap, smem, stream);
   if (e != cudaSuccess) { g_last_cuda_error = (int)e; return ST_CUDA; }
   return ST_OK;
 }
@@ -398,6 +486,8 @@ static int run_gemm(const void* a, int lda, const void* bq, const void* scales, 
     return run_umma(a, lda, bq, scales, c, ldc, M, N, K, var, group, workspace, ws_bytes, stream, pl);
   if (pl.kernel == 2)
     return run_stream(a, lda, bq, scales, c, ldc, M, N, K, var, group, workspace, ws_bytes, stream, pl);
+  if (pl.kernel == 3)
+    return run_wide(a, lda, bq, scales, c, ldc, M, N, K, var, group, workspace, ws_bytes, stream, pl);
   return ST_UNSUPPORTED;
 }
 

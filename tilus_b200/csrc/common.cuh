@@ -97,6 +97,25 @@ struct UmmaParams {
   unsigned long long* tl;  // wait accounting (side builds with B200Q_TIMELINE only), else null
 };
 
+// ---- wide tcgen05 kernel (a few dozen rows): weights on the 256-column side of the MMA ---------
+struct WideParams {
+  const void* bq;        // b200 layout
+  const __half* scales;  // [K/group, N]
+  __half* c;             // [M, N], leading dimension ldc (multiple of 8)
+  float* partial;        // [M, N] fp32 split-K scratch, zero on entry and on exit
+  int* counters;         // [n_tiles * m_tiles], zero on entry and on exit
+  int* status;           // workspace status header
+  int M, N, K, KB;       // KB = K / 512
+  int ldc;
+  int gshift;            // log2(group / 128), or -1 when group == K
+  int m_tiles, n_tiles;  // ceil(M / 128), ceil(N / 256)
+  int splits;            // split-K factor
+  int kblocks_per_split; // 64-row k blocks per work item (even)
+  int wg_stages;         // packed 128-row weight groups in the shared-memory ring
+  int grid;              // persistent CTAs: min(work items, SMs)
+  unsigned long long* tl;  // wait accounting (side builds with B200Q_TIMELINE only), else null
+};
+
 // ---- dequantize kernel -----------------------------------------------------------------------
 struct DequantParams {
   const uint4* bq;

@@ -1,0 +1,472 @@
+// Batches of a few dozen rows: C[M<=128 per tile, N] = A[M, K] x dequant(Bq[K, N]) on tcgen05 with
+// the weights on the wide side of the instruction.
+//
+// A tcgen05.mma with 128 rows costs about 170 cycles whatever its column count (measured for N = 16,
+// 64 and 256), so for small M the product is bound by the number of instructions per weight.  This
+// kernel therefore computes D[m, n] = sum_k A[m, k] * W[k, n] with M = 128 activation rows (rows
+// past the batch are zero-filled by TMA and cost nothing to fetch) and N = 256 weight columns per
+// instruction - twice the weights per instruction of the transposed form used for prefill
+// (umma_kernel.cu), and one decode per weight shared by all rows of the batch:
+//
+//   * warp 21 brings the packed weights of the tile's 256 columns, one 128-row group at a time
+//     (sixteen 16-column pieces of 256*b contiguous bytes, cp.async.bulk) and their 256 fp16
+//     scales into a shared-memory ring;
+//   * warps 0-15 dequantize: thread t is column n = t % 256 of the tile and takes unit t / 256 of
+//     every 64-row block: it reads the unit's 32 codes from the ring, decodes and scales them in registers
+//     (decode.cuh, unit_decode_scaled: fp16_rn(value * scale), exactly the values the reference
+//     multiplies by, examples/quantization/matmul_a16wx.py:316-320) and stores the 32 halfs as its
+//     half of row n of the K-major, 128-byte-swizzled B operand tile in shared memory (4 x 16 bytes);
+//   * warp 20 brings A[m0 : m0+128, k : k+64] with one 2-D tiled TMA copy per block;
+//   * warp 22 owns tensor memory and issues 4 x tcgen05.mma.cta_group::1.kind::f16 per block
+//     (M = 128, N = 256, K = 16, both operands through shared-memory descriptors), fp32
+//     accumulators 128 lanes x 256 columns, two of them so that the epilogue of one tile runs
+//     under the MMAs of the next;
+//   * warps 16-19 read the accumulator (lane = activation row, 32 columns = 32 consecutive output
+//     columns per tcgen05.ld) and store 64-byte row segments of C, or add into the fp32 split-K
+//     scratch (red.global.add.v4.f32); the last split to arrive converts and restores the zeros.
+//
+// Persistent CTAs walk over (split, column tile, row tile) work items.  Every mbarrier wait is
+// bounded in time; a wait that runs out raises a CTA-wide abort flag, all loops leave, tensor
+// memory is still freed and the status word of the workspace reports it.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "umma_common.cuh"
+
+#ifndef B200Q_PART
+#define B200Q_PART 0
+#endif
+#ifndef B200Q_NPARTS
+#define B200Q_NPARTS 1
+#endif
+
+namespace b200q {
+
+constexpr int WIDE_THREADS = 736;   // 16 dequant warps, 4 epilogue warps, 2 producers, MMA warp
+constexpr int WIDE_SA = 4;          // activation stages (16 KB each)
+constexpr int WIDE_SB = 3;          // dequantized weight stages (32 KB each)
+constexpr int WIDE_WG_MAX = 3;      // packed 128-row weight groups in the ring (4096*b + 512 bytes each)
+constexpr int WIDE_TMEM_COLS = 512; // two accumulators of 256 columns
+
+struct WideBarriers {
+  uint64_t a_full[WIDE_SA], a_empty[WIDE_SA];
+  uint64_t b_full[WIDE_SB], b_empty[WIDE_SB];
+  uint64_t g_full[WIDE_WG_MAX], g_empty[WIDE_WG_MAX];
+  uint64_t d_full[2], d_empty[2];
+  uint32_t tmem_base;
+  volatile int abort_flag;
+  int last_flag;
+};
+
+__host__ __device__ constexpr int wide_wstage_bytes(int bits) { return 4096 * bits + 512; }
+
+template <int VAR>
+__global__ void __launch_bounds__(WIDE_THREADS, 1)
+wide_kernel(const WideParams p, const __grid_constant__ CUtensorMap tmap_a) {
+  constexpr int B = var_bits(VAR);
+  constexpr uint32_t WSTAGE = (uint32_t)wide_wstage_bytes(B);
+  constexpr uint32_t ASTAGE = 128u * 128u, BSTAGE = 256u * 128u;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  const uint32_t smem_unaligned = (uint32_t)__cvta_generic_to_shared(smem_raw);
+  const uint32_t smem_base = (smem_unaligned + 1023u) & ~1023u;
+  unsigned char* smem_al = smem_raw + (smem_base - smem_unaligned);
+  const int WG = p.wg_stages;
+  const uint32_t a_s = smem_base;
+  const uint32_t b_s = a_s + WIDE_SA * ASTAGE;
+  const uint32_t w_s = b_s + WIDE_SB * BSTAGE;
+  const uint32_t bars_off = WIDE_SA * ASTAGE + WIDE_SB * BSTAGE + (uint32_t)WG * WSTAGE;
+  WideBarriers* bars = reinterpret_cast<WideBarriers*>(smem_al + bars_off);
+  const uint32_t bars_s = smem_base + bars_off;
+#define BAR_ADDR(field, i) (bars_s + (uint32_t)offsetof(WideBarriers, field) + (uint32_t)(i) * 8u)
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+#ifdef B200Q_TIMELINE
+  const long long t_kernel = clock64();
+#endif
+  const int total_items = p.splits * p.n_tiles * p.m_tiles;
+  const int nkk = p.kblocks_per_split;  // 64-blocks per work item (even)
+  const int ngrp = nkk >> 1;
+  volatile int* abort_flag = &bars->abort_flag;
+
+  if (tid == 0) {
+    for (int i = 0; i < WIDE_SA; ++i) { mbar_init(BAR_ADDR(a_full, i), 1); mbar_init(BAR_ADDR(a_empty, i), 1); }
+    for (int i = 0; i < WIDE_SB; ++i) { mbar_init(BAR_ADDR(b_full, i), 16); mbar_init(BAR_ADDR(b_empty, i), 1); }
+    for (int i = 0; i < WIDE_WG_MAX; ++i) { mbar_init(BAR_ADDR(g_full, i), 1); mbar_init(BAR_ADDR(g_empty, i), 16); }
+    for (int i = 0; i < 2; ++i) { mbar_init(BAR_ADDR(d_full, i), 1); mbar_init(BAR_ADDR(d_empty, i), 4); }
+    bars->abort_flag = 0;
+    bars->last_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 22) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     bars_s + (uint32_t)offsetof(WideBarriers, tmem_base)),
+                 "r"(WIDE_TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = bars->tmem_base;
+
+  // work item w -> (split, n_tile, m_tile), m fastest
+#define ITEM_COORDS(w)                                         \
+  const int m_tile = (w) % p.m_tiles;                          \
+  const int n_tile = ((w) / p.m_tiles) % p.n_tiles;            \
+  const int split = (w) / (p.m_tiles * p.n_tiles);             \
+  const int kk0 = split * nkk;                                 \
+  const int m0 = m_tile * 128;                                 \
+  (void)m_tile; (void)n_tile; (void)split; (void)kk0; (void)m0;
+
+  if (warp < 16) {
+    // ================= dequantize: packed ring -> registers -> swizzled B operand tile =================
+    const int nl = tid & 255;  // column inside the tile = row of the B operand
+    const int u = tid >> 8;    // which of the two 32-row units of a 64-row block this thread takes
+    // this column inside a ring stage: 16-column piece nl / 16, then unit (half*32 + r*4 + j)
+    const uint32_t lane_off = (uint32_t)((nl >> 4) * (256 * B) + (((nl >> 3) & 1) * 32 + (nl & 7) * 4) * (B * 4));
+    // row nl of a K-major 128-byte-swizzled tile: 8-row atoms of 1024 bytes, 16-byte chunk c at c ^ (row % 8)
+    const uint32_t row_off = (uint32_t)((nl >> 3) * 1024 + (nl & 7) * 128);
+    const uint32_t sw = (uint32_t)(nl & 7);
+    int g_run = 0, bi = 0;  // groups / blocks consumed so far (all work items)
+    bool good = true;
+    TL_DECL(acc_g); TL_DECL(acc_be); TL_DECL(acc_dec); TL_DECL(acc_sts); TL_DECL(acc_fence);
+#ifdef B200Q_TIMELINE
+    const long long t_begin = clock64();
+#endif
+    for (int w = blockIdx.x; w < total_items && good; w += gridDim.x) {
+      ITEM_COORDS(w)
+      const bool nvalid = n_tile * 256 + nl < p.N;
+      for (int g = 0; g < ngrp && good; ++g, ++g_run) {
+        const int gs = g_run % WG;
+        if (!WAIT_ACC(acc_g, mbar_wait_abortable(BAR_ADDR(g_full, gs), (uint32_t)(g_run / WG) & 1u, abort_flag))) { good = false; break; }
+        const uint32_t st = w_s + (uint32_t)gs * WSTAGE;
+        unsigned short sbits;
+        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sbits) : "r"(st + 4096u * B + (uint32_t)nl * 2u));
+        if (!nvalid) sbits = 0;
+        const __half2 s2 = __half2half2(__ushort_as_half(sbits));
+#pragma unroll
+        for (int h = 0; h < 2; ++h, ++bi) {  // the two 64-row blocks of the group
+#ifdef B200Q_TIMELINE
+          const long long t_d0 = clock64();
+#endif
+          uint32_t wq[B];
+          lds_unit_words<B>(st + lane_off + (uint32_t)((h * 2 + u) * B * 4), wq);
+          if (!nvalid) {
+#pragma unroll
+            for (int q = 0; q < B; ++q) wq[q] = 0u;
+          }
+          uint32_t out[16];
+          unit_decode_scaled<VAR>(wq, s2, out);
+          if (h == 1) {  // the ring stage has been read (its values fed the arithmetic above)
+            __syncwarp();
+            if (lane == 0) mbar_arrive(BAR_ADDR(g_empty, gs));
+          }
+#ifdef B200Q_TIMELINE
+          acc_dec += clock64() - t_d0;
+#endif
+          const int sb = bi % WIDE_SB;
+          if (!WAIT_ACC(acc_be, mbar_wait_abortable(BAR_ADDR(b_empty, sb), ((uint32_t)(bi / WIDE_SB) & 1u) ^ 1u, abort_flag))) { good = false; break; }
+          const uint32_t dst = b_s + (uint32_t)sb * BSTAGE + row_off;
+#ifdef B200Q_TIMELINE
+          const long long t_s0 = clock64();
+#endif
+#pragma unroll
+          for (int c = 0; c < 4; ++c)  // 16-byte chunks 4u .. 4u+3 of the row
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst + (((uint32_t)(4 * u + c) ^ sw) << 4)),
+                         "r"(out[4 * c]), "r"(out[4 * c + 1]), "r"(out[4 * c + 2]), "r"(out[4 * c + 3])
+                         : "memory");
+#ifdef B200Q_TIMELINE
+          const long long t_f0 = clock64();
+          acc_sts += t_f0 - t_s0;
+#endif
+          // generic-proxy writes must be visible to the tensor core's (async proxy) reads
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+#ifdef B200Q_TIMELINE
+          acc_fence += clock64() - t_f0;
+#endif
+          __syncwarp();
+          if (lane == 0) mbar_arrive(BAR_ADDR(b_full, sb));
+        }
+      }
+    }
+#ifdef B200Q_TIMELINE
+    if (tid == 0) { TL_WRITE(5, clock64() - t_begin); TL_WRITE(6, acc_g); TL_WRITE(7, acc_be); TL_WRITE(9, acc_dec); TL_WRITE(10, acc_sts); TL_WRITE(11, acc_fence); }
+#endif
+  } else if (warp < 20) {
+    // ================= epilogue: read D, write C (or add into the split-K scratch) =================
+    const int ew = warp - 16;  // lane quadrant of tensor memory
+    int it = 0;
+    bool good = true;
+    for (int w = blockIdx.x; w < total_items && good; w += gridDim.x, ++it) {
+      ITEM_COORDS(w)
+      const int buf = it & 1;
+      const int m = m0 + ew * 32 + lane;
+      if (!mbar_wait_abortable(BAR_ADDR(d_full, buf), (uint32_t)(it >> 1) & 1u, abort_flag)) { good = false; break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t daddr = tmem + ((uint32_t)(ew * 32) << 16) + (uint32_t)(buf * 256);
+      const bool rows_here = m0 + ew * 32 < p.M;  // any row of this warp inside the batch
+      for (int c0 = 0; c0 < 256; c0 += 32) {
+        const int n = n_tile * 256 + c0;
+        if (!rows_here || n >= p.N) continue;  // warp-uniform
+        uint32_t v[32];
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, "
+            "%14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+            : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+              "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]),
+              "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]),
+              "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]),
+              "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+            : "r"(daddr + (uint32_t)c0)
+            : "memory");
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (m < p.M) {
+          const int ncols = min(32, p.N - n);  // multiple of 16
+          if (p.splits == 1) {
+            __half* dst = p.c + (size_t)m * p.ldc + n;
+#pragma unroll
+            for (int q = 0; q < 32; q += 8) {
+              if (q < ncols) {
+                uint4 o;
+                o.x = bits_from_h2(__floats2half2_rn(__uint_as_float(v[q]), __uint_as_float(v[q + 1])));
+                o.y = bits_from_h2(__floats2half2_rn(__uint_as_float(v[q + 2]), __uint_as_float(v[q + 3])));
+                o.z = bits_from_h2(__floats2half2_rn(__uint_as_float(v[q + 4]), __uint_as_float(v[q + 5])));
+                o.w = bits_from_h2(__floats2half2_rn(__uint_as_float(v[q + 6]), __uint_as_float(v[q + 7])));
+                *reinterpret_cast<uint4*>(dst + q) = o;
+              }
+            }
+          } else {
+            float* dst = p.partial + (size_t)m * p.N + n;
+#pragma unroll
+            for (int q = 0; q < 32; q += 4)
+              if (q < ncols)
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + q), "f"(__uint_as_float(v[q])),
+                             "f"(__uint_as_float(v[q + 1])), "f"(__uint_as_float(v[q + 2])),
+                             "f"(__uint_as_float(v[q + 3]))
+                             : "memory");
+          }
+        }
+      }
+      // the accumulator has been read: the MMAs of the tile after next may overwrite it
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(BAR_ADDR(d_empty, buf));
+      if (p.splits > 1) {
+        // the last split to arrive converts the fp32 sums and restores the zeros
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (warp == 16 && lane == 0) {
+          __threadfence();
+          const int old = atomicAdd(p.counters + n_tile * p.m_tiles + m_tile, 1);
+          const int last = (old + 1 == p.splits) ? 1 : 0;
+          if (last) __threadfence();
+          bars->last_flag = last;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (bars->last_flag) {
+          const int rows = min(128, p.M - m0), cols = min(256, p.N - n_tile * 256);
+          for (int idx = tid - 512; idx < rows * (cols / 8); idx += 128) {
+            const int mm = m0 + idx / (cols / 8), nn = n_tile * 256 + (idx % (cols / 8)) * 8;
+            float4* src = reinterpret_cast<float4*>(p.partial + (size_t)mm * p.N + nn);
+            const float4 x0 = __ldcg(src), x1 = __ldcg(src + 1);
+            uint4 o;
+            o.x = bits_from_h2(__floats2half2_rn(x0.x, x0.y)); o.y = bits_from_h2(__floats2half2_rn(x0.z, x0.w));
+            o.z = bits_from_h2(__floats2half2_rn(x1.x, x1.y)); o.w = bits_from_h2(__floats2half2_rn(x1.z, x1.w));
+            *reinterpret_cast<uint4*>(p.c + (size_t)mm * p.ldc + nn) = o;
+            __stcg(src, make_float4(0.f, 0.f, 0.f, 0.f));
+            __stcg(src + 1, make_float4(0.f, 0.f, 0.f, 0.f));
+          }
+          if (warp == 16 && lane == 0) p.counters[n_tile * p.m_tiles + m_tile] = 0;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // last_flag may be rewritten by the next item
+      }
+    }
+  } else if (warp == 20) {
+    // ================= TMA producer: activations =================
+    if (lane == 0) {
+      int ai = 0;
+      bool good = true;
+      for (int w = blockIdx.x; w < total_items && good; w += gridDim.x) {
+        ITEM_COORDS(w)
+        for (int i = 0; i < nkk; ++i, ++ai) {
+          const int sa = ai % WIDE_SA;
+          if (!mbar_wait_abortable(BAR_ADDR(a_empty, sa), ((uint32_t)(ai / WIDE_SA) & 1u) ^ 1u, abort_flag)) { good = false; break; }
+          const uint32_t bar = BAR_ADDR(a_full, sa);
+          asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(ASTAGE) : "memory");
+          const int kx = (kk0 + i) * 64;
+          asm volatile(
+              "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+              ::"r"(a_s + (uint32_t)sa * ASTAGE), "l"(&tmap_a), "r"(bar), "r"(kx), "r"(m0)
+              : "memory");
+        }
+      }
+    }
+  } else if (warp == 21) {
+    // ================= bulk-copy producer: packed weights and scales =================
+    int g_run = 0;
+    bool good = true;
+    const unsigned char* bq = reinterpret_cast<const unsigned char*>(p.bq);
+    for (int w = blockIdx.x; w < total_items && good; w += gridDim.x) {
+      ITEM_COORDS(w)
+      const int nt0 = n_tile * 16;
+      const int pieces = min(16, p.N / BLOCK_N - nt0);  // 16-column pieces of this tile that exist
+      for (int g = 0; g < ngrp; ++g, ++g_run) {
+        const int gs = g_run % WG;
+        int ok = 1;
+        if (lane == 0)
+          ok = mbar_wait_abortable(BAR_ADDR(g_empty, gs), ((uint32_t)(g_run / WG) & 1u) ^ 1u, abort_flag) ? 1 : 0;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) { good = false; break; }
+        const uint32_t bar = BAR_ADDR(g_full, gs);
+        const uint32_t dst = w_s + (uint32_t)gs * WSTAGE;
+        if (lane == 0)
+          asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar),
+                       "r"((uint32_t)pieces * (256u * B + 32u))
+                       : "memory");
+        __syncwarp();
+        const int G = (kk0 >> 1) + g;  // 128-row group of K
+        if (lane < pieces) {
+          const unsigned char* src = bq + ((size_t)(nt0 + lane) * p.KB + (G >> 2)) * (size_t)(1024 * B) +
+                                     (size_t)(G & 3) * (256 * B);
+          asm volatile(
+              "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                  dst + (uint32_t)lane * (256u * B)),
+              "l"(src), "r"(256u * B), "r"(bar)
+              : "memory");
+        } else if (lane == 16) {
+          const int row = p.gshift >= 0 ? (G >> p.gshift) : 0;
+          const __half* src = p.scales + (size_t)row * p.N + n_tile * 256;
+          asm volatile(
+              "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                  dst + 4096u * B),
+              "l"(src), "r"((uint32_t)pieces * 32u), "r"(bar)
+              : "memory");
+        }
+      }
+    }
+  } else {
+    // ================= MMA issuer =================
+    if (lane == 0) {
+      // instruction descriptor: D fp32, A/B fp16, both K-major, M = 128, N = 256
+      const uint32_t idesc = (1u << 4) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+      bool good = true;
+      int bi = 0, it = 0;
+      TL_DECL(acc_de); TL_DECL(acc_af); TL_DECL(acc_bf);
+#ifdef B200Q_TIMELINE
+      const long long t_begin = clock64();
+#endif
+      for (int w = blockIdx.x; w < total_items && good; w += gridDim.x, ++it) {
+        const int buf = it & 1;
+        // the accumulator must have been read out by the epilogue two items ago
+        if (!WAIT_ACC(acc_de, mbar_wait_abortable(BAR_ADDR(d_empty, buf), ((uint32_t)(it >> 1) & 1u) ^ 1u, abort_flag))) { good = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t d_tmem = tmem + (uint32_t)(buf * 256);
+        for (int i = 0; i < nkk; ++i, ++bi) {
+          const int sa = bi % WIDE_SA, sb = bi % WIDE_SB;
+          good = WAIT_ACC(acc_af, mbar_wait_abortable(BAR_ADDR(a_full, sa), (uint32_t)(bi / WIDE_SA) & 1u, abort_flag)) &&
+                 WAIT_ACC(acc_bf, mbar_wait_abortable(BAR_ADDR(b_full, sb), (uint32_t)(bi / WIDE_SB) & 1u, abort_flag));
+          if (!good) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint64_t adesc = umma_smem_desc(a_s + (uint32_t)sa * ASTAGE);
+          const uint64_t bdesc = umma_smem_desc(b_s + (uint32_t)sb * BSTAGE);
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {
+            const uint32_t accumulate = (i > 0 || ks > 0) ? 1u : 0u;
+            asm volatile(
+                "{\n\t.reg .pred p;\n\t"
+                "setp.ne.b32 p, %4, 0;\n\t"
+                "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                ::"r"(d_tmem), "l"(adesc + (uint64_t)(ks * 2)), "l"(bdesc + (uint64_t)(ks * 2)), "r"(idesc),
+                "r"(accumulate)
+                : "memory");
+          }
+          // the stages may be overwritten once these MMAs have read them
+          asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                           BAR_ADDR(a_empty, sa))
+                       : "memory");
+          asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                           BAR_ADDR(b_empty, sb))
+                       : "memory");
+        }
+        if (good)
+          asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                           BAR_ADDR(d_full, buf))
+                       : "memory");
+      }
+#ifdef B200Q_TIMELINE
+      TL_WRITE(0, clock64() - t_begin); TL_WRITE(1, acc_de); TL_WRITE(2, acc_af); TL_WRITE(3, acc_bf);
+      TL_WRITE(4, t_begin - t_kernel);
+#endif
+    }
+  }
+
+  // ================= teardown =================
+  __syncwarp();
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (*abort_flag && tid == 0) {
+    atomicExch(p.status, ST_DEVICE_TIMEOUT);
+    p.status[1] = 6;  // where: wide tcgen05 kernel pipeline
+    p.status[2] = blockIdx.x;
+    p.status[3] = 0;
+  }
+  if (warp == 22) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(WIDE_TMEM_COLS) : "memory");
+  }
+#ifdef B200Q_TIMELINE
+  if (tid == 0) TL_WRITE(8, clock64() - t_kernel);
+#endif
+#undef BAR_ADDR
+#undef ITEM_COORDS
+}
+
+template <int VAR>
+static cudaError_t wide_launch_one(const WideParams& p, const CUtensorMap& tmap, int smem_bytes, cudaStream_t stream) {
+  auto kern = wide_kernel<VAR>;
+  static int configured_smem[16] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 16 || configured_smem[dev] < smem_bytes) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < 16) configured_smem[dev] = smem_bytes;
+  }
+  kern<<<p.grid, WIDE_THREADS, smem_bytes, stream>>>(p, tmap);
+  return cudaGetLastError();
+}
+
+template <int VAR>
+static cudaError_t wide_launch_var(int var, const WideParams& p, const CUtensorMap& tmap, int smem_bytes,
+                                   cudaStream_t stream) {
+  if constexpr (VAR % B200Q_NPARTS == B200Q_PART) {
+    if (var == VAR) return wide_launch_one<VAR>(p, tmap, smem_bytes, stream);
+  }
+  if constexpr (VAR + 1 < VAR_COUNT) return wide_launch_var<VAR + 1>(var, p, tmap, smem_bytes, stream);
+  else return cudaErrorInvalidValue;
+}
+
+#define B200Q_CAT2(a, b) a##b
+#define B200Q_CAT(a, b) B200Q_CAT2(a, b)
+
+// One of these per compiled part; api.cu picks the part as var % B200Q_NPARTS.
+cudaError_t B200Q_CAT(wide_launch_part, B200Q_PART)(int var, const WideParams& p, const void* tmap, int smem_bytes,
+                                                    cudaStream_t stream) {
+  return wide_launch_var<0>(var, p, *reinterpret_cast<const CUtensorMap*>(tmap), smem_bytes, stream);
+}
+
+#if B200Q_PART == 0
+// dynamic shared memory: alignment slack + activation stages + B operand stages + packed ring + barriers
+int wide_smem_bytes(int bits, int wg_stages) {
+  return 1024 + WIDE_SA * 128 * 128 + WIDE_SB * 256 * 128 + wg_stages * wide_wstage_bytes(bits) +
+         (int)sizeof(WideBarriers) + 64;
+}
+// most packed weight groups in the ring (<= WIDE_WG_MAX) that fit
+int wide_wg_stages(int bits, int max_smem) {
+  int wg = WIDE_WG_MAX;
+  while (wg > 1 && wide_smem_bytes(bits, wg) > max_smem) --wg;
+  return wg;
+}
+#endif
+
+}  // namespace b200q
