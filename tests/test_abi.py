@@ -46,8 +46,14 @@ def test_plan_static_table():
     assert (8192 // 16) % p["ctas_per_split"] == 0 and p["smem_bytes"] <= 113 * 1024 and p["stages"] >= 2
     assert p["workspace_bytes"] >= 256 + 8192 * 4
     assert ops.plan(4096, 28672, 8192, "int4b", 0, 128)["kernel"] == 1  # prefill: tcgen05 kernel
-    p16 = ops.plan(16, 4096, 4096, "uint4b", 8, 128)
-    assert p16["m_tiles"] == 2 and p16["smem_bytes"] <= 227 * 1024
+    p8 = ops.plan(8, 4096, 4096, "uint4b", 8, 128)
+    assert p8["kernel"] == 2 and p8["m_tiles"] == 1 and p8["smem_bytes"] <= 113 * 1024
+    # 9..128 rows: tcgen05 kernel with the weights on the 256-column side of the MMA
+    for m in (9, 16, 64, 128):
+        pw = ops.plan(m, 4096, 4096, "uint4b", 8, 128)
+        assert pw["kernel"] == 3 and pw["smem_bytes"] <= 227 * 1024
+        assert pw["splits"] * pw["ctas_per_split"] <= 148 + 148 // 8
+    assert ops.plan(129, 4096, 4096, "uint4b", 8, 128)["kernel"] == 1
     # per-channel scales, float weights
     assert ops.plan(4, 4096, 4096, "float6_e3m2", 0, 4096)["passes"] == 1
 

@@ -89,7 +89,9 @@ def _forced(M, N, K, dt, zp, override, seed=11, group=128):
     prob = synth.make_problem(M, N, K, dt, group, seed=seed)
     prob["zero_point"] = zp
     bq = packing.interleave(prob["codes"], dt).to(dev)
-    ws = torch.zeros(ops.workspace_bytes(M, N, K, dt, zp, group), dtype=torch.uint8, device=dev)
+    # a forced plan may run another kernel than the default one for M: room for either's scratch
+    need = max(ops.workspace_bytes(m, N, K, dt, zp, group) for m in (1, M, 200))
+    ws = torch.zeros(need + M * N * 4, dtype=torch.uint8, device=dev)
     ref = qo.quantized_matmul(prob["a"].numpy(), prob["codes"].numpy(), prob["scales"].numpy(), dt, group, zp)
     for _ in range(2):  # second call runs on the workspace the first one left behind
         c = ops.quantized_matmul(prob["a"].to(dev), bq, prob["scales"].to(dev), dt, group, zp, workspace=ws,

@@ -31,8 +31,9 @@ B200Q_DECL_UPART(4) B200Q_DECL_UPART(5) B200Q_DECL_UPART(6) B200Q_DECL_UPART(7)
   cudaError_t wide_launch_part##i(int, const WideParams&, const void*, int, cudaStream_t);
 B200Q_DECL_WPART(0) B200Q_DECL_WPART(1) B200Q_DECL_WPART(2) B200Q_DECL_WPART(3)
 B200Q_DECL_WPART(4) B200Q_DECL_WPART(5) B200Q_DECL_WPART(6) B200Q_DECL_WPART(7)
-int wide_smem_bytes(int bits, int wg_stages);
-int wide_wg_stages(int bits, int max_smem);
+int wide_smem_bytes(int bits, int wg_stages, int a_rows);
+int wide_wg_stages(int bits, int max_smem, int a_rows);
+int wide_a_rows(int M);
 int umma_smem_bytes(int tm, int bits, int a_stages);
 int umma_a_stages(int tm, int bits, int max_smem);
 
@@ -190,7 +191,7 @@ static int stream_ctas_per_chunk(int NT, int s, int per_sm, const DeviceInfo& di
     if (NT % c == 0) return c;
   return full > NT ? NT : full;
 }
-static const int kStreamMaxRows = 16;
+static const int kStreamMaxRows = 8;
 static size_t stream_workspace_bytes(int N) { return WS_HEADER_BYTES + ws_counter_bytes(N) + (size_t)16 * N * sizeof(float); }
 // K is cut into the fewest chunks S (a divisor of K/512, at most one per SM) that leave room for
 // three ring slots per warp next to the activation chunk [M, K/S]; the grid is S * CPC.
@@ -277,8 +278,8 @@ static void plan_wide(int M, int N, int K, int bits, const DeviceInfo& di, b200q
   pl->splits = splits;
   pl->cluster = 1;
   pl->ctas_per_split = tiles;
-  pl->stages = wide_wg_stages(bits, di.max_smem);
-  pl->smem_bytes = wide_smem_bytes(bits, pl->stages);
+  pl->stages = wide_wg_stages(bits, di.max_smem, wide_a_rows(M));
+  pl->smem_bytes = wide_smem_bytes(bits, pl->stages, wide_a_rows(M));
   pl->tile_m = 128;
   pl->warps = 23;
   pl->passes = 1;
@@ -286,14 +287,14 @@ static void plan_wide(int M, int N, int K, int bits, const DeviceInfo& di, b200q
   pl->debug = 0;
 }
 
-static int make_plan(int M, int N, int K, int var, b200q_plan_t* pl) {
+static int make_plan(int M, int N, int K, int var, b200q_plan_t* pl, int stream_max_rows = kStreamMaxRows) {
   const DeviceInfo di = device_info();
   std::memset(pl, 0, sizeof(*pl));
   const int bits = var_bits(var);
-  // up to 16 rows: the mma.sync stream kernel; above, the tcgen05 kernel.  (The stream kernel was
-  // also tried with 32 rows per launch for M <= 64: 45 us for M = 32, K = N = 8192 against ~40 us of the
-  // tcgen05 kernel - with K cut in 16 chunks its fp32 partial sums cost more than the decode saves.)
-  if (M <= kStreamMaxRows) {
+  // up to 8 rows: the mma.sync stream kernel; above, the tcgen05 kernels.  (With more rows the stream
+  // kernel has to cut K in chunks to fit its activations in shared memory, and the fp32 partial sums
+  // then cost more than the decode saves: 34 us at M = 16 and 45 us at M = 32, K = N = 8192.)
+  if (M <= stream_max_rows) {
     const int rows = stream_rows_per_pass(M);
     const int m_pass = M < rows ? M : rows;
     if (plan_stream(m_pass, N, K, bits, di, pl) == ST_OK) {
@@ -301,7 +302,6 @@ static int make_plan(int M, int N, int K, int var, b200q_plan_t* pl) {
       pl->workspace_bytes = stream_workspace_bytes(N);  // fp32 scratch [N][8 or 16]
       return ST_OK;
     }
-    if (M <= 16) return ST_UNSUPPORTED;
   }
   // a few dozen rows: weights on the wide side of the MMA; beyond, the transposed prefill kernel
   if (M <= kWideMaxRows) plan_wide(M, N, K, bits, di, pl);
@@ -377,7 +377,8 @@ static int run_wide(const void* a, int lda, const void* bq, const void* scales, 
   CUtensorMap tmap;
   const cuuint64_t gdim[2] = {(cuuint64_t)K, (cuuint64_t)M};
   const cuuint64_t gstride[1] = {(cuuint64_t)lda * 2};
-  const cuuint32_t box[2] = {64u, 128u};
+  const int a_rows = wide_a_rows(M);
+  const cuuint32_t box[2] = {64u, (cuuint32_t)a_rows};
   const cuuint32_t estr[2] = {1u, 1u};
   CUresult r = enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(a), gdim, gstride, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -394,14 +395,16 @@ static int run_wide(const void* a, int lda, const void* bq, const void* scales, 
   p.gshift = gshift_of(group, K);
   p.m_tiles = m_tiles; p.n_tiles = n_tiles;
   p.splits = pl.splits; p.kblocks_per_split = 2 * G / pl.splits;
-  p.wg_stages = wide_wg_stages(bits, device_info().max_smem);
+  p.a_rows = a_rows;
+  p.wg_stages = wide_wg_stages(bits, device_info().max_smem, a_rows);
+  p.debug = pl.debug;
   p.tl = nullptr;
 #ifdef B200Q_TIMELINE
   p.tl = g_tl_buf;
 #endif
   const int items = pl.splits * m_tiles * n_tiles;
   p.grid = items < device_info().sm_count ? items : device_info().sm_count;
-  const int smem = wide_smem_bytes(bits, p.wg_stages);
+  const int smem = wide_smem_bytes(bits, p.wg_stages, a_rows);
   if (smem > device_info().max_smem) return ST_UNSUPPORTED;
   cudaError_t e = wide_launch(var, p, &tmap, smem, stream);
   if (e != cudaSuccess) { g_last_cuda_error = (int)e; return ST_CUDA; }
@@ -554,7 +557,7 @@ int b200q_gemm_gather(const void* a, int lda, const void* bq, const void* scales
   int st = check_problem(M, N, K, wtype, zero_point, group, 128, &var);
   if (st != ST_OK) return st;
   b200q_plan_t pl;
-  st = make_plan(M, N, K, var, &pl);
+  st = make_plan(M, N, K, var, &pl, 16);  // the fused gather lives in the stream kernel only
   if (st != ST_OK) return st;
   if (pl.kernel != 2) return ST_UNSUPPORTED;
   return run_stream(a, lda, bq, scales, nullptr, gather->ldc, M, N, K, var, group, workspace, workspace_bytes,

@@ -112,7 +112,10 @@ struct WideParams {
   int splits;            // split-K factor
   int kblocks_per_split; // 64-row k blocks per work item (even)
   int wg_stages;         // packed 128-row weight groups in the shared-memory ring
+  int a_rows;            // rows per activation copy: 32, 64 or 128
   int grid;              // persistent CTAs: min(work items, SMs)
+  int debug;             // timing experiments (results are wrong): 2 no activation copies, 4 no operand
+                         // stores, 16 one contiguous weight copy per group, 32 no MMAs
   unsigned long long* tl;  // wait accounting (side builds with B200Q_TIMELINE only), else null
 };
 

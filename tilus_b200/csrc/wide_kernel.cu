@@ -11,11 +11,12 @@
 //   * warp 21 brings the packed weights of the tile's 256 columns, one 128-row group at a time
 //     (sixteen 16-column pieces of 256*b contiguous bytes, cp.async.bulk) and their 256 fp16
 //     scales into a shared-memory ring;
-//   * warps 0-15 dequantize: thread t is column n = t % 256 of the tile and takes unit t / 256 of
-//     every 64-row block: it reads the unit's 32 codes from the ring, decodes and scales them in registers
+//   * warps 0-15 dequantize, in two sets of eight that take alternate 128-row groups: thread t is
+//     column n = t % 256 of the tile; per 64-row block it reads its column's 2 units (64 codes) from the
+//     ring, decodes and scales them in registers
 //     (decode.cuh, unit_decode_scaled: fp16_rn(value * scale), exactly the values the reference
-//     multiplies by, examples/quantization/matmul_a16wx.py:316-320) and stores the 32 halfs as its
-//     half of row n of the K-major, 128-byte-swizzled B operand tile in shared memory (4 x 16 bytes);
+//     multiplies by, examples/quantization/matmul_a16wx.py:316-320) and stores the 64 halfs as
+//     row n of the K-major, 128-byte-swizzled B operand tile in shared memory (8 x 16 bytes);
 //   * warp 20 brings A[m0 : m0+128, k : k+64] with one 2-D tiled TMA copy per block;
 //   * warp 22 owns tensor memory and issues 4 x tcgen05.mma.cta_group::1.kind::f16 per block
 //     (M = 128, N = 256, K = 16, both operands through shared-memory descriptors), fp32
@@ -43,9 +44,9 @@
 namespace b200q {
 
 constexpr int WIDE_THREADS = 736;   // 16 dequant warps, 4 epilogue warps, 2 producers, MMA warp
-constexpr int WIDE_SA = 4;          // activation stages (16 KB each)
+constexpr int WIDE_SA = 4;          // activation stages (a_rows * 128 bytes apart; the MMA reads 16 KB from each)
 constexpr int WIDE_SB = 3;          // dequantized weight stages (32 KB each)
-constexpr int WIDE_WG_MAX = 3;      // packed 128-row weight groups in the ring (4096*b + 512 bytes each)
+constexpr int WIDE_WG_MAX = 8;      // packed 128-row weight groups in the ring (4096*b + 512 bytes each)
 constexpr int WIDE_TMEM_COLS = 512; // two accumulators of 256 columns
 
 struct WideBarriers {
@@ -65,16 +66,22 @@ __global__ void __launch_bounds__(WIDE_THREADS, 1)
 wide_kernel(const WideParams p, const __grid_constant__ CUtensorMap tmap_a) {
   constexpr int B = var_bits(VAR);
   constexpr uint32_t WSTAGE = (uint32_t)wide_wstage_bytes(B);
-  constexpr uint32_t ASTAGE = 128u * 128u, BSTAGE = 256u * 128u;
+  constexpr uint32_t BSTAGE = 256u * 128u;
+  // Activation stages: the copy fills a_rows rows (32, 64 or 128: the batch rounded up); the MMA
+  // always reads 128 rows, i.e. 16 KB, from the stage's base.  Rows beyond the batch only feed
+  // accumulator rows that nobody reads, so for small batches the stages are laid a_rows * 128 bytes
+  // apart and the MMA's surplus rows alias the following stages: what is saved goes to the packed ring.
+  const uint32_t ASTAGE = (uint32_t)p.a_rows * 128u;
+  const uint32_t AREGION = (WIDE_SA - 1) * ASTAGE + 128u * 128u;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const uint32_t smem_unaligned = (uint32_t)__cvta_generic_to_shared(smem_raw);
   const uint32_t smem_base = (smem_unaligned + 1023u) & ~1023u;
   unsigned char* smem_al = smem_raw + (smem_base - smem_unaligned);
   const int WG = p.wg_stages;
   const uint32_t a_s = smem_base;
-  const uint32_t b_s = a_s + WIDE_SA * ASTAGE;
+  const uint32_t b_s = a_s + AREGION;
   const uint32_t w_s = b_s + WIDE_SB * BSTAGE;
-  const uint32_t bars_off = WIDE_SA * ASTAGE + WIDE_SB * BSTAGE + (uint32_t)WG * WSTAGE;
+  const uint32_t bars_off = AREGION + WIDE_SB * BSTAGE + (uint32_t)WG * WSTAGE;
   WideBarriers* bars = reinterpret_cast<WideBarriers*>(smem_al + bars_off);
   const uint32_t bars_s = smem_base + bars_off;
 #define BAR_ADDR(field, i) (bars_s + (uint32_t)offsetof(WideBarriers, field) + (uint32_t)(i) * 8u)
@@ -90,14 +97,18 @@ wide_kernel(const WideParams p, const __grid_constant__ CUtensorMap tmap_a) {
 
   if (tid == 0) {
     for (int i = 0; i < WIDE_SA; ++i) { mbar_init(BAR_ADDR(a_full, i), 1); mbar_init(BAR_ADDR(a_empty, i), 1); }
-    for (int i = 0; i < WIDE_SB; ++i) { mbar_init(BAR_ADDR(b_full, i), 16); mbar_init(BAR_ADDR(b_empty, i), 1); }
-    for (int i = 0; i < WIDE_WG_MAX; ++i) { mbar_init(BAR_ADDR(g_full, i), 1); mbar_init(BAR_ADDR(g_empty, i), 16); }
+    for (int i = 0; i < WIDE_SB; ++i) { mbar_init(BAR_ADDR(b_full, i), 8); mbar_init(BAR_ADDR(b_empty, i), 1); }
+    for (int i = 0; i < WIDE_WG_MAX; ++i) { mbar_init(BAR_ADDR(g_full, i), 1); mbar_init(BAR_ADDR(g_empty, i), 8); }
     for (int i = 0; i < 2; ++i) { mbar_init(BAR_ADDR(d_full, i), 1); mbar_init(BAR_ADDR(d_empty, i), 4); }
     bars->abort_flag = 0;
     bars->last_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
+  // programmatic dependent launch: the next kernel of the stream may become resident when there is
+  // room; this one reads activations / writes C only after its predecessor has completed (the two
+  // roles that do so wait below), while the packed weights - constants - stream in right away
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (warp == 22) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      bars_s + (uint32_t)offsetof(WideBarriers, tmem_base)),
@@ -121,16 +132,18 @@ wide_kernel(const WideParams p, const __grid_constant__ CUtensorMap tmap_a) {
 
   if (warp < 16) {
     // ================= dequantize: packed ring -> registers -> swizzled B operand tile =================
+    // Two sets of eight warps take alternate 128-row groups, so that one set's loads and decode run
+    // under the other set's stores and hand-over instead of all warps moving in lockstep.
+    const int set = warp >> 3;
     const int nl = tid & 255;  // column inside the tile = row of the B operand
-    const int u = tid >> 8;    // which of the two 32-row units of a 64-row block this thread takes
     // this column inside a ring stage: 16-column piece nl / 16, then unit (half*32 + r*4 + j)
     const uint32_t lane_off = (uint32_t)((nl >> 4) * (256 * B) + (((nl >> 3) & 1) * 32 + (nl & 7) * 4) * (B * 4));
     // row nl of a K-major 128-byte-swizzled tile: 8-row atoms of 1024 bytes, 16-byte chunk c at c ^ (row % 8)
     const uint32_t row_off = (uint32_t)((nl >> 3) * 1024 + (nl & 7) * 128);
     const uint32_t sw = (uint32_t)(nl & 7);
-    int g_run = 0, bi = 0;  // groups / blocks consumed so far (all work items)
+    int g_run = 0;  // groups passed so far (all work items)
     bool good = true;
-    TL_DECL(acc_g); TL_DECL(acc_be); TL_DECL(acc_dec); TL_DECL(acc_sts); TL_DECL(acc_fence);
+    TL_DECL(acc_g); TL_DECL(acc_be);
 #ifdef B200Q_TIMELINE
     const long long t_begin = clock64();
 #endif
@@ -138,6 +151,7 @@ wide_kernel(const WideParams p, const __grid_constant__ CUtensorMap tmap_a) {
       ITEM_COORDS(w)
       const bool nvalid = n_tile * 256 + nl < p.N;
       for (int g = 0; g < ngrp && good; ++g, ++g_run) {
+        if ((g_run & 1) != set) continue;  // the other set's group
         const int gs = g_run % WG;
         if (!WAIT_ACC(acc_g, mbar_wait_abortable(BAR_ADDR(g_full, gs), (uint32_t)(g_run / WG) & 1u, abort_flag))) { good = false; break; }
         const uint32_t st = w_s + (uint32_t)gs * WSTAGE;
@@ -145,56 +159,50 @@ wide_kernel(const WideParams p, const __grid_constant__ CUtensorMap tmap_a) {
         asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sbits) : "r"(st + 4096u * B + (uint32_t)nl * 2u));
         if (!nvalid) sbits = 0;
         const __half2 s2 = __half2half2(__ushort_as_half(sbits));
+        // all of this column's codes of the group go to registers first, so that the ring stage is
+        // free for the next copy while the decode and the stores below run
+        uint32_t wq[2][2 * B];
+        lds_two_units<B>(st + lane_off, wq[0]);
+        lds_two_units<B>(st + lane_off + (uint32_t)(2 * B * 4), wq[1]);
+        if (!nvalid) {
 #pragma unroll
-        for (int h = 0; h < 2; ++h, ++bi) {  // the two 64-row blocks of the group
-#ifdef B200Q_TIMELINE
-          const long long t_d0 = clock64();
-#endif
-          uint32_t wq[B];
-          lds_unit_words<B>(st + lane_off + (uint32_t)((h * 2 + u) * B * 4), wq);
-          if (!nvalid) {
+          for (int q = 0; q < 2 * B; ++q) { wq[0][q] = 0u; wq[1][q] = 0u; }
+        }
+        // order the arrive after the loads have returned: make it depend on the loaded values
+        {
+          uint32_t dep = wq[0][0] ^ wq[1][2 * B - 1];
+          asm volatile("" : "+r"(dep));
+          __syncwarp();
+          if (lane == 0) mbar_arrive(BAR_ADDR(g_empty, gs));
+        }
 #pragma unroll
-            for (int q = 0; q < B; ++q) wq[q] = 0u;
-          }
-          uint32_t out[16];
-          unit_decode_scaled<VAR>(wq, s2, out);
-          if (h == 1) {  // the ring stage has been read (its values fed the arithmetic above)
-            __syncwarp();
-            if (lane == 0) mbar_arrive(BAR_ADDR(g_empty, gs));
-          }
-#ifdef B200Q_TIMELINE
-          acc_dec += clock64() - t_d0;
-#endif
+        for (int h = 0; h < 2; ++h) {  // the two 64-row blocks of the group
+          uint32_t out[32];
+          unit_decode_scaled<VAR>(wq[h], s2, out);
+          unit_decode_scaled<VAR>(wq[h] + B, s2, out + 16);
+          const int bi = 2 * g_run + h;  // running 64-block index
           const int sb = bi % WIDE_SB;
           if (!WAIT_ACC(acc_be, mbar_wait_abortable(BAR_ADDR(b_empty, sb), ((uint32_t)(bi / WIDE_SB) & 1u) ^ 1u, abort_flag))) { good = false; break; }
           const uint32_t dst = b_s + (uint32_t)sb * BSTAGE + row_off;
-#ifdef B200Q_TIMELINE
-          const long long t_s0 = clock64();
-#endif
+          if (!(p.debug & 4))
 #pragma unroll
-          for (int c = 0; c < 4; ++c)  // 16-byte chunks 4u .. 4u+3 of the row
-            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst + (((uint32_t)(4 * u + c) ^ sw) << 4)),
+          for (int c = 0; c < 8; ++c)
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst + (((uint32_t)c ^ sw) << 4)),
                          "r"(out[4 * c]), "r"(out[4 * c + 1]), "r"(out[4 * c + 2]), "r"(out[4 * c + 3])
                          : "memory");
-#ifdef B200Q_TIMELINE
-          const long long t_f0 = clock64();
-          acc_sts += t_f0 - t_s0;
-#endif
           // generic-proxy writes must be visible to the tensor core's (async proxy) reads
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-#ifdef B200Q_TIMELINE
-          acc_fence += clock64() - t_f0;
-#endif
           __syncwarp();
           if (lane == 0) mbar_arrive(BAR_ADDR(b_full, sb));
         }
       }
     }
 #ifdef B200Q_TIMELINE
-    if (tid == 0) { TL_WRITE(5, clock64() - t_begin); TL_WRITE(6, acc_g); TL_WRITE(7, acc_be); TL_WRITE(9, acc_dec); TL_WRITE(10, acc_sts); TL_WRITE(11, acc_fence); }
+    if (tid == 0) { TL_WRITE(5, clock64() - t_begin); TL_WRITE(6, acc_g); TL_WRITE(7, acc_be); }
 #endif
   } else if (warp < 20) {
     // ================= epilogue: read D, write C (or add into the split-K scratch) =================
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // writes C and the split-K scratch
     const int ew = warp - 16;  // lane quadrant of tensor memory
     int it = 0;
     bool good = true;
@@ -284,6 +292,7 @@ wide_kernel(const WideParams p, const __grid_constant__ CUtensorMap tmap_a) {
   } else if (warp == 20) {
     // ================= TMA producer: activations =================
     if (lane == 0) {
+      asm volatile("griddepcontrol.wait;" ::: "memory");  // reads A
       int ai = 0;
       bool good = true;
       for (int w = blockIdx.x; w < total_items && good; w += gridDim.x) {
@@ -292,8 +301,11 @@ wide_kernel(const WideParams p, const __grid_constant__ CUtensorMap tmap_a) {
           const int sa = ai % WIDE_SA;
           if (!mbar_wait_abortable(BAR_ADDR(a_empty, sa), ((uint32_t)(ai / WIDE_SA) & 1u) ^ 1u, abort_flag)) { good = false; break; }
           const uint32_t bar = BAR_ADDR(a_full, sa);
-          asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(ASTAGE) : "memory");
+          asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar),
+                       "r"((p.debug & 2) ? 0u : ASTAGE)
+                       : "memory");
           const int kx = (kk0 + i) * 64;
+          if (!(p.debug & 2))
           asm volatile(
               "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
               ::"r"(a_s + (uint32_t)sa * ASTAGE), "l"(&tmap_a), "r"(bar), "r"(kx), "r"(m0)
@@ -325,7 +337,16 @@ wide_kernel(const WideParams p, const __grid_constant__ CUtensorMap tmap_a) {
                        : "memory");
         __syncwarp();
         const int G = (kk0 >> 1) + g;  // 128-row group of K
-        if (lane < pieces) {
+        if (p.debug & 16) {
+          if (lane == 0) {
+            const unsigned char* src = bq + ((size_t)nt0 * p.KB + (G >> 2) * 4) * (size_t)(1024 * B) +
+                                       (size_t)(G & 3) * (4096 * B);
+            asm volatile(
+                "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                "l"(src), "r"((uint32_t)pieces * 256u * B), "r"(bar)
+                : "memory");
+          }
+        } else if (lane < pieces) {
           const unsigned char* src = bq + ((size_t)(nt0 + lane) * p.KB + (G >> 2)) * (size_t)(1024 * B) +
                                      (size_t)(G & 3) * (256 * B);
           asm volatile(
@@ -333,7 +354,8 @@ wide_kernel(const WideParams p, const __grid_constant__ CUtensorMap tmap_a) {
                   dst + (uint32_t)lane * (256u * B)),
               "l"(src), "r"(256u * B), "r"(bar)
               : "memory");
-        } else if (lane == 16) {
+        }
+        if (lane == 16) {
           const int row = p.gshift >= 0 ? (G >> p.gshift) : 0;
           const __half* src = p.scales + (size_t)row * p.N + n_tile * 256;
           asm volatile(
@@ -369,6 +391,7 @@ wide_kernel(const WideParams p, const __grid_constant__ CUtensorMap tmap_a) {
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint64_t adesc = umma_smem_desc(a_s + (uint32_t)sa * ASTAGE);
           const uint64_t bdesc = umma_smem_desc(b_s + (uint32_t)sb * BSTAGE);
+          if (!(p.debug & 32))
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks) {
             const uint32_t accumulate = (i > 0 || ks > 0) ? 1u : 0u;
@@ -432,8 +455,17 @@ static cudaError_t wide_launch_one(const WideParams& p, const CUtensorMap& tmap,
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 16) configured_smem[dev] = smem_bytes;
   }
-  kern<<<p.grid, WIDE_THREADS, smem_bytes, stream>>>(p, tmap);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)p.grid, 1, 1);
+  cfg.blockDim = dim3(WIDE_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = (size_t)smem_bytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, p, tmap);
 }
 
 template <int VAR>
@@ -457,14 +489,16 @@ cudaError_t B200Q_CAT(wide_launch_part, B200Q_PART)(int var, const WideParams& p
 
 #if B200Q_PART == 0
 // dynamic shared memory: alignment slack + activation stages + B operand stages + packed ring + barriers
-int wide_smem_bytes(int bits, int wg_stages) {
-  return 1024 + WIDE_SA * 128 * 128 + WIDE_SB * 256 * 128 + wg_stages * wide_wstage_bytes(bits) +
+int wide_smem_bytes(int bits, int wg_stages, int a_rows) {
+  return 1024 + (WIDE_SA - 1) * a_rows * 128 + 128 * 128 + WIDE_SB * 256 * 128 + wg_stages * wide_wstage_bytes(bits) +
          (int)sizeof(WideBarriers) + 64;
 }
+// rows one activation copy fills: the batch rounded up to 32, 64 or 128
+int wide_a_rows(int M) { return M <= 32 ? 32 : (M <= 64 ? 64 : 128); }
 // most packed weight groups in the ring (<= WIDE_WG_MAX) that fit
-int wide_wg_stages(int bits, int max_smem) {
+int wide_wg_stages(int bits, int max_smem, int a_rows) {
   int wg = WIDE_WG_MAX;
-  while (wg > 1 && wide_smem_bytes(bits, wg) > max_smem) --wg;
+  while (wg > 1 && wide_smem_bytes(bits, wg, a_rows) > max_smem) --wg;
   return wg;
 }
 #endif
