@@ -51,14 +51,16 @@ enum { B200Q_F16 = 0 };
  * python/tilus/lang/instantiated_script.py:700-801).  Filled by b200q_plan; may be edited
  * and passed to b200q_gemm_planned for experiments. */
 typedef struct b200q_plan {
-  int32_t kernel;        /* 2 = mma.sync stream kernel (M <= 16 per pass), 1 = tcgen05 kernel */
-  int32_t m_tiles;       /* kernel 2: 8-row activation tiles per pass (1 or 2); kernel 1: tiles along M */
-  int32_t splits;        /* k chunks (kernel 2) / split-K factor (kernel 1) */
+  int32_t kernel;        /* 2 = mma.sync stream kernel (M <= 8; up to 16 rows when forced), 3 = tcgen05 kernel with
+                            the weights on the 256-column side (M <= 128), 1 = tcgen05 kernel for larger M */
+  int32_t m_tiles;       /* kernel 2: 8-row activation tiles per pass (1 or 2); kernels 1, 3: tiles along M */
+  int32_t splits;        /* k chunks (kernel 2) / split-K factor (kernels 1, 3) */
   int32_t cluster;       /* 1 (no kernel launches clusters) */
-  int32_t ctas_per_split;/* kernel 2: CTAs per k chunk, grid = splits * ctas_per_split; kernel 1: output tiles */
+  int32_t ctas_per_split;/* kernel 2: CTAs per k chunk, grid = splits * ctas_per_split; kernels 1, 3: output tiles */
   int32_t smem_bytes;    /* dynamic shared memory per CTA */
-  int32_t tile_m;        /* kernel 1: activation rows per CTA tile (32, 64, 128 or 256) */
-  int32_t stages;        /* pipeline depth (kernel 2: ring slots per warp; kernel 1: activation stages) */
+  int32_t tile_m;        /* kernel 1: activation rows per CTA tile (32, 64, 128 or 256); kernel 3: 128 */
+  int32_t stages;        /* pipeline depth (kernel 2: ring slots per warp; kernel 1: activation stages;
+                            kernel 3: 128-row weight groups in the packed ring) */
   int32_t warps;         /* warps per CTA (output only) */
   int32_t passes;        /* launches needed to cover M */
   int32_t pdl;           /* 1: launch with programmatic stream serialization (overlap with the previous kernel) */
