@@ -114,6 +114,34 @@ def test_stream_kernel_variants(dt, zp):
     _forced(9, 256, 1024, dt, zp, dict(kernel=2, splits=2, ctas_per_split=7, cluster=1, stages=2, pdl=1), seed=5)
 
 
+@pytest.mark.parametrize("M,N,K,splits", [(9, 272, 2048, 1), (33, 272, 2048, 4), (64, 512, 1024, 2), (65, 256, 1024, 8),
+                                          (128, 768, 1536, 3), (17, 16, 512, 1)])
+def test_wide_kernel_shapes_and_clean_workspace(M, N, K, splits):
+    """Kernel 3 (tcgen05, weights as the 256-column operand) with forced split-K factors: ragged
+    last column tile (N not a multiple of 256), every activation-stage spacing (M <= 32, <= 64,
+    <= 128), odd group counts per split."""
+    tiles = (N + 255) // 256
+    _forced(M, N, K, D.int4b, 0, dict(kernel=3, splits=splits, ctas_per_split=tiles, tile_m=128))
+
+
+@pytest.mark.parametrize("dt,zp,group", [(D.uint4b, 8, 128), (D.uint3b, 4, 128), (D.float6_e3m2, 0, 1024),
+                                         (D.uint8, 0, 256), (D.uint1b, 1, 128), (D.int6b, 0, 512)],
+                         ids=lambda x: getattr(x, "name", str(x)))
+def test_wide_kernel_variants(dt, zp, group):
+    _forced(40, 528, 1024, dt, zp, dict(kernel=3, splits=2, ctas_per_split=3, tile_m=128), seed=7, group=group)
+
+
+def test_wide_kernel_more_items_than_sms():
+    """Persistent CTAs walk over several work items each: the pipelines, accumulator buffers and
+    barrier phases carry over item boundaries."""
+    M, N, K = 20, 256 * 200, 512
+    prob = synth.make_problem(M, N, K, D.uint4b, 128, seed=2)
+    c, _, _ = _run(prob)
+    ref = qo.quantized_matmul(prob["a"].numpy(), prob["codes"].numpy(), prob["scales"].numpy(), D.uint4b, 128, 8)
+    assert _rel_err(c, ref) <= REL_TOL
+    assert ops.plan(M, N, K, D.uint4b, 8, 128)["kernel"] == 3
+
+
 def test_config0_m16_k4096_n4096_u4():
     prob = synth.make_problem(16, 4096, 4096, D.uint4b, 128, seed=0)
     c, bq, sc = _run(prob)
