@@ -1,7 +1,7 @@
 """Benchmark of the weight-only quantized matmul hot path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
-                    [--no-sweep] [--no-prefill] [--stack] [--profile-case decode|prefill|batch16]
+                    [--no-sweep] [--no-prefill] [--stack] [--profile-case decode|prefill|batch16|batch32]
 
 Headline workload (one GPU): decode GEMV, M=1, K=N=8192, uint4 codes with zero point 8,
 group 128, fp16 scales - the "u4 g128" decode configuration the metric is quoted on.
@@ -247,6 +247,8 @@ def run_profile_case(args) -> None:
         dt, m, n, k, count = dtypes.uint4b, 1, 8192, 8192, 6
     elif case == "batch16":
         dt, m, n, k, count = dtypes.uint4b, 16, 8192, 8192, 6
+    elif case == "batch32":
+        dt, m, n, k, count = dtypes.uint4b, 32, 8192, 8192, 6
     elif case == "prefill":
         dt, m, n, k, count = dtypes.int4b, 4096, 7168, 8192, 2
     else:
@@ -555,7 +557,7 @@ def main():
                     help="time the N-sharded Llama-3-8B-shaped decode linear stack (all-gather per layer) instead")
     ap.add_argument("--fused", action="store_true",
                     help="with --stack: all-gather fused into the GEMV kernel (peer stores + flags) for M <= 16")
-    ap.add_argument("--profile-case", default=None, choices=["decode", "batch16", "prefill"],
+    ap.add_argument("--profile-case", default=None, choices=["decode", "batch16", "batch32", "prefill"],
                     help="run a few plain launches of one kernel (for ncu) instead of the benchmark")
     args = ap.parse_args()
     if args.impl == "reference":
