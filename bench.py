@@ -17,8 +17,9 @@ through QuantizedLinear.forward with pinned host activations copied in and the r
 copied out every step), `cpu_baseline` (the CPU oracle - the reference's PyTorch
 dequantize + matmul semantics - timed on this host), `clocks`, `gpu_launches`, and an
 `extra` sweep: the other bit widths at M=1, M=16, the M=16 K=N=4096 configuration, the
-per-channel float6 / int3 batch sweep, the Llama-3-8B layer shapes at M in {1, 8, 32, 64}
-and the M=4096 prefill GEMM in TFLOP/s.
+per-channel float6 / int3 batch sweep, the Llama-3-8B layer shapes at M in {1, 8, 32, 64},
+the reference example's own table (K=4096, N=12288, eight weight types, M in {1, 16, 4096,
+4097}) and the M=4096 prefill GEMM in TFLOP/s.
 
 `--impl reference` times the CPU dequantize + matmul path alone (the reference operator's
 semantics on the host cores), on the same workload and metric.
@@ -509,6 +510,15 @@ def run_b200(args) -> None:
             r = _sweep_shape(dtypes.uint4b, n_out, k_in, GROUP, [1, 8, 32, 64], dev, 10)
             for m, v in r.items():
                 extra[f"llama8b_{name}_M{m}"] = mem_entry(v)
+        # the reference example's own table (examples/quantization/matmul_a16wx.py:551-622):
+        # K=4096, N=12288, group 128, eight weight types, M in {1, 16, 4096, 4097}
+        for d in (dtypes.float8_e5m2, dtypes.float6_e3m2, dtypes.float4_e2m1, dtypes.float3_e1m1, dtypes.int8,
+                  dtypes.int6b, dtypes.int4b, dtypes.int3b):
+            ms_list = [1, 16] if args.no_prefill else [1, 16, 4096, 4097]
+            r = _sweep_shape(d, 12288, 4096, GROUP, ms_list, dev, 5)
+            extra[f"example_table_{d.short_name}_K4096_N12288"] = {
+                f"M{m}": {"us": round(v["us"], 2), "tflops": round(v["tflops"], 2), "gbs": round(v["gbs"], 1)}
+                for m, v in r.items()}
         if not args.no_prefill:
             r = _sweep_shape(dtypes.int4b, 28672, 8192, GROUP, [4096], dev, 3)[4096]
             extra["prefill_i4_M4096_K8192_N28672"] = {

@@ -181,7 +181,6 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, 2) stream_kernel(const Stre
 
   const uint32_t bar0 = smem_base + warp * 64;
   const uint32_t ring_s = smem_base + 1024 + warp * NST * SLOT_BYTES;
-  const uint32_t ring_end = ring_s + NST * SLOT_BYTES;
 
   // ---- producer: lane 0 requests the items of the warp, in order, into the warp's ring ----
   int pc_q, issued = 0;
