@@ -272,13 +272,25 @@ umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
         }
         asm volatile("bar.sync 1, 256;" ::: "memory");
         if (bars->last_flag) {
-          for (int idx = tid - 256; idx < 64 * TM; idx += 256) {
-            const int nn = n_tile * 128 + (idx & 63) * 2, m = m0 + (idx >> 6);
-            if (nn < p.N && m < p.M) {
-              float2* src = reinterpret_cast<float2*>(p.partial + (size_t)m * p.N + nn);
-              const float2 x = __ldcg(src);
-              *reinterpret_cast<__half2*>(p.c + (size_t)m * p.ldc + nn) = __floats2half2_rn(x.x, x.y);
-              __stcg(src, make_float2(0.f, 0.f));
+          // eight independent loads per thread in flight: one L2 round trip per batch, not per load
+          for (int base = tid - 256; base < 64 * TM; base += 8 * 256) {
+            float2 x[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              const int idx = base + u * 256;
+              const int nn = n_tile * 128 + (idx & 63) * 2, m = m0 + (idx >> 6);
+              if (idx < 64 * TM && nn < p.N && m < p.M)
+                x[u] = __ldcg(reinterpret_cast<const float2*>(p.partial + (size_t)m * p.N + nn));
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              const int idx = base + u * 256;
+              const int nn = n_tile * 128 + (idx & 63) * 2, m = m0 + (idx >> 6);
+              if (idx < 64 * TM && nn < p.N && m < p.M) {
+                float2* src = reinterpret_cast<float2*>(p.partial + (size_t)m * p.N + nn);
+                *reinterpret_cast<__half2*>(p.c + (size_t)m * p.ldc + nn) = __floats2half2_rn(x[u].x, x[u].y);
+                __stcg(src, make_float2(0.f, 0.f));
+              }
             }
           }
           if (warp == 8 && lane == 0) p.counters[n_tile * p.m_tiles + m_tile] = 0;

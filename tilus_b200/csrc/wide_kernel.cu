@@ -47,6 +47,9 @@ constexpr int WIDE_THREADS = 736;   // 16 dequant warps, 4 epilogue warps, 2 pro
 constexpr int WIDE_SA = 4;          // activation stages (a_rows * 128 bytes apart; the MMA reads 16 KB from each)
 constexpr int WIDE_SB = 3;          // dequantized weight stages (32 KB each)
 constexpr int WIDE_WG_MAX = 8;      // packed 128-row weight groups in the ring (4096*b + 512 bytes each)
+#ifndef WIDE_FINALIZE_BATCH
+#define WIDE_FINALIZE_BATCH 3
+#endif
 constexpr int WIDE_TMEM_COLS = 512; // two accumulators of 256 columns
 
 struct WideBarriers {
@@ -273,16 +276,37 @@ wide_kernel(const WideParams p, const __grid_constant__ CUtensorMap tmap_a) {
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (bars->last_flag) {
           const int rows = min(128, p.M - m0), cols = min(256, p.N - n_tile * 256);
-          for (int idx = tid - 512; idx < rows * (cols / 8); idx += 128) {
-            const int mm = m0 + idx / (cols / 8), nn = n_tile * 256 + (idx % (cols / 8)) * 8;
-            float4* src = reinterpret_cast<float4*>(p.partial + (size_t)mm * p.N + nn);
-            const float4 x0 = __ldcg(src), x1 = __ldcg(src + 1);
-            uint4 o;
-            o.x = bits_from_h2(__floats2half2_rn(x0.x, x0.y)); o.y = bits_from_h2(__floats2half2_rn(x0.z, x0.w));
-            o.z = bits_from_h2(__floats2half2_rn(x1.x, x1.y)); o.w = bits_from_h2(__floats2half2_rn(x1.z, x1.w));
-            *reinterpret_cast<uint4*>(p.c + (size_t)mm * p.ldc + nn) = o;
-            __stcg(src, make_float4(0.f, 0.f, 0.f, 0.f));
-            __stcg(src + 1, make_float4(0.f, 0.f, 0.f, 0.f));
+          // FB independent 32-byte loads per thread in flight: one L2 round trip per batch, not per load
+          constexpr int FB = WIDE_FINALIZE_BATCH;
+          const int per_row = cols / 8, total = rows * per_row;
+          for (int base = tid - 512; base < total; base += FB * 128) {
+            float4 x[FB][2];
+#pragma unroll
+            for (int u = 0; u < FB; ++u) {
+              const int idx = base + u * 128;
+              if (idx < total) {
+                const float4* src = reinterpret_cast<const float4*>(
+                    p.partial + (size_t)(m0 + idx / per_row) * p.N + n_tile * 256 + (idx % per_row) * 8);
+                x[u][0] = __ldcg(src);
+                x[u][1] = __ldcg(src + 1);
+              }
+            }
+#pragma unroll
+            for (int u = 0; u < FB; ++u) {
+              const int idx = base + u * 128;
+              if (idx < total) {
+                const int mm = m0 + idx / per_row, nn = n_tile * 256 + (idx % per_row) * 8;
+                float4* src = reinterpret_cast<float4*>(p.partial + (size_t)mm * p.N + nn);
+                uint4 o;
+                o.x = bits_from_h2(__floats2half2_rn(x[u][0].x, x[u][0].y));
+                o.y = bits_from_h2(__floats2half2_rn(x[u][0].z, x[u][0].w));
+                o.z = bits_from_h2(__floats2half2_rn(x[u][1].x, x[u][1].y));
+                o.w = bits_from_h2(__floats2half2_rn(x[u][1].z, x[u][1].w));
+                *reinterpret_cast<uint4*>(p.c + (size_t)mm * p.ldc + nn) = o;
+                __stcg(src, make_float4(0.f, 0.f, 0.f, 0.f));
+                __stcg(src + 1, make_float4(0.f, 0.f, 0.f, 0.f));
+              }
+            }
           }
           if (warp == 16 && lane == 0) p.counters[n_tile * p.m_tiles + m_tile] = 0;
         }
