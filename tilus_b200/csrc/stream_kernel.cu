@@ -565,15 +565,21 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, 2) stream_kernel(const Stre
         s_last[t] = (old + IPT == items_per_tile_total) ? 1 : 0;
       }
       __syncthreads();
-      for (int idx = tid; idx < ncols * MP; idx += NWARPS * 32) {
+      // four rows of one column per thread and step; one fence per thread, not per element
+      bool fenced = false;
+      for (int idx = tid * 4; idx < ncols * MP; idx += NWARPS * 32 * 4) {
         const int t = idx / (16 * MP);
         if (!s_last[t]) continue;
-        __threadfence();
+        if (!fenced) { __threadfence(); fenced = true; }
         const int m = idx % MP, n = n0 + idx / MP;
         if (m < p.M) {
-          float* src = p.partial + (size_t)n0 * MP + idx;
-          store_out<GATHER>(p, gather_buf, m, n, __ldcg(src));
-          __stcg(src, 0.f);
+          float4* src = reinterpret_cast<float4*>(p.partial + (size_t)n0 * MP + idx);
+          const float4 v = __ldcg(src);
+          __stcg(src, make_float4(0.f, 0.f, 0.f, 0.f));
+          store_out<GATHER>(p, gather_buf, m, n, v.x);
+          if (m + 1 < p.M) store_out<GATHER>(p, gather_buf, m + 1, n, v.y);
+          if (m + 2 < p.M) store_out<GATHER>(p, gather_buf, m + 2, n, v.z);
+          if (m + 3 < p.M) store_out<GATHER>(p, gather_buf, m + 3, n, v.w);
         }
         if ((idx % (16 * MP)) == 0) p.counters[own_tile0 + t] = 0;
       }
