@@ -160,9 +160,19 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, 2) stream_kernel(const Stre
   const int own_tile0 = ci * p.T_own;
   const int left_tile0 = p.CPC * p.T_own;
   const long long left_items = (long long)(p.NT - left_tile0) * IPT;
-  const int l0 = (int)(left_items * ci / p.CPC), l1 = (int)(left_items * (ci + 1) / p.CPC);
+  int l0 = 0, l1 = 0;
+  if (left_items > 0) {  // 32-bit division where the products fit (64-bit division costs ~100 instructions)
+    if (left_items <= 0x7fffffffLL / p.CPC) {
+      l0 = (int)((unsigned)left_items * (unsigned)ci / (unsigned)p.CPC);
+      l1 = (int)((unsigned)left_items * (unsigned)(ci + 1) / (unsigned)p.CPC);
+    } else {
+      l0 = (int)(left_items * ci / p.CPC);
+      l1 = (int)(left_items * (ci + 1) / p.CPC);
+    }
+  }
   const int n_left = l1 - l0, n_total = n_left + p.T_own * IPT;
-  const int v0 = (int)((long long)n_total * warp / NWARPS), v1 = (int)((long long)n_total * (warp + 1) / NWARPS);
+  // n_total < 2^26 (column tiles x k blocks x 4 of one CTA), NWARPS = 16: the products fit in 32 bits
+  const int v0 = (int)((unsigned)n_total * (unsigned)warp / NWARPS), v1 = (int)((unsigned)n_total * (unsigned)(warp + 1) / NWARPS);
   // this warp's two item runs: cA items of left-over tiles, then cB items of the CTA's own tiles
   const int cA = v0 < n_left ? min(v1, n_left) - v0 : 0;
   const int tileA = left_tile0 + (l0 + v0) / IPT, qA = (l0 + v0) % IPT;
@@ -209,6 +219,19 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, 2) stream_kernel(const Stre
   // half a row (16 bytes) of one of 16 consecutive groups.  Scales are constants: the first
   // fill runs ahead of the wait on the previous kernel. ----
   unsigned char* sc_warp = sScale + (size_t)warp * SCG * 32;
+  auto scale_src = [&](int gidx) -> const uint4* {
+    const int itx = gidx / GI, gi = gidx - itx * GI;
+    int tile, q;
+    if (itx < cA) {
+      const int gg = l0 + v0 + itx;
+      tile = left_tile0 + gg / IPT; q = gg % IPT;
+    } else {
+      const int o = oB + itx - cA;
+      tile = own_tile0 + o / IPT; q = o % IPT;
+    }
+    const int row = p.gshift >= 0 ? ((kb_base * 4 + q * GI + gi) >> p.gshift) : 0;
+    return reinterpret_cast<const uint4*>(p.scales + (size_t)row * p.N + tile * 16) + (lane & 1);
+  };
   auto fill_scales = [&](int first) {
     const int gidx = first + (lane >> 1);
     if (gidx < n_items * GI) {
@@ -234,8 +257,12 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, 2) stream_kernel(const Stre
   __syncwarp();
   if (lane == 0 && p.debug_skip < 2)
     for (int s = 0; s < NST && issued < n_items; ++s) issue_next(bar0 + s * 8, ring_s + s * SLOT_BYTES);
-  if (p.debug_skip < 2) fill_scales(0);
-  __syncwarp();
+  // the first fill of the scale cache: requested now, stored after the activations have been
+  // requested as well (a CTA that starts after its predecessor has finished then waits for the
+  // two round trips at the same time, not one after the other)
+  uint4 sc_first = make_uint4(0u, 0u, 0u, 0u);
+  const bool sc_first_valid = p.debug_skip < 2 && (lane >> 1) < n_items * GI;
+  if (sc_first_valid) sc_first = __ldg(scale_src(lane >> 1));
   for (int idx = tid; idx < p.T_own * 16 * MP; idx += NWARPS * 32) sAcc[idx] = 0.f;
 
   TL_STAMP(1);
@@ -329,7 +356,8 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, 2) stream_kernel(const Stre
       *reinterpret_cast<uint4*>(sA + (size_t)m * p.pitch + kk + (kk >> 5) * 8) = v;
     }
   }
-  __syncthreads();  // activations staged, tile sums cleared
+  if (sc_first_valid) *reinterpret_cast<uint4*>(sc_warp + ((lane >> 1) % SCG) * 32 + (lane & 1) * 16) = sc_first;
+  __syncthreads();  // activations staged, tile sums cleared, first scales cached
   TL_STAMP(3);
 
   const int items_per_tile_total = p.KB * NI;
