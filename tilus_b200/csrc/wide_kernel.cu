@@ -144,6 +144,9 @@ wide_kernel(const WideParams p, const __grid_constant__ CUtensorMap tmap_a) {
     // row nl of a K-major 128-byte-swizzled tile: 8-row atoms of 1024 bytes, 16-byte chunk c at c ^ (row % 8)
     const uint32_t row_off = (uint32_t)((nl >> 3) * 1024 + (nl & 7) * 128);
     const uint32_t sw = (uint32_t)(nl & 7);
+    // lanes that take the second unit of a block first (see the loads below): every other pair of
+    // columns for 4-bit types (columns 64 bytes apart), every other column for 8-bit types (128 bytes)
+    const uint32_t usw = B == 4 ? (uint32_t)((nl >> 1) & 1) : (B == 8 ? (uint32_t)(nl & 1) : 0u);
     int g_run = 0;  // groups passed so far (all work items)
     bool good = true;
     TL_DECL(acc_g); TL_DECL(acc_be);
@@ -164,16 +167,31 @@ wide_kernel(const WideParams p, const __grid_constant__ CUtensorMap tmap_a) {
         const __half2 s2 = __half2half2(__ushort_as_half(sbits));
         // all of this column's codes of the group go to registers first, so that the ring stage is
         // free for the next copy while the decode and the stores below run
-        uint32_t wq[2][2 * B];
-        lds_two_units<B>(st + lane_off, wq[0]);
-        lds_two_units<B>(st + lane_off + (uint32_t)(2 * B * 4), wq[1]);
+        // Adjacent columns lie 16 * B bytes apart in the ring stage, so lanes reading the same unit of
+        // their columns collide on the shared-memory banks.  Half of the lanes (usw = 1) therefore
+        // read and process the two units of a block in the opposite order: wq[h][0] is unit usw of
+        // block h, wq[h][1] unit usw ^ 1 (halves the conflicts; the decode does not care which unit it gets).
+        uint32_t wq[2][2][B];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const uint32_t blk = st + lane_off + (uint32_t)(2 * h * B * 4);
+          if constexpr (B == 4 || B == 8) {
+            lds_unit_words<B>(blk + usw * (uint32_t)(B * 4), wq[h][0]);
+            lds_unit_words<B>(blk + (usw ^ 1u) * (uint32_t)(B * 4), wq[h][1]);
+          } else {  // usw = 0: both units with the widest loads
+            uint32_t two[2 * B];
+            lds_two_units<B>(blk, two);
+#pragma unroll
+            for (int q = 0; q < B; ++q) { wq[h][0][q] = two[q]; wq[h][1][q] = two[B + q]; }
+          }
+        }
         if (!nvalid) {
 #pragma unroll
-          for (int q = 0; q < 2 * B; ++q) { wq[0][q] = 0u; wq[1][q] = 0u; }
+          for (int q = 0; q < B; ++q) { wq[0][0][q] = 0u; wq[0][1][q] = 0u; wq[1][0][q] = 0u; wq[1][1][q] = 0u; }
         }
         // order the arrive after the loads have returned: make it depend on the loaded values
         {
-          uint32_t dep = wq[0][0] ^ wq[1][2 * B - 1];
+          uint32_t dep = wq[0][0][0] ^ wq[1][1][B - 1];
           asm volatile("" : "+r"(dep));
           __syncwarp();
           if (lane == 0) mbar_arrive(BAR_ADDR(g_empty, gs));
@@ -181,16 +199,16 @@ wide_kernel(const WideParams p, const __grid_constant__ CUtensorMap tmap_a) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {  // the two 64-row blocks of the group
           uint32_t out[32];
-          unit_decode_scaled<VAR>(wq[h], s2, out);
-          unit_decode_scaled<VAR>(wq[h] + B, s2, out + 16);
+          unit_decode_scaled<VAR>(wq[h][0], s2, out);
+          unit_decode_scaled<VAR>(wq[h][1], s2, out + 16);
           const int bi = 2 * g_run + h;  // running 64-block index
           const int sb = bi % WIDE_SB;
           if (!WAIT_ACC(acc_be, mbar_wait_abortable(BAR_ADDR(b_empty, sb), ((uint32_t)(bi / WIDE_SB) & 1u) ^ 1u, abort_flag))) { good = false; break; }
           const uint32_t dst = b_s + (uint32_t)sb * BSTAGE + row_off;
           if (!(p.debug & 4))
 #pragma unroll
-          for (int c = 0; c < 8; ++c)
-            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst + (((uint32_t)c ^ sw) << 4)),
+          for (int c = 0; c < 8; ++c)  // out[0..15] is unit usw (chunks 4 * usw ..), out[16..31] the other one
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst + (((uint32_t)c ^ sw ^ (usw << 2)) << 4)),
                          "r"(out[4 * c]), "r"(out[4 * c + 1]), "r"(out[4 * c + 2]), "r"(out[4 * c + 3])
                          : "memory");
           // generic-proxy writes must be visible to the tensor core's (async proxy) reads
