@@ -86,3 +86,32 @@ def test_shape_check():
         P.interleave(torch.zeros(256, 16, dtype=torch.uint8), D.uint4b)
     with pytest.raises(ValueError):
         P.interleave(torch.zeros(512, 24, dtype=torch.uint8), D.uint4b)
+
+
+@pytest.mark.parametrize("name", ["int4b", "int3b", "float6_e3m2", "int8"])
+def test_reference_checkpoint_loads_directly(name):
+    """A state dict written by the reference's QuantizedLinear (quantized_weight in its
+    [K/16, N/16, 32*b] tiling + scales, no layout tag) loads into this library's class; a
+    checkpoint with another layout version is refused."""
+    from tilus_b200 import QuantizedLinear, float16
+
+    dt = D.weight_dtype(name)
+    K, N, g = 1024, 48, 128
+    gen = torch.Generator().manual_seed(5)
+    codes = torch.randint(0, 1 << dt.nbits, (K, N), dtype=torch.uint8, generator=gen)
+    scales = (torch.rand(K // g, N, generator=gen) * 0.015 + 0.005).half()
+    ref_sd = {"quantized_weight": P.pack_ref_tiled(codes, dt.nbits), "scales": scales}
+    layer = QuantizedLinear(float16, dt, g, K, N)
+    layer.load_state_dict(ref_sd)
+    assert torch.equal(layer.codes(), codes)
+    assert torch.equal(layer.scales.data, scales)
+    assert int(layer.layout_version) == P.LAYOUT_VERSION
+    # own checkpoints round-trip unchanged
+    other = QuantizedLinear(float16, dt, g, K, N)
+    other.load_state_dict(layer.state_dict())
+    assert torch.equal(other.quantized_weight.data, layer.quantized_weight.data)
+    # unknown layout version: refused
+    bad = dict(layer.state_dict())
+    bad["layout_version"] = torch.tensor(P.LAYOUT_VERSION + 1, dtype=torch.int32)
+    with pytest.raises(RuntimeError, match="layout version"):
+        QuantizedLinear(float16, dt, g, K, N).load_state_dict(bad)

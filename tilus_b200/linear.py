@@ -102,6 +102,30 @@ class QuantizedLinear(nn.Module):
             raise ValueError(f"unknown layout {layout!r}")
         self.load_codes(codes, scales)
 
+    def _load_from_state_dict(self, state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys,
+                              error_msgs):
+        """Checkpoints carry ``layout_version``.  A state dict without it was written by the
+        reference's QuantizedLinear (parameters ``quantized_weight`` + ``scales`` only,
+        examples/quantization/matmul_a16wx.py:455-468): its ``quantized_weight`` is the
+        [K/16, N/16, 32*b] tiling of QuantizedMatmulChangeLayout (:64-98) and is re-packed here,
+        so reference checkpoints load directly.  Any other version is refused."""
+        key_w, key_v = prefix + "quantized_weight", prefix + "layout_version"
+        if key_w in state_dict and key_v not in state_dict:
+            K, N, b = self.in_features, self.out_features, self.w_dtype.nbits
+            stored = state_dict[key_w]
+            if stored.numel() != K * N * b // 8:
+                error_msgs.append(f"{key_w}: expected {K * N * b // 8} bytes, got {stored.numel()}")
+            else:
+                codes = packing.unpack_ref_tiled(stored.detach().cpu().reshape(-1), b, K, N)
+                state_dict = dict(state_dict)
+                state_dict[key_w] = packing.interleave(codes, self.w_dtype)
+                state_dict[key_v] = torch.tensor(packing.LAYOUT_VERSION, dtype=torch.int32)
+        elif key_v in state_dict and int(state_dict[key_v]) != packing.LAYOUT_VERSION:
+            error_msgs.append(f"{key_v}: checkpoint has packed-weight layout version {int(state_dict[key_v])}, "
+                              f"this library reads version {packing.LAYOUT_VERSION}")
+        super()._load_from_state_dict(state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys,
+                                      error_msgs)
+
     def codes(self) -> torch.Tensor:
         """Type-native codes uint8[in_features, out_features] (inverse of load_codes)."""
         return packing.deinterleave(self.quantized_weight.data, self.w_dtype, self.in_features, self.out_features)
