@@ -93,7 +93,16 @@ int b200q_gemm(const void* a, int lda, const void* bq, const void* scales, void*
                int wtype, int zero_point, int group, int act_dtype, void* workspace, size_t workspace_bytes,
                void* stream);
 
-/* Same, with the kernel selection supplied by the caller. */
+/* The same GEMM for a host that keeps activations and results in host memory (no counterpart in
+ * the reference, whose operator takes device tensors): copies A[M, K] from `a_host` (row stride
+ * lda, pinned memory if the copy is to be asynchronous) into `a_staging` (device, M*K fp16), runs
+ * b200q_gemm into `c_staging` (device, M*N fp16) and copies the result to `c_host` (row stride
+ * ldc), all queued on `stream` by this one call; the caller synchronises before it reads c_host. */
+int b200q_gemm_host(const void* a_host, int lda, const void* bq, const void* scales, void* c_host, int ldc, int M,
+                    int N, int K, int wtype, int zero_point, int group, int act_dtype, void* a_staging,
+                    void* c_staging, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Same as b200q_gemm, with the kernel selection supplied by the caller. */
 int b200q_gemm_planned(const void* a, int lda, const void* bq, const void* scales, void* c, int ldc, int M, int N,
                        int K, int wtype, int zero_point, int group, int act_dtype, void* workspace,
                        size_t workspace_bytes, void* stream, const b200q_plan_t* plan);

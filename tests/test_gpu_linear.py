@@ -71,6 +71,32 @@ def test_state_dict_round_trip():
     assert torch.equal(layer(x), other(x))
 
 
+@pytest.mark.parametrize("M", [1, 5, 40, 200])
+def test_forward_host_matches_forward(M):
+    """Host-buffer path (b200q_gemm_host through forward_host): pinned contiguous buffers and
+    strided views of pageable ones give what forward() gives on the same data."""
+    k, n = 1024, 272
+    layer = QuantizedLinear(float16, D.int4b, 128, k, n).cuda()
+    layer.load_and_quantize(torch.randn(n, k))
+    x = torch.randn(M, k).half()
+    want = layer(x.cuda()).cpu().float()
+    scale = float(want.abs().max())
+    got = layer.forward_host(x.pin_memory())
+    torch.cuda.synchronize()
+    assert got.shape == (M, n) and not got.is_cuda
+    assert float((got.float() - want).abs().max()) <= 2e-3 * scale
+    # row-strided views (lda > K, ldc > N)
+    xs = torch.zeros(M, k + 8, dtype=torch.float16)
+    xs[:, :k] = x
+    outs = torch.full((M, n + 16), 7.0, dtype=torch.float16)
+    layer.forward_host(xs[:, :k], outs[:, :n])
+    torch.cuda.synchronize()
+    assert float((outs[:, :n].float() - want).abs().max()) <= 2e-3 * scale
+    assert bool((outs[:, n:] == 7.0).all())
+    with pytest.raises(ValueError):
+        layer.forward_host(x.cuda())
+
+
 @pytest.mark.parametrize("dt", [D.int4b, D.int5b, D.int2b, D.float6_e2m3, D.float5_e2m2, D.float8_e5m2, D.uint4b],
                          ids=lambda d: d.name)
 @pytest.mark.parametrize("group,wdtype", [(32, torch.float32), (128, torch.float16), (512, torch.float32)])

@@ -71,6 +71,7 @@ SYMBOLS = {
     "b200q_gemm_planned": (_i, [_vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp,
                                 ctypes.POINTER(Plan)]),
     "b200q_gemm_static_ws": (_i, [_vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp]),
+    "b200q_gemm_host": (_i, [_vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _sz, _vp]),
     "b200q_static_workspace_limit": (_sz, []),
     "b200q_dequantize": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "b200q_gemm_gather": (_i, [_vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp, ctypes.POINTER(Gather)]),

@@ -615,6 +615,29 @@ int b200q_gemm(const void* a, int lda, const void* bq, const void* scales, void*
                   reinterpret_cast<cudaStream_t>(stream), pl);
 }
 
+// ---- GEMM on host buffers ------------------------------------------------------------------------
+// Activations in (pinned) host memory, result back in host memory: the three steps - copy in, GEMM,
+// copy out - are queued on the stream by one call, through staging buffers the caller owns.
+int b200q_gemm_host(const void* a_host, int lda, const void* bq, const void* scales, void* c_host, int ldc, int M,
+                    int N, int K, int wtype, int zero_point, int group, int act_dtype, void* a_staging,
+                    void* c_staging, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!a_host || !c_host || !a_staging || !c_staging) return ST_INVALID_ARG;
+  if (M < 1 || N < 1 || K < 1 || lda < K || ldc < N) return ST_INVALID_ARG;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  cudaError_t e = lda == K ? cudaMemcpyAsync(a_staging, a_host, (size_t)M * K * 2, cudaMemcpyHostToDevice, st)
+                           : cudaMemcpy2DAsync(a_staging, (size_t)K * 2, a_host, (size_t)lda * 2, (size_t)K * 2, M,
+                                               cudaMemcpyHostToDevice, st);
+  if (e != cudaSuccess) { g_last_cuda_error = (int)e; return ST_CUDA; }
+  const int status = b200q_gemm(a_staging, K, bq, scales, c_staging, N, M, N, K, wtype, zero_point, group, act_dtype,
+                                workspace, workspace_bytes, stream);
+  if (status != ST_OK) return status;
+  e = ldc == N ? cudaMemcpyAsync(c_host, c_staging, (size_t)M * N * 2, cudaMemcpyDeviceToHost, st)
+               : cudaMemcpy2DAsync(c_host, (size_t)ldc * 2, c_staging, (size_t)N * 2, (size_t)N * 2, M,
+                                   cudaMemcpyDeviceToHost, st);
+  if (e != cudaSuccess) { g_last_cuda_error = (int)e; return ST_CUDA; }
+  return ST_OK;
+}
+
 // ---- GEMM without a caller-supplied workspace and without any allocation ----------------------
 // The split-K scratch (status header, arrival counters, fp32 partial sums) lives in this
 // file-scope device array instead of a caller buffer.  Every GPU that loads the library holds

@@ -144,6 +144,17 @@ class QuantizedLinear(nn.Module):
                                  self.group_size, self.in_features, self.out_features, self._ws_need)
         return out if x.dim() == 2 else out.reshape(*x.shape[:-1], self.out_features)
 
+    def forward_host(self, x_host: torch.Tensor, out_host: torch.Tensor | None = None) -> torch.Tensor:
+        """forward() for activations kept in host memory: ``x_host`` [M, in_features] fp16 (pinned
+        for an asynchronous copy) in, ``out_host`` [M, out_features] fp16 out (allocated pinned when
+        not given).  Copy-in, GEMM and copy-out are queued on the layer's current stream by one
+        library call (b200q_gemm_host); synchronise the stream before reading the result."""
+        if out_host is None:
+            out_host = torch.empty(x_host.shape[0], self.out_features, dtype=torch.float16).pin_memory()
+        return ops.linear_forward_host(x_host, out_host, self.quantized_weight.data, self.scales.data,
+                                       self.w_dtype.code, self.zero_point, self.group_size, self.in_features,
+                                       self.out_features, self._ws_need)
+
     def extra_repr(self) -> str:
         return (f"in_features={self.in_features}, out_features={self.out_features}, w_dtype={self.w_dtype.name}, "
                 f"group_size={self.group_size}, zero_point={self.zero_point}")

@@ -132,6 +132,53 @@ def linear_forward(x2: torch.Tensor, bq: torch.Tensor, scales: torch.Tensor, cod
     return out
 
 
+_host_staging: dict = {}
+
+
+def linear_forward_host(x_host: torch.Tensor, out_host: torch.Tensor, bq: torch.Tensor, scales: torch.Tensor,
+                        code: int, zero_point: int, group_size: int, K: int, N: int, ws_need: dict) -> torch.Tensor:
+    """QuantizedLinear.forward_host: activations and result live in host memory (pinned, so that the
+    copies are asynchronous).  One library call queues copy-in, GEMM and copy-out on the current
+    stream of the layer's device; the caller synchronises that stream before reading ``out_host``."""
+    if x_host.is_cuda or out_host.is_cuda:
+        raise ValueError("forward_host takes host tensors (use forward for device tensors)")
+    if x_host.dtype != torch.float16 or out_host.dtype != torch.float16:
+        raise TypeError("activations and result must be float16")
+    if x_host.dim() != 2 or x_host.stride(1) != 1 or x_host.shape[1] != K:
+        raise ValueError(f"x_host must be [M, {K}] with unit inner stride")
+    M = x_host.shape[0]
+    if out_host.dim() != 2 or out_host.stride(1) != 1 or tuple(out_host.shape) != (M, N):
+        raise ValueError(f"out_host must be [{M}, {N}] with unit inner stride")
+    if M == 0:
+        return out_host
+    lib = _lib.load()
+    dev = bq.device
+    need = ws_need.get(M)
+    if need is None:
+        need = lib.b200q_workspace_bytes(M, N, K, code, zero_point, group_size)
+        if need == 0:
+            raise _lib.B200QError(_lib.ST_UNSUPPORTED, f"no kernel for M={M} N={N} K={K}")
+        ws_need[M] = need
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        key = (dev.index, stream)
+        ws = _workspaces.get(key)
+        if ws is None or ws.numel() < need:
+            ws = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=dev)
+            _workspaces[key] = ws
+        stage = _host_staging.get(key)
+        if stage is None or stage[0].numel() < M * K or stage[1].numel() < M * N:
+            stage = (torch.empty(M * K, dtype=torch.float16, device=dev), torch.empty(M * N, dtype=torch.float16, device=dev))
+            _host_staging[key] = stage
+        st = lib.b200q_gemm_host(x_host.data_ptr(), x_host.stride(0), bq.data_ptr(), scales.data_ptr(),
+                                 out_host.data_ptr(), out_host.stride(0), M, N, K, code, zero_point, group_size,
+                                 _lib.ACT_F16, stage[0].data_ptr(), stage[1].data_ptr(), ws.data_ptr(), ws.numel(),
+                                 stream)
+    if st != 0:
+        _lib.check(st)
+    return out_host
+
+
 def dequantize(bq: torch.Tensor, scales: torch.Tensor, w_dtype, group_size: int, zero_point: int = 0) -> torch.Tensor:
     """W[K, N] fp16, the weights the GEMM multiplies by (bit-exact with the reference's
     cast-then-scale)."""
