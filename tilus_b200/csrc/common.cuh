@@ -32,7 +32,7 @@ constexpr int BLOCK_K = 512;
 constexpr size_t WS_HEADER_BYTES = 256;
 inline size_t ws_counter_bytes(int N) { return (((size_t)(N / BLOCK_N) * 4) + 255) / 256 * 256; }
 
-// ---- stream kernel (M <= 16 per launch): one CTA per SM, item-balanced, ring-fed ---------------
+// ---- stream kernel (up to 16 rows per launch; the default for M <= 8): item-balanced, ring-fed --
 constexpr int STREAM_WARPS = 16;
 constexpr int STREAM_SC_GROUPS = 16;  // groups per warp in the shared-memory scale cache (32 bytes each)
 // 128-row groups per ring item: items of 1..2 KB for every bit width
@@ -76,7 +76,7 @@ struct StreamParams {
   GatherArgs ga;
 };
 
-// ---- tcgen05 kernel (any M; used for M > 16) ---------------------------------------------------
+// ---- tcgen05 kernel with the weights in tensor memory (any M; used for M > 128) ----------------
 struct UmmaParams {
   const uint4* bq;       // b200 layout
   const __half* scales;  // [K/group, N]
