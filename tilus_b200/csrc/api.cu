@@ -321,7 +321,7 @@ static int run_umma(const void* a, int lda, const void* bq, const void* scales, 
   const int kblocks = K / 64;
   if (pl.splits < 1 || kblocks % (2 * pl.splits) != 0) return ST_INVALID_ARG;  // whole 128-row groups per split
   if (pl.splits > 1 && m_tiles * n_tiles > N / BLOCK_N) return ST_INVALID_ARG;  // counters region
-  if ((ldc & 1) || (((uintptr_t)scales) & 15)) return ST_INVALID_ARG;  // paired stores, bulk-copied scale rows
+  if ((ldc % 8) != 0 || (((uintptr_t)scales) & 15)) return ST_INVALID_ARG;  // 16-byte stores, bulk-copied scale rows
   const int bits = var_bits(var);
   const int a_stages = umma_a_stages(tm, bits, device_info().max_smem);
   const size_t need = WS_HEADER_BYTES + ws_counter_bytes(N) + (pl.splits > 1 ? (size_t)M * N * sizeof(float) : 0);

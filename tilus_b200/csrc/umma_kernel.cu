@@ -238,23 +238,53 @@ umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
           if (lane == 0) mbar_arrive(BAR_ADDR(d_empty, 0));
         }
         if (m0 + c0 < p.M && !(p.debug & 4)) {
-          // lanes 2i and 2i+1 hold columns n, n+1 of the same 32 rows: exchange so that the even
-          // lane stores the even rows and the odd lane the odd rows, two columns (4 bytes) at a time
-          const bool odd = lane & 1;
+          if (p.splits == 1) {
+            // Lane l holds column n of 32 rows.  Three exchange rounds (lanes l ^ 1, l ^ 2, l ^ 4)
+            // transpose 8 x 8 blocks, so that a lane ends with 8 consecutive columns of 4 rows and
+            // writes each as one 16-byte store: a quarter of the store instructions of 4-byte stores.
+            const bool b0 = lane & 1, b1 = lane & 2, b2 = lane & 4;
+            uint32_t h[16];  // round 1: columns (n & ~1, +1) as half2, row 2 i + b0
 #pragma unroll
-          for (int q = 0; q < 32; q += 2) {
-            const uint32_t mine = odd ? v[q + 1] : v[q];      // row q + odd, own column
-            const uint32_t give = odd ? v[q] : v[q + 1];      // row q + !odd, own column
-            const uint32_t got = __shfl_xor_sync(0xffffffffu, give, 1);  // row q + odd, the other column
-            const float lo = __uint_as_float(odd ? got : mine), hi = __uint_as_float(odd ? mine : got);
-            const int m = m0 + c0 + q + (odd ? 1 : 0);
-            const int ne = n & ~1;
-            if (m < p.M && ne < p.N) {
-              if (p.splits == 1) {
-                *reinterpret_cast<__half2*>(p.c + (size_t)m * p.ldc + ne) = __floats2half2_rn(lo, hi);
-              } else {
-                red_add_v2(p.partial + (size_t)m * p.N + ne, lo, hi);
+            for (int i = 0; i < 16; ++i) {
+              const uint32_t mine = b0 ? v[2 * i + 1] : v[2 * i];
+              const uint32_t give = b0 ? v[2 * i] : v[2 * i + 1];
+              const uint32_t got = __shfl_xor_sync(0xffffffffu, give, 1);
+              h[i] = bits_from_h2(__floats2half2_rn(__uint_as_float(b0 ? got : mine), __uint_as_float(b0 ? mine : got)));
+            }
+            uint32_t w2[8][2];  // round 2: columns (n & ~3 .. +3), row 4 j + 2 b1 + b0
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const uint32_t mine = b1 ? h[2 * j + 1] : h[2 * j];
+              const uint32_t give = b1 ? h[2 * j] : h[2 * j + 1];
+              const uint32_t got = __shfl_xor_sync(0xffffffffu, give, 2);
+              w2[j][0] = b1 ? got : mine;
+              w2[j][1] = b1 ? mine : got;
+            }
+            const int n8 = n_tile * 128 + (nl & ~7);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {  // round 3: columns (n & ~7 .. +7), row 8 k + (lane & 7)
+              const uint32_t m0r = b2 ? w2[2 * k + 1][0] : w2[2 * k][0], m1r = b2 ? w2[2 * k + 1][1] : w2[2 * k][1];
+              const uint32_t g0r = b2 ? w2[2 * k][0] : w2[2 * k + 1][0], g1r = b2 ? w2[2 * k][1] : w2[2 * k + 1][1];
+              const uint32_t r0 = __shfl_xor_sync(0xffffffffu, g0r, 4), r1 = __shfl_xor_sync(0xffffffffu, g1r, 4);
+              const int m = m0 + c0 + 8 * k + (lane & 7);
+              if (m < p.M && n8 < p.N) {
+                uint4 o;
+                o.x = b2 ? r0 : m0r; o.y = b2 ? r1 : m1r; o.z = b2 ? m0r : r0; o.w = b2 ? m1r : r1;
+                *reinterpret_cast<uint4*>(p.c + (size_t)m * p.ldc + n8) = o;
               }
+            }
+          } else {
+            // split-K: lanes 2i and 2i+1 exchange so that each adds two columns (8 bytes) of a row
+            const bool odd = lane & 1;
+#pragma unroll
+            for (int q = 0; q < 32; q += 2) {
+              const uint32_t mine = odd ? v[q + 1] : v[q];      // row q + odd, own column
+              const uint32_t give = odd ? v[q] : v[q + 1];      // row q + !odd, own column
+              const uint32_t got = __shfl_xor_sync(0xffffffffu, give, 1);  // row q + odd, the other column
+              const float lo = __uint_as_float(odd ? got : mine), hi = __uint_as_float(odd ? mine : got);
+              const int m = m0 + c0 + q + (odd ? 1 : 0);
+              const int ne = n & ~1;
+              if (m < p.M && ne < p.N) red_add_v2(p.partial + (size_t)m * p.N + ne, lo, hi);
             }
           }
         }
