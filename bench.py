@@ -489,7 +489,7 @@ def run_b200(args) -> None:
     # ---- extra sweep -------------------------------------------------------------------
     extra = {}
     if world == 1 and not args.no_sweep:
-        del graph, layers, acts, dev_in
+        del graph, layers, acts
         torch.cuda.empty_cache()
         hbm = peaks["hbm_gbs"]
 
