@@ -1,7 +1,8 @@
 """Benchmark of the weight-only quantized matmul hot path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
-                    [--no-sweep] [--no-prefill] [--stack] [--profile-case decode|prefill|batch16|batch32]
+                    [--no-sweep] [--no-prefill] [--no-stack] [--stack]
+                    [--profile-case decode|prefill|batch16|batch32]
 
 Headline workload (one GPU): decode GEMV, M=1, K=N=8192, uint4 codes with zero point 8,
 group 128, fp16 scales - the "u4 g128" decode configuration the metric is quoted on.
@@ -15,17 +16,21 @@ collective on the data path) and `value` is the aggregate.
 The JSON line also carries: `roofline` (HBM, for the GEMV kernel), `e2e` (same metric
 through QuantizedLinear.forward with pinned host activations copied in and the result
 copied out every step), `cpu_baseline` (the CPU oracle - the reference's PyTorch
-dequantize + matmul semantics - timed on this host), `clocks`, `gpu_launches`, and an
+dequantize + matmul semantics - timed on this host), `clocks`, `gpu_launches`,
+`headline_shapes` (the metric's three shapes M = 1 / 16 / 4096 against their rooflines),
+`stack` (the Llama-3-8B-shaped decode linear stack, N-sharded over the ranks of this run
+with an all-gather per layer: NCCL and fused into the GEMV kernel, strong scaling) and an
 `extra` sweep: the other bit widths at M=1, M=16, the M=16 K=N=4096 configuration, the
 per-channel float6 / int3 batch sweep, the Llama-3-8B layer shapes at M in {1, 8, 32, 64},
 the reference example's own table (K=4096, N=12288, eight weight types, M in {1, 16, 4096,
-4097}) and the M=4096 prefill GEMM in TFLOP/s.
+4097}) and the M=4096 prefill GEMM in TFLOP/s.  Every sweep entry is checked against the
+oracle on sampled columns (`rel_err`).
 
 `--impl reference` times the CPU dequantize + matmul path alone (the reference operator's
 semantics on the host cores), on the same workload and metric.
 
-`--stack` times the Llama-3-8B-shaped decode linear stack, N-sharded over the ranks with an
-NCCL all-gather of every layer's output (strong scaling), for M in {1, 8, 32, 64}.
+`--stack` runs only the Llama-3-8B-shaped decode linear stack (the `stack` entry of the main
+line) and prints it as a line of its own.
 
 `--profile-case X` runs a few plain launches of one kernel on a problem larger than L2 and
 prints its CUDA-event time: the command line used for the ncu captures under profiles/.
@@ -44,6 +49,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
+import numpy as np  # noqa: E402
 import torch  # noqa: E402
 
 M, K, N, GROUP, NBITS = 1, 8192, 8192, 128, 4
@@ -51,9 +57,17 @@ WORKLOAD = "decode_gemv_u4_g128_M1_K8192_N8192"
 METRIC = "quant-GEMM HBM GB/s (u4 g128, M=1, K=N=8192)"
 R_LAYERS = 10   # distinct layers per pass: 10 x 33.5 MB of weights = 335 MB > 126 MB L2
 ROUNDS = 10     # passes per graph: 100 launches per replay
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the headline kernel, from the
-# ncu capture summarised in profiles/stream_kernel_u4_m1_k8192_n8192.md
-DECODE_DRAM_TRAFFIC_BYTES = 34_660_864
+
+
+def _decode_dram_traffic():
+    """dram__bytes_read.sum + dram__bytes_write.sum of one launch of the headline kernel, as recorded
+    with the ncu capture it came from (None when no capture is on record)."""
+    path = os.path.join(ROOT, "profiles", "decode_dram_traffic.json")
+    try:
+        with open(path) as f:
+            return json.load(f)
+    except (OSError, ValueError):
+        return None
 
 
 def _peaks():
@@ -115,13 +129,14 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def _cpu_gemv_seconds(prob, repeats: int) -> float:
-    """The oracle's dequantize + matmul (reference semantics) on the host cores."""
+def _cpu_gemv_seconds(prob, repeats: int, warm: bool = True) -> float:
+    """The oracle's dequantize + matmul (reference semantics) on the host cores: seconds per call."""
     from oracle import quant_oracle as qo
 
     torch.set_num_threads(os.cpu_count() or 1)
     a, codes, scales = prob["a"].numpy(), prob["codes"].numpy(), prob["scales"].numpy()
-    qo.quantized_matmul(a, codes, scales, prob["dtype"], prob["group_size"], prob["zero_point"])  # warm
+    if warm:
+        qo.quantized_matmul(a, codes, scales, prob["dtype"], prob["group_size"], prob["zero_point"])
     t0 = time.perf_counter()
     for _ in range(repeats):
         qo.quantized_matmul(a, codes, scales, prob["dtype"], prob["group_size"], prob["zero_point"])
@@ -136,12 +151,8 @@ def run_reference(args) -> None:
         return
     prob = synth.make_problem(M, N, K, dtypes.uint4b, GROUP, seed=0)
     nbytes = synth.gemm_bytes(M, N, K, NBITS, GROUP)
-    for _ in range(max(args.warmup, 1)):
-        _cpu_gemv_seconds(prob, 1)
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        _cpu_gemv_seconds(prob, 1)
-    dt = (time.perf_counter() - t0) / args.steps
+    _cpu_gemv_seconds(prob, max(args.warmup, 1), warm=False)      # warm-up steps: one oracle call each
+    dt = _cpu_gemv_seconds(prob, args.steps, warm=False)          # a step = one oracle call
     val = nbytes / dt / 1e9
     cores = os.cpu_count() or 1
     print(json.dumps({
@@ -167,16 +178,18 @@ def _time_graph(graph, reps: int) -> float:
     return e0.elapsed_time(e1)
 
 
-def _make_layers(dt, n, k, group, count, dev, seed=0, scale_range=(0.005, 0.02), distinct=True):
+def _make_layers(dt, n, k, group, count, dev, seed=0, scale_range=(0.005, 0.02), distinct=True, prob0=None):
     """`count` QuantizedLinear layers [k -> n] on the device.  distinct=False generates one
-    synthetic problem and gives every layer its own copy of it (same timing, faster set-up)."""
+    synthetic problem (or takes `prob0`) and gives every layer its own copy of it (same timing,
+    faster set-up)."""
     from tilus_b200 import QuantizedLinear, float16, synth
 
     layers = []
     first = None
     for i in range(count):
         if distinct or first is None:
-            prob = synth.make_problem(1, n, k, dt, group, seed=seed + i, scale_range=scale_range)
+            prob = prob0 if (prob0 is not None and not distinct) else \
+                synth.make_problem(1, n, k, dt, group, seed=seed + i, scale_range=scale_range)
             layer = QuantizedLinear(float16, dt, group, k, n, zero_point=prob["zero_point"]).to(dev)
             layer.load_codes(prob["codes"].to(dev), prob["scales"].to(dev))
             if first is None:
@@ -215,23 +228,38 @@ def _layer_count(dt, n, k):
     return max(2, min(40, (300 * 2**20 + wbytes - 1) // wbytes))
 
 
+def _spot_check(prob, a_cpu, got, cols) -> float:
+    """rel-err of the kernel's output against the oracle on sampled columns."""
+    from oracle import quant_oracle as qo
+
+    ref = qo.quantized_matmul(a_cpu.numpy(), prob["codes"][:, cols].numpy(), prob["scales"][:, cols].numpy(),
+                              prob["dtype"], prob["group_size"], prob["zero_point"]).astype("float32")
+    out = got[:, cols.to(got.device)].float().cpu().numpy()
+    return float(abs(out - ref).max() / max(abs(ref).max(), 1e-30))
+
+
 def _sweep_shape(dt, n, k, group, ms_list, dev, reps, scale_range=(0.005, 0.02)):
-    """us / GB/s / TFLOP/s of one layer shape for each M, layers rotated so weights stream from HBM."""
+    """us / GB/s / TFLOP/s of one layer shape for each M, layers rotated so weights stream from HBM.
+    All layers of a shape hold the same synthetic weights (own copies, so the bytes still stream
+    from HBM); what was timed is compared with the oracle on 64 sampled columns."""
     from tilus_b200 import synth
 
     count = _layer_count(dt, n, k)
-    layers = _make_layers(dt, n, k, group, count, dev, seed=100, scale_range=scale_range, distinct=False)
+    prob = synth.make_problem(1, n, k, dt, group, seed=100, scale_range=scale_range)
+    layers = _make_layers(dt, n, k, group, count, dev, seed=100, scale_range=scale_range, distinct=False, prob0=prob)
+    cols = torch.arange(3, n, max(1, n // 64))[:64]
     out = {}
     for m in ms_list:
         acts = _acts(m, k, count, dev, seed=m)
         rounds = max(1, 40 // count) if m <= 64 else 1
-        g, _ = _capture(layers, acts, rounds)
+        g, outs = _capture(layers, acts, rounds)
         _time_graph(g, 3)
         ms = _time_graph(g, reps) / (reps * count * rounds)
         nbytes = synth.gemm_bytes(m, n, k, dt.nbits, group)
         out[m] = {"us": ms * 1e3, "gbs": nbytes / (ms * 1e-3) / 1e9,
-                  "tflops": synth.gemm_flops(m, n, k) / (ms * 1e-3) / 1e12}
-        del g, acts
+                  "tflops": synth.gemm_flops(m, n, k) / (ms * 1e-3) / 1e12,
+                  "rel_err": _spot_check(prob, acts[0].cpu(), outs[0], cols)}
+        del g, acts, outs
     del layers
     torch.cuda.empty_cache()
     return out
@@ -271,29 +299,27 @@ def run_profile_case(args) -> None:
                       "us_per_launch_plain_stream": us}))
 
 
-def run_stack(args) -> None:
+def measure_stack(world, rank, dev, steps, warmup, batches=(1, 8, 32, 64)) -> dict:
     """Llama-3-8B-shaped decode linear stack, N-sharded over the ranks, all-gather of every layer's
     output: 32 x {qkv 4096->6144, o 4096->4096, gate_up 4096->28672, down 14336->4096}, uint4 g128
-    weights, batch M in {1, 8, 32, 64}.  Strong scaling: the model is fixed, the shards shrink with N.
-    A step = one pass over the 128 linears (+ 128 all-gathers), replayed from one CUDA graph when the
-    collectives can be captured, else launched eagerly."""
+    weights, batch M in {1, 8, 32, 64}.  Strong scaling: the model is fixed, the shards shrink with the
+    number of ranks.  A step = one pass over the 128 linears, replayed from one CUDA graph.  Two forms
+    of the all-gather: `nccl` (a collective per layer) and - for M <= 16 - `fused` (the GEMV kernel
+    stores its columns into every rank's row buffer over NVLink and raises flags).  Before timing the
+    fused rows are compared with the NCCL path's and, for the first block of four linears, both with
+    the oracle.  The process group must be up when world > 1."""
     import torch.distributed as dist
 
+    from oracle import quant_oracle as qo
     from tilus_b200 import dtypes, float16, packing, sharded, synth
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    dev = torch.device("cuda", local_rank)
-    torch.cuda.set_device(dev)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
     dt = dtypes.uint4b
     shapes = [("qkv", 4096, 6144), ("o", 4096, 4096), ("gate_up", 4096, 28672), ("down", 14336, 4096)]
     n_layers = 32
-    protos = {}
+    protos, probs = {}, {}
     for name, k_in, n_out in shapes:  # one synthetic weight per shape, one device copy per layer
         prob = synth.make_problem(1, n_out, k_in, dt, GROUP, seed=7)
+        probs[name] = prob
         n0, n1 = sharded.shard_range(n_out, world, rank)
         protos[name] = (packing.interleave(prob["codes"][:, n0:n1].contiguous().to(dev), dt),
                         prob["scales"][:, n0:n1].contiguous().to(dev), prob["zero_point"])
@@ -309,86 +335,140 @@ def run_stack(args) -> None:
     del protos
     weight_bytes = sum(k * n // 2 + (k // GROUP) * n * 2 for _, k, n in shapes) * n_layers // world
 
-    def step(x):
-        for qkv, o, gate_up, down in layers:
+    def step(x, blocks=layers):
+        for qkv, o, gate_up, down in blocks:
             h = qkv(x)
             h = o(h[:, :4096])
             h = gate_up(h)
             x = down(h[:, :14336])
         return x
 
-    # --fused: the all-gather is done by the GEMV kernel itself (stores into every rank's row buffer
-    # over NVLink, flags instead of a collective); covers M <= 16, wider batches use the NCCL path
-    ctx = sharded.PeerGather.create(16, 28672, dev) if args.fused else None
+    ctx = sharded.PeerGather.create(16, 28672, dev)
 
-    def step_fused(x):
+    def step_fused(x, blocks=layers):
         row = x
-        for qkv, o, gate_up, down in layers:
+        for qkv, o, gate_up, down in blocks:
             row = ctx.gemm(row, qkv)
             row = ctx.gemm(row.cols(0, 4096), o)
             row = ctx.gemm(row, gate_up)
             row = ctx.gemm(row.cols(0, 14336), down)
         return row
 
-    results = {}
-    graphs = []
-    for m in (1, 8, 32, 64):
-        x = (torch.randn(m, 4096, generator=torch.Generator().manual_seed(m)) * 0.05).to(torch.float16).to(dev)
-        fn = step_fused if (ctx is not None and m <= 16) else step
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            for _ in range(2):
-                fn(x)
-        torch.cuda.synchronize()
+    w_ref = {}
+
+    def oracle_block(x_cpu):  # the first block of four linears, fp16 between them
+        def mm(name, h):
+            if name not in w_ref:
+                pr = probs[name]
+                w_ref[name] = qo.dequantize(pr["codes"].numpy(), pr["scales"].numpy(), dt, GROUP, pr["zero_point"])
+            return qo.gemm_fp16(h, w_ref[name])
+
+        h = mm("qkv", x_cpu.numpy())[:, :4096]
+        h = mm("o", np.ascontiguousarray(h))
+        h = mm("gate_up", h)[:, :14336]
+        return mm("down", np.ascontiguousarray(h)).astype("float32")
+
+    def rel(a, b):
+        return float(abs(a - b).max() / max(abs(b).max(), 1e-30))
+
+    def barrier():
         if world > 1:
             dist.barrier()
-        mode = "cuda graph"
-        try:
+        torch.cuda.synchronize()
+
+    results, graphs = {}, []
+    for m in batches:
+        x = (torch.randn(m, 4096, generator=torch.Generator().manual_seed(m)) * 0.05).to(torch.float16).to(dev)
+        modes = ["nccl" if world > 1 else "single"] + (["fused"] if m <= 16 else [])
+        entry = {}
+        # ---- correctness of what is timed (all device work first: a rank that computed the oracle
+        # in between would keep its peers' fused kernels waiting beyond their bounded wait) ----
+        barrier()
+        y_nccl = step(x).float().cpu().numpy()                      # full stack, NCCL gather
+        y_blk = step(x, layers[:1]).float().cpu().numpy()           # first block
+        if "fused" in modes:
+            barrier()
+            y_fused = ctx.fetch(step_fused(x)).float().cpu().numpy()
+            y_fblk = ctx.fetch(step_fused(x, layers[:1])).float().cpu().numpy()
+            entry["fused_vs_nccl_rel_err"] = rel(y_fused, y_nccl)
+        barrier()
+        if rank == 0:
+            want = oracle_block(x.cpu())
+            entry["block_vs_oracle_rel_err"] = rel(y_blk, want)
+            if "fused" in modes:
+                entry["fused_block_vs_oracle_rel_err"] = rel(y_fblk, want)
+        barrier()
+        for mode in modes:
+            fn = step_fused if mode == "fused" else step
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                fn(x)
+            barrier()
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, stream=side):
-                out = fn(x)  # noqa: F841
-            run = g.replay
+                fn(x)
             graphs.append(g)
-        except Exception:  # collectives that cannot be captured: launch eagerly
+            for _ in range(max(warmup, 3)):
+                g.replay()
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                g.replay()
+            e1.record()
             torch.cuda.synchronize()
-            mode = "eager"
-            run = lambda: fn(x)  # noqa: E731
-        for _ in range(max(args.warmup, 3)):
-            run()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(args.steps):
-            run()
-        e1.record()
-        torch.cuda.synchronize()
-        t = torch.tensor([e0.elapsed_time(e1) / args.steps], dtype=torch.float64, device=dev)
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-        results[f"M{m}"] = {"ms_per_step": round(ms, 4), "tokens_per_s": round(m / (ms * 1e-3), 1),
-                            "us_per_linear": round(ms * 1e3 / (4 * n_layers), 2),
-                            "per_gpu_weight_gbs": round(weight_bytes / (ms * 1e-3) / 1e9, 1), "launch": mode,
-                            "gather": "fused in the GEMV kernel" if fn is step_fused else ("nccl all-gather" if world > 1 else "none")}
+            t = torch.tensor([e0.elapsed_time(e1) / steps], dtype=torch.float64, device=dev)
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+            entry[mode] = {"ms_per_step": round(ms, 4), "tokens_per_s": round(m / (ms * 1e-3), 1),
+                           "us_per_linear": round(ms * 1e3 / (4 * n_layers), 2),
+                           "per_gpu_weight_gbs": round(weight_bytes / (ms * 1e-3) / 1e9, 1)}
+            barrier()
+        results[f"M{m}"] = entry
+    # graphs that captured collectives go before the communicator does
+    for g in graphs:
+        g.reset()
+    del graphs
+    barrier()
+    ctx.close()
+    return {"workload": "llama3_8b_linear_stack_u4_g128", "layers": n_layers, "linears_per_step": 4 * n_layers,
+            "scaling": "strong", "unit": "ms per 128-linear step", "per_gpu_weight_bytes": weight_bytes,
+            "gather": {"nccl": "ncclAllGather per layer (M > 1: + one permute copy)",
+                       "fused": "peer stores from the GEMV kernel + per-rank flags (b200q_gemm_gather), M <= 16"},
+            "results": results}
+
+
+def _teardown_guard(seconds: float = 60.0):
+    """The line has been printed; if tearing the communicator down blocks (seen once with graphs that
+    had captured collectives), leave after `seconds` so that the launcher does not hang."""
+    import threading
+
+    t = threading.Timer(seconds, lambda: os._exit(0))
+    t.daemon = True
+    t.start()
+
+
+def run_stack(args) -> None:
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    res = measure_stack(world, rank, dev, args.steps, args.warmup)
     if rank == 0:
         print(json.dumps({"metric": "Llama-3-8B-shaped decode linear stack, N-sharded, all-gather per layer",
-                          "unit": "ms per 128-linear step", "n_gpus": world, "steps": args.steps,
-                          "scaling": "strong", "dtype": "f16", "data": "synthetic",
-                          "config": {"workload": "llama3_8b_linear_stack_u4_g128", "layers": n_layers,
-                                     "per_gpu_weight_bytes": weight_bytes},
-                          "results": results}), flush=True)
+                          "n_gpus": world, "steps": args.steps, "dtype": "f16", "data": "synthetic", **res}),
+              flush=True)
     if world > 1:
-        # graphs that captured NCCL kernels must be gone before the communicator is; tearing the
-        # communicator down under them has been seen to block, so the ranks leave without it
-        del run, graphs
-        torch.cuda.synchronize()
+        _teardown_guard()
         dist.barrier()
-        torch.cuda.synchronize()
-        sys.stdout.flush()
-        os._exit(0)
+        dist.destroy_process_group()
 
 
 def run_b200(args) -> None:
@@ -464,8 +544,70 @@ def run_b200(args) -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_val = world * nbytes / float(t.item()) / 1e9
 
+    hbm = peaks["hbm_gbs"]
+
+    def build_line(stack, cpu_baseline, extra, sweep_clocks, parity, headline_shapes):
+        achieved = nbytes / per_launch_s / 1e9
+        traffic = _decode_dram_traffic()
+        return {
+            "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "layers_per_pass": R_LAYERS, "passes_per_graph": ROUNDS,
+                       "replays_per_step": inner,
+                       "l2": f"inputs larger than L2: {R_LAYERS} distinct weight sets, "
+                             f"{R_LAYERS * K * N // 2 // 2**20} MiB, rotated",
+                       "sharding": "replicas: one GEMV of this shape per GPU, no data-path collective "
+                                   "(the sharded workload with its all-gather is `stack`)",
+                       "sweep_weights": "every layer of a sweep shape holds its own copy of one synthetic weight"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s",
+                         "frac": achieved / hbm,
+                         "traffic": traffic["dram_bytes_per_launch"] if traffic else None,
+                         "traffic_capture": {k: traffic[k] for k in ("commit", "command")} if traffic else None,
+                         "peak_source": peaks["source"], "kernel": "stream_kernel<u4 zp8, MT=1>",
+                         "bytes_per_launch": nbytes, "us_per_launch": per_launch_s * 1e6},
+            "cpu_baseline": cpu_baseline,
+            "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": R_LAYERS * M * K * 2,
+                    "d2h_bytes_per_step": R_LAYERS * M * N * 2, "us_per_call": e2e_s * 1e6},
+            "gpu_launches": launches,
+            "clocks": clocks,
+            "sweep_clocks": sweep_clocks,
+            "parity": parity,
+            "headline_shapes": headline_shapes,
+            "stack": stack,
+            "extra": extra,
+        }
+
+    prob0_a = acts[0].cpu()
+    out0 = outs[0].float().cpu().numpy()
+    host0 = host_out[0].float().numpy()  # what the end-to-end path left in host memory for the same layer
+    del graph, layers, acts, outs
+    torch.cuda.empty_cache()
+
+    # ---- the N-sharded decode stack (strong scaling over the ranks of this run) -----------
+    stack = None
+    if not args.no_stack:
+        import threading
+
+        def bail():  # a rank stuck in the stack's collectives must not keep the headline number from being reported
+            if rank == 0:
+                print(json.dumps(build_line({"error": "no result within 300 s"}, None, {}, None, None, None)), flush=True)
+            os._exit(0)
+
+        watchdog = threading.Timer(300.0, bail)
+        watchdog.daemon = True
+        watchdog.start()
+        try:
+            stack = measure_stack(world, rank, dev, max(3, min(args.steps, 10)), args.warmup)
+        except Exception as exc:  # the headline line must still be printed
+            stack = {"error": f"{type(exc).__name__}: {exc}"}
+        finally:
+            watchdog.cancel()
+        torch.cuda.empty_cache()
+
     if rank != 0:
         if world > 1:
+            _teardown_guard()
             dist.barrier()
             dist.destroy_process_group()
         return
@@ -474,33 +616,35 @@ def run_b200(args) -> None:
     from oracle import quant_oracle as qo
 
     prob0 = synth.make_problem(1, N, K, dt, GROUP, seed=0)
-    ref = qo.quantized_matmul(acts[0].cpu().numpy(), prob0["codes"].numpy(), prob0["scales"].numpy(), dt, GROUP, 8)
-    got = outs[0].float().cpu().numpy()
-    rel = float(abs(got - ref.astype("float32")).max() / abs(ref.astype("float32")).max())
-    got_host = host_out[0].float().numpy()  # what the end-to-end path left in host memory for the same layer
-    rel_e2e = float(abs(got_host - ref.astype("float32")).max() / abs(ref.astype("float32")).max())
+    ref = qo.quantized_matmul(prob0_a.numpy(), prob0["codes"].numpy(), prob0["scales"].numpy(), dt, GROUP, 8)
+    rel = float(abs(out0 - ref.astype("float32")).max() / abs(ref.astype("float32")).max())
+    rel_e2e = float(abs(host0 - ref.astype("float32")).max() / abs(ref.astype("float32")).max())
 
     # ---- CPU baseline (bounded sample) -----------------------------------------------
-    prob0["a"] = acts[0].cpu()
+    prob0["a"] = prob0_a
     cpu_s = _cpu_gemv_seconds(prob0, 5)
     cpu_baseline = {"value": nbytes / cpu_s / 1e9, "unit": "GB/s", "cores": os.cpu_count() or 1, "kind": "port",
                     "sample": "5 full M=1 K=N=8192 u4 g128 dequantize+matmul calls (oracle, torch CPU threads)"}
 
     # ---- extra sweep -------------------------------------------------------------------
     extra = {}
+    sweep_clocks = None
+    headline_shapes = {"M1_K8192_N8192_u4": {"us": round(per_launch_s * 1e6, 3), "gbs": round(nbytes / per_launch_s / 1e9, 1),
+                                             "hbm_frac": round(nbytes / per_launch_s / 1e9 / hbm, 4), "rel_err": rel}}
     if world == 1 and not args.no_sweep:
-        del graph, layers, acts
-        torch.cuda.empty_cache()
-        hbm = peaks["hbm_gbs"]
+        sweep_sampler = ClockSampler(local_rank)
+        sweep_sampler.start()
 
         def mem_entry(r):
-            return {"us": round(r["us"], 3), "gbs": round(r["gbs"], 1), "hbm_frac": round(r["gbs"] / hbm, 4)}
+            return {"us": round(r["us"], 3), "gbs": round(r["gbs"], 1), "hbm_frac": round(r["gbs"] / hbm, 4),
+                    "rel_err": float(f"{r['rel_err']:.3g}")}
 
         for d in (dtypes.uint1b, dtypes.uint2b, dtypes.uint3b, dtypes.uint6b, dtypes.uint8):
             extra[f"decode_{d.short_name}_M1"] = mem_entry(_sweep_shape(d, N, K, GROUP, [1], dev, 10)[1])
-        r = _sweep_shape(dtypes.uint4b, 8192, 8192, GROUP, [8, 16], dev, 10)
-        extra["decode_u4_M8"] = mem_entry(r[8])
-        extra["decode_u4_M16"] = mem_entry(r[16])
+        r = _sweep_shape(dtypes.uint4b, 8192, 8192, GROUP, [8, 16, 32, 64], dev, 10)
+        for m in (8, 16, 32, 64):
+            extra[f"decode_u4_M{m}"] = mem_entry(r[m])
+        headline_shapes["M16_K8192_N8192_u4"] = extra["decode_u4_M16"]
         extra["config0_u4_M16_K4096_N4096"] = mem_entry(_sweep_shape(dtypes.uint4b, 4096, 4096, GROUP, [16], dev, 10)[16])
         for d in (dtypes.float6_e3m2, dtypes.int3b):
             r = _sweep_shape(d, 4096, 4096, 4096, [1, 4, 16, 64, 256], dev, 10, scale_range=(0.5, 2.0))
@@ -518,7 +662,8 @@ def run_b200(args) -> None:
             ms_list = [1, 16] if args.no_prefill else [1, 16, 4096, 4097]
             r = _sweep_shape(d, 12288, 4096, GROUP, ms_list, dev, 5)
             extra[f"example_table_{d.short_name}_K4096_N12288"] = {
-                f"M{m}": {"us": round(v["us"], 2), "tflops": round(v["tflops"], 2), "gbs": round(v["gbs"], 1)}
+                f"M{m}": {"us": round(v["us"], 2), "tflops": round(v["tflops"], 2), "gbs": round(v["gbs"], 1),
+                          "rel_err": float(f"{v['rel_err']:.3g}")}
                 for m, v in r.items()}
         if not args.no_prefill:
             r = _sweep_shape(dtypes.int4b, 28672, 8192, GROUP, [4096], dev, 3)[4096]
@@ -526,32 +671,16 @@ def run_b200(args) -> None:
                 "ms": round(r["us"] / 1e3, 4), "tflops": round(r["tflops"], 1),
                 "tensor_frac_of_measured_burst": round(r["tflops"] / peaks["tflops"], 4) if peaks["tflops"] else None,
                 "tensor_frac_of_measured_sustained":
-                    round(r["tflops"] / peaks["tflops_sustained"], 4) if peaks["tflops_sustained"] else None}
+                    round(r["tflops"] / peaks["tflops_sustained"], 4) if peaks["tflops_sustained"] else None,
+                "rel_err": float(f"{r['rel_err']:.3g}")}
+            headline_shapes["M4096_K8192_N28672_i4"] = extra["prefill_i4_M4096_K8192_N28672"]
+        sweep_clocks = sweep_sampler.stop()
 
-    achieved = nbytes / per_launch_s / 1e9
-    line = {
-        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "layers_per_pass": R_LAYERS, "passes_per_graph": ROUNDS,
-                   "replays_per_step": inner,
-                   "l2": f"inputs larger than L2: {R_LAYERS} distinct weight sets, "
-                         f"{R_LAYERS * K * N // 2 // 2**20} MiB, rotated",
-                   "sharding": "one column shard of this shape per GPU, no data-path collective"},
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                     "frac": achieved / peaks["hbm_gbs"], "traffic": DECODE_DRAM_TRAFFIC_BYTES,
-                     "peak_source": peaks["source"], "kernel": "stream_kernel<u4 zp8, MT=1>",
-                     "bytes_per_launch": nbytes, "us_per_launch": per_launch_s * 1e6},
-        "cpu_baseline": cpu_baseline,
-        "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": R_LAYERS * M * K * 2,
-                "d2h_bytes_per_step": R_LAYERS * M * N * 2, "us_per_call": e2e_s * 1e6},
-        "gpu_launches": launches,
-        "clocks": clocks,
-        "parity": {"rel_err_vs_oracle": rel, "e2e_rel_err_vs_oracle": rel_e2e, "tolerance": 1e-2},
-        "extra": extra,
-    }
-    print(json.dumps(line))
+    line = build_line(stack, cpu_baseline, extra, sweep_clocks,
+                      {"rel_err_vs_oracle": rel, "e2e_rel_err_vs_oracle": rel_e2e, "tolerance": 1e-2}, headline_shapes)
+    print(json.dumps(line), flush=True)
     if world > 1:
+        _teardown_guard()
         dist.barrier()
         dist.destroy_process_group()
 
@@ -566,8 +695,7 @@ def main():
     ap.add_argument("--no-prefill", action="store_true", help="skip the M=4096 prefill entry of the sweep")
     ap.add_argument("--stack", action="store_true",
                     help="time the N-sharded Llama-3-8B-shaped decode linear stack (all-gather per layer) instead")
-    ap.add_argument("--fused", action="store_true",
-                    help="with --stack: all-gather fused into the GEMV kernel (peer stores + flags) for M <= 16")
+    ap.add_argument("--no-stack", action="store_true", help="skip the N-sharded decode stack")
     ap.add_argument("--profile-case", default=None, choices=["decode", "batch16", "batch32", "prefill"],
                     help="run a few plain launches of one kernel (for ncu) instead of the benchmark")
     args = ap.parse_args()

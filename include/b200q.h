@@ -44,15 +44,16 @@ enum {
  * floats_subbyte.py:89-109). */
 #define B200Q_WTYPE(kind, nbits, e, m) (((kind) << 16) | ((nbits) << 8) | ((e) << 4) | (m))
 
-/* Activation / output dtype tags. */
-enum { B200Q_F16 = 0 };
+/* Activation dtype tags: the type of A, of the scales and of C, as the reference's a_dtype
+ * (float16 or bfloat16, examples/quantization/matmul_a16wx.py:35-41, :418-419). */
+enum { B200Q_F16 = 0, B200Q_BF16 = 1 };
 
 /* Kernel selection made by the static shape table (replaces the reference's autotuner,
  * python/tilus/lang/instantiated_script.py:700-801).  Filled by b200q_plan; may be edited
  * and passed to b200q_gemm_planned for experiments. */
 typedef struct b200q_plan {
-  int32_t kernel;        /* 2 = mma.sync stream kernel (M <= 8; up to 16 rows when forced), 3 = tcgen05 kernel with
-                            the weights on the 256-column side (M <= 128), 1 = tcgen05 kernel for larger M */
+  int32_t kernel;        /* 2 = mma.sync stream kernel (M <= 16), 3 = tcgen05 kernel with the weights on the
+                            256-column side (M <= 128), 1 = tcgen05 kernel for larger M */
   int32_t m_tiles;       /* kernel 2: 8-row activation tiles per pass (1 or 2); kernels 1, 3: tiles along M */
   int32_t splits;        /* k chunks (kernel 2) / split-K factor (kernels 1, 3) */
   int32_t cluster;       /* 1 (no kernel launches clusters) */
@@ -64,7 +65,7 @@ typedef struct b200q_plan {
   int32_t warps;         /* warps per CTA (output only) */
   int32_t passes;        /* launches needed to cover M */
   int32_t pdl;           /* 1: launch with programmatic stream serialization (overlap with the previous kernel) */
-  int32_t debug;         /* 0; non-zero values switch parts of the kernels off for timing experiments */
+  int32_t reserved;      /* 0 */
   uint64_t workspace_bytes;
 } b200q_plan_t;
 
@@ -86,18 +87,22 @@ int b200q_plan(int M, int N, int K, int wtype, int zero_point, int group, b200q_
  * python/tilus/hidet/include/tilus/context.h:97-117).  One workspace per stream. */
 size_t b200q_workspace_bytes(int M, int N, int K, int wtype, int zero_point, int group);
 
-/* C = A x dequant(Bq).  a: fp16 [M, K] (row stride lda elements), bq: b200-packed weights,
- * scales: fp16 [K/group, N], c: fp16 [M, N] (row stride ldc).  Replaces tilus_launch for
- * QuantizedMatmul (examples/quantization/matmul_a16wx.py:231-405). */
+/* C = A x dequant(Bq).  a: [M, K] (row stride lda elements), bq: b200-packed weights,
+ * scales: [K/group, N], c: [M, N] (row stride ldc), all three of dtype act_dtype.  Replaces
+ * tilus_launch for QuantizedMatmul (examples/quantization/matmul_a16wx.py:231-405).  With bf16
+ * and M <= 16 the activations are converted to fp16 for the tensor core: exactly, except that
+ * magnitudes above 65504 saturate there and magnitudes below 2^-24 become zero. */
 int b200q_gemm(const void* a, int lda, const void* bq, const void* scales, void* c, int ldc, int M, int N, int K,
                int wtype, int zero_point, int group, int act_dtype, void* workspace, size_t workspace_bytes,
                void* stream);
 
 /* The same GEMM for a host that keeps activations and results in host memory (no counterpart in
  * the reference, whose operator takes device tensors): copies A[M, K] from `a_host` (row stride
- * lda, pinned memory if the copy is to be asynchronous) into `a_staging` (device, M*K fp16), runs
- * b200q_gemm into `c_staging` (device, M*N fp16) and copies the result to `c_host` (row stride
- * ldc), all queued on `stream` by this one call; the caller synchronises before it reads c_host. */
+ * lda, pinned memory if the copy is to be asynchronous) into `a_staging` (device, M*K 16-bit
+ * elements) and runs b200q_gemm.  A result of at most 1 MiB whose `c_host` (row stride ldc) is
+ * pinned memory the GPU can address is written there by the kernel itself; otherwise the GEMM
+ * writes `c_staging` (device, M*N elements) and a copy to `c_host` follows.  All of it is queued
+ * on `stream` by this one call; the caller synchronises before it reads c_host. */
 int b200q_gemm_host(const void* a_host, int lda, const void* bq, const void* scales, void* c_host, int ldc, int M,
                     int N, int K, int wtype, int zero_point, int group, int act_dtype, void* a_staging,
                     void* c_staging, void* workspace, size_t workspace_bytes, void* stream);
@@ -115,15 +120,21 @@ int b200q_gemm_planned(const void* a, int lda, const void* bq, const void* scale
  * python/tilus/hidet/include/tilus/context.h:97-131.)
  *
  * Same arguments and results as b200q_gemm without `workspace`: the split-K scratch is a
- * fixed array inside the library, b200q_static_workspace_limit() bytes (8 MiB) per GPU, held
- * from library load to process exit.  Problems whose b200q_workspace_bytes exceeds that limit
- * return B200Q_ERR_WORKSPACE and launch nothing.  The function allocates nothing and frees
- * nothing.  The first call on each device looks the array's address up and clears it, so make
- * that call outside any stream capture.  All calls on a device share the one array: calls
- * that may overlap on the GPU (different streams) race on it and must be serialised by the
- * caller; back-to-back calls on one stream are fine, each leaves the scratch zeroed. */
+ * fixed array inside the library, b200q_static_workspace_limit() bytes (8 MiB) per GPU.  Problems
+ * whose b200q_workspace_bytes exceeds that limit return B200Q_ERR_WORKSPACE and launch nothing.
+ * The function allocates nothing and frees nothing.  The array belongs to the library's device
+ * code: the CUDA runtime reserves its 8 MiB on a GPU when it loads that code there, which with
+ * lazy module loading (the default) is the first call of b200q_static_ws_init or of this
+ * function on that GPU.  Call b200q_static_ws_init once per GPU at set-up time, outside any stream
+ * capture and before the memory plan is frozen; it looks the array's address up (the first call of
+ * this function does the same if it was skipped).  All calls on a device share the one array:
+ * calls that may overlap on the GPU (different streams) race on it and must be serialised by the
+ * caller; back-to-back calls on one stream are fine, each leaves the scratch zeroed.  A bounded
+ * device-side wait that gave up is reported by b200q_device_status(NULL, ...), which also puts
+ * the array back to zero. */
 int b200q_gemm_static_ws(const void* a, int lda, const void* bq, const void* scales, void* c, int ldc, int M, int N,
                          int K, int wtype, int zero_point, int group, int act_dtype, void* stream);
+int b200q_static_ws_init(void);
 size_t b200q_static_workspace_limit(void);
 
 /* ---- column-sharded GEMV with the all-gather fused into the kernel -------------------------------
@@ -131,7 +142,8 @@ size_t b200q_static_workspace_limit(void);
  * there; they serve the N-sharded decode stack: rank r holds columns [col_offset, col_offset + N)
  * of a layer and every rank needs the full output row as the next layer's activations.
  *
- * b200q_gemm_gather computes this rank's columns like b200q_gemm (M <= 16) and stores them straight
+ * b200q_gemm_gather computes this rank's columns like b200q_gemm (M <= 16; workspace of
+ * b200q_workspace_bytes for the same problem) and stores them straight
  * into the full output row [M, ldc] of every rank (peer-mapped device pointers; stores only, no
  * loads from peers), then raises this rank's flag on every rank.  Every rank owns two row
  * buffers used alternately (`out[g]` = buffer 0 of rank g, buffer 1 is `buffer_elems` elements
@@ -171,23 +183,27 @@ int b200q_peer_open(const unsigned char handle[64], void** ptr);
 int b200q_peer_close(void* ptr);
 int b200q_peer_free(void* ptr);
 
-/* W[K, N] (fp16, row-major) = dequantized weights, bit-exact with the reference's
- * cast-then-scale (examples/quantization/matmul_a16wx.py:316-320; cast kernel
+/* W[K, N] (row-major, dtype act_dtype like the scales) = dequantized weights, bit-exact with the
+ * reference's cast-then-scale (examples/quantization/matmul_a16wx.py:316-320; cast kernel
  * python/tilus/kernels/cast.py:27-55). */
 int b200q_dequantize(const void* bq, const void* scales, void* w, int N, int K, int wtype, int zero_point, int group,
-                     void* stream);
+                     int act_dtype, void* stream);
 
 /* QuantizedLinear.load_and_quantize on the GPU (examples/quantization/matmul_a16wx.py:470-528):
- * weight [N, K] (row = output feature; weight_dtype 0 = fp16, 1 = fp32; row stride ldw elements) ->
- * scales fp16 [K/group, N] = max(absmax / max_value, 1e-6) per (group, column) and the packed
+ * weight [N, K] (row = output feature; weight_dtype 0 = fp16, 1 = fp32, 2 = bf16; row stride ldw
+ * elements) -> scales [K/group, N] of dtype act_dtype = max(absmax / max_value, 1e-6) per (group, column) and the packed
  * weights bq (b200 layout, K*N*nbits/8 bytes): q = clamp(w / scale, min, max), integers rounded
  * half to even, floats encoded as python/tilus/hidet/ir/primitives/cuda/cast.py:44-100.  The
  * reference does this with PyTorch ops followed by its change-layout kernel (:520-525). */
 int b200q_quantize(const void* weight, int weight_dtype, int ldw, void* bq, void* scales, int N, int K, int wtype,
-                   int group, void* stream);
+                   int group, int act_dtype, void* stream);
 
 /* Reads the device status header of a workspace (synchronises `stream`): status[0] is 0 or
- * B200Q_ERR_DEVICE_TIMEOUT, status[1..3] say which wait gave up.  Clears the header. */
+ * B200Q_ERR_DEVICE_TIMEOUT, status[1..3] say which wait gave up (1: 2 = tcgen05 prefill pipeline,
+ * 3 = decode kernel's weight ring, 5 = wait for a peer's columns, 6 = tcgen05 small-batch pipeline;
+ * 2: CTA; 3: warp or thread).  Clears the header.  A launch that gave up may leave partial sums
+ * behind: zero the workspace before it is used again.  workspace == NULL names the built-in
+ * scratch of b200q_gemm_static_ws, which this call then puts back to zero itself. */
 int b200q_device_status(void* workspace, int32_t status[4], void* stream);
 
 #ifdef __cplusplus

@@ -238,10 +238,45 @@ def quantized_matmul(a, codes, scales, dt, group_size, zero_point=0) -> np.ndarr
 
 
 # ---------------------------------------------------------------------------
+# bfloat16 activations (a_dtype = bfloat16, examples/quantization/matmul_a16wx.py:35-41, :418-419)
+# numpy has no bfloat16: these take and return torch CPU tensors
+# ---------------------------------------------------------------------------
+def dequantize_bf16(codes: np.ndarray, scales, dt, group_size: int, zero_point: int = 0):
+    """W[k,n] = bf16_rn( bf16(decode(q[k,n]) - zp) * s[k // g, n] ) as a torch.bfloat16 tensor.
+
+    Same two steps as `dequantize` in the other activation dtype: the cast of the code to
+    bfloat16 (exact: every value of an at-most-8-bit type has at most 8 significant bits) and
+    one bfloat16 multiply, rounded to nearest even (the 16-bit product of two bfloat16 numbers
+    is exact in fp32, so rounding that product once is the same thing)."""
+    import torch
+
+    codes = np.asarray(codes)
+    K, N = codes.shape
+    v = torch.from_numpy(decode_codes(codes, dt) - np.float32(zero_point))
+    v16 = v.to(torch.bfloat16)
+    assert torch.equal(v16.float(), v), "decoded value not exact in bfloat16"
+    s = scales if isinstance(scales, torch.Tensor) else torch.from_numpy(np.asarray(scales))
+    s = s.to(torch.bfloat16)
+    assert tuple(s.shape) == (K // group_size, N)
+    s_full = s.float().repeat_interleave(group_size, dim=0)
+    return (v16.float() * s_full).to(torch.bfloat16)
+
+
+def gemm_bf16(a, w):
+    """C = bf16_rn( sum_k fp32(A[m,k]) * fp32(W[k,n]) ), fp32 accumulation; torch.bfloat16 in and out."""
+    return (a.float() @ w.float()).to(a.dtype)
+
+
+def quantized_matmul_bf16(a, codes, scales, dt, group_size, zero_point=0):
+    return gemm_bf16(a, dequantize_bf16(codes, scales, dt, group_size, zero_point))
+
+
+# ---------------------------------------------------------------------------
 # weight quantization (QuantizedLinear.load_and_quantize)
 # ---------------------------------------------------------------------------
-def quantize_weight(weight: np.ndarray, dt, group_size: int):
-    """weight[out, in] (any float) -> (codes[K=in, N=out] uint8, scales[K/g, N] fp16).
+def quantize_weight(weight: np.ndarray, dt, group_size: int, bf16_scales: bool = False):
+    """weight[out, in] (any float) -> (codes[K=in, N=out] uint8, scales[K/g, N] fp16; with
+    bf16_scales the scales are rounded to bfloat16 instead and returned as float32 values).
 
     examples/quantization/matmul_a16wx.py:470-528: transpose to [K, N] in fp32, view
     as [K/g, g, N], scales = max(absmax / max_value, 1e-6) cast to fp16, q = w / scales
@@ -253,7 +288,13 @@ def quantize_weight(weight: np.ndarray, dt, group_size: int):
     K, N = w.shape
     wg = w.reshape(K // group_size, group_size, N)
     absmax = np.abs(wg).max(axis=1, keepdims=True)
-    scales = np.maximum(absmax / np.float32(dt.max_value), np.float32(1e-6)).astype(np.float16)
+    scales = np.maximum(absmax / np.float32(dt.max_value), np.float32(1e-6))
+    if bf16_scales:
+        import torch
+
+        scales = torch.from_numpy(scales).to(torch.bfloat16).float().numpy()
+    else:
+        scales = scales.astype(np.float16)
     q = wg / scales.astype(np.float32)
     q = np.clip(q, np.float32(dt.min_value), np.float32(dt.max_value))
     if kind == KIND_FLOAT:

@@ -48,8 +48,13 @@ def test_plan_static_table():
     assert ops.plan(4096, 28672, 8192, "int4b", 0, 128)["kernel"] == 1  # prefill: tcgen05 kernel
     p8 = ops.plan(8, 4096, 4096, "uint4b", 8, 128)
     assert p8["kernel"] == 2 and p8["m_tiles"] == 1 and p8["smem_bytes"] <= 113 * 1024
-    # 9..128 rows: tcgen05 kernel with the weights on the 256-column side of the MMA
-    for m in (9, 16, 64, 128):
+    # 9..16 rows: the same kernel with two 8-row activation tiles, one CTA per SM with all of its shared memory
+    for m in (9, 16):
+        ps = ops.plan(m, 8192, 8192, "uint4b", 8, 128)
+        assert ps["kernel"] == 2 and ps["m_tiles"] == 2 and ps["smem_bytes"] <= 227 * 1024
+        assert ps["splits"] * ps["ctas_per_split"] <= 148 and ps["stages"] >= 2
+    # 17..128 rows: tcgen05 kernel with the weights on the 256-column side of the MMA
+    for m in (17, 64, 128):
         pw = ops.plan(m, 4096, 4096, "uint4b", 8, 128)
         assert pw["kernel"] == 3 and pw["smem_bytes"] <= 227 * 1024
         assert pw["splits"] * pw["ctas_per_split"] <= 148 + 148 // 8
@@ -73,7 +78,10 @@ def test_rejects_bad_problems(lib):
     # null pointers are refused before anything is launched
     assert lib.b200q_gemm(None, 8192, None, None, None, 8192, 1, 8192, 8192, u4, 8, 128, 0, None, 0, None) \
         == _lib.ST_INVALID_ARG
-    assert lib.b200q_dequantize(None, None, None, 8192, 8192, u4, 8, 128, None) == _lib.ST_INVALID_ARG
+    assert lib.b200q_dequantize(None, None, None, 8192, 8192, u4, 8, 128, 0, None) == _lib.ST_INVALID_ARG
+    # activation dtype tags other than fp16 (0) and bf16 (1) are refused
+    assert lib.b200q_gemm(None, 8192, None, None, None, 8192, 1, 8192, 8192, u4, 8, 128, 2, None, 0, None) \
+        == _lib.ST_UNSUPPORTED
 
 
 def test_ops_refuse_cpu_tensors():

@@ -142,6 +142,71 @@ def test_wide_kernel_more_items_than_sms():
     assert ops.plan(M, N, K, D.uint4b, 8, 128)["kernel"] == 3
 
 
+@pytest.mark.parametrize("M,N,K,splits", [(300, 256, 2048, 4), (200, 384, 1024, 2), (129, 128, 4096, 8),
+                                          (520, 256, 1024, 1)])
+def test_umma_kernel_forced_split_k_and_clean_workspace(M, N, K, splits):
+    """Kernel 1 (tcgen05, weights in tensor memory) with forced split-K factors: several row tiles,
+    a ragged last row tile, fp32 partial sums and arrival counters left zeroed."""
+    m_tiles, n_tiles = (M + 255) // 256, (N + 127) // 128
+    _forced(M, N, K, D.int4b, 0, dict(kernel=1, splits=splits, tile_m=256, m_tiles=m_tiles,
+                                      ctas_per_split=m_tiles * n_tiles), seed=13)
+
+
+@pytest.mark.parametrize("M", [512, 4096, 4097])
+def test_umma_kernel_many_row_tiles(M):
+    """The persistent tile walk of the prefill kernel with more than one row tile, more tiles than
+    SMs, row-tile groups (rasterisation) and - for 4097 - a last row tile of a single row that the
+    activation copy fills with zeros (the reference benchmarks M = 4096 and 4097 itself,
+    examples/quantization/matmul_a16wx.py:566-571).  Full comparison with the oracle."""
+    N, K = 1024, 8192
+    prob = synth.make_problem(M, N, K, D.int4b, 128, seed=M)
+    pl = ops.plan(M, N, K, D.int4b, 0, 128)
+    assert pl["kernel"] == 1 and pl["m_tiles"] > 1
+    c, _, _ = _run(prob)
+    ref = qo.quantized_matmul(prob["a"].numpy(), prob["codes"].numpy(), prob["scales"].numpy(), D.int4b, 128, 0)
+    assert c.shape == (M, N)
+    assert _rel_err(c, ref) <= REL_TOL
+    # every row tile separately: a wrong tile cannot hide behind the largest element of the matrix
+    for m0 in range(0, M, 256):
+        assert _rel_err(c[m0:m0 + 256], ref[m0:m0 + 256]) <= REL_TOL, m0
+
+
+def test_config2_prefill_full_size_sampled_columns():
+    """BASELINE configuration 2 at full size: M = 4096, K = 8192, N = 28672, int4 g128, seed 0.  The
+    oracle dequantizes and multiplies 512 sampled columns (every 128-column tile boundary region is
+    hit: the stride 56 is coprime to 128); on the same columns the library's dequantized weights
+    must be bit-identical."""
+    dev = _dev()
+    M, N, K = 4096, 28672, 8192
+    prob = synth.make_problem(M, N, K, D.int4b, 128, seed=0)
+    bq = packing.interleave(prob["codes"].to(dev), D.int4b)
+    sc = prob["scales"].to(dev)
+    a = prob["a"].to(dev)
+    c = ops.quantized_matmul(a, bq, sc, D.int4b, 128, 0)
+    cols = torch.arange(5, N, 56)[:512]
+    w_cols = ops.dequantize(bq, sc, D.int4b, 128, 0)[:, cols.to(dev)].cpu().numpy()
+    torch.cuda.synchronize()
+    want_w = qo.dequantize(prob["codes"][:, cols].numpy(), prob["scales"][:, cols].numpy(), D.int4b, 128, 0)
+    np.testing.assert_array_equal(w_cols.view(np.uint16), want_w.view(np.uint16))
+    ref = qo.gemm_fp16(prob["a"].numpy(), want_w)
+    got = c[:, cols.to(dev)].cpu().numpy()
+    assert _rel_err(got, ref) <= REL_TOL
+    for m0 in range(0, M, 1024):
+        assert _rel_err(got[m0:m0 + 1024], ref[m0:m0 + 1024]) <= REL_TOL, m0
+
+
+@pytest.mark.parametrize("M", [9, 12, 16])
+@pytest.mark.parametrize("N,K", [(8192, 8192), (4096, 4096), (272, 14336)])
+def test_stream_kernel_two_row_tiles_default_plan(M, N, K):
+    """9..16 rows run the mma.sync kernel with two 8-row activation tiles, one CTA per SM: K in
+    chunks, own tiles meeting in the fp32 scratch, left-over tiles (N = 272)."""
+    prob = synth.make_problem(M, N, K, D.uint4b, 128, seed=M + N)
+    assert ops.plan(M, N, K, D.uint4b, 8, 128)["kernel"] == 2
+    c, _, _ = _run(prob)
+    ref = qo.quantized_matmul(prob["a"].numpy(), prob["codes"].numpy(), prob["scales"].numpy(), D.uint4b, 128, 8)
+    assert _rel_err(c, ref) <= REL_TOL
+
+
 def test_config0_m16_k4096_n4096_u4():
     prob = synth.make_problem(16, 4096, 4096, D.uint4b, 128, seed=0)
     c, bq, sc = _run(prob)

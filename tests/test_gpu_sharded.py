@@ -10,7 +10,7 @@ import pytest
 import torch
 
 from oracle import quant_oracle as qo
-from tilus_b200 import float16, sharded, synth
+from tilus_b200 import _lib, float16, ops, sharded, synth
 from tilus_b200 import dtypes as D
 
 pytestmark = pytest.mark.gpu
@@ -104,3 +104,58 @@ def test_fused_gather_rejects_wide_batches():
     lin.load_codes(prob["codes"], prob["scales"])
     with pytest.raises(ValueError):
         ctxs[0].gemm(torch.zeros(17, 512, dtype=torch.float16, device=dev), lin)
+
+
+@pytest.mark.parametrize("M", [9, 12])
+def test_fused_gather_wide_shard_workspace(M):
+    """9..16 rows with a wide shard: the workspace b200q_workspace_bytes reports for the problem (fp32
+    scratch [N_loc][16]) is what the fused call needs - here more than the 1 MiB the operator layer
+    allocates at least."""
+    dev = torch.device("cuda:0")
+    dt, g, world = D.uint4b, 128, 2
+    K, N = 512, 2 * 28672
+    prob = synth.make_problem(M, N, K, dt, g, seed=M)
+    need = ops.workspace_bytes(M, N // world, K, dt, prob["zero_point"], g)
+    assert need > (1 << 20)
+    regions, ctxs = _virtual_group(world, 16, N, dev)
+    rows = []
+    for r in range(world):
+        lin = sharded.ShardedQuantizedLinear(float16, dt, g, K, N, zero_point=prob["zero_point"], shard=(world, r)).to(dev)
+        lin.load_codes(prob["codes"], prob["scales"])
+        rows.append(ctxs[r].gemm(prob["a"].to(dev), lin))
+    ref = qo.quantized_matmul(prob["a"].numpy(), prob["codes"].numpy(), prob["scales"].numpy(), dt, g,
+                              prob["zero_point"]).astype(np.float32)
+    for r in range(world):
+        got = ctxs[r].fetch(rows[r]).float().cpu().numpy()
+        assert np.abs(got - ref).max() / np.abs(ref).max() <= 1e-2
+
+
+def test_fused_gather_wait_runs_out_and_reports():
+    """A bounded device-side wait that runs out: rank 0 of a two-rank group makes two fused calls while
+    rank 1 makes none, so rank 0's second launch waits for a flag that nothing raises.  After a
+    quarter of a second it gives up, completes normally and leaves B200Q_ERR_DEVICE_TIMEOUT with the
+    place (5 = wait for a peer's columns) in the workspace header; reading the status clears it, and
+    the context stays usable."""
+    dev = torch.device("cuda:0")
+    dt, g, M = D.int4b, 128, 2
+    prob = synth.make_problem(M, 512, 512, dt, g, seed=4)
+    regions, ctxs = _virtual_group(2, 16, 512, dev)
+    lin = sharded.ShardedQuantizedLinear(float16, dt, g, 512, 512, shard=(2, 0)).to(dev)
+    lin.load_codes(prob["codes"], prob["scales"])
+    x = prob["a"].to(dev)
+    ws = ops.get_workspace(dev, ops.workspace_bytes(M, 256, 512, dt, 0, g))
+    assert ops.device_status(ws) == [0, 0, 0, 0]
+    ctxs[0].gemm(x, lin)  # call 1: nothing to wait for
+    assert ops.device_status(ws) == [0, 0, 0, 0]
+    ctxs[0].gemm(x, lin)  # call 2: rank 1 never finished call 1
+    torch.cuda.synchronize()
+    st = ops.device_status(ws)
+    assert st[0] == _lib.ST_DEVICE_TIMEOUT and st[1] == 5, st
+    assert ops.device_status(ws) == [0, 0, 0, 0]  # reading cleared the report
+    assert ctxs[0].calls_completed() == 2          # the launch ran to its end
+    # the library still computes: an ordinary GEMM on the same workspace right after
+    assert int(ws.count_nonzero()) == 0
+    c = ops.quantized_matmul(x, lin.local.quantized_weight.data, lin.local.scales.data, dt, g, 0, workspace=ws)
+    ref = qo.quantized_matmul(prob["a"].numpy(), prob["codes"][:, :256].numpy(), prob["scales"][:, :256].numpy(), dt, g, 0)
+    err = np.abs(c.float().cpu().numpy() - ref.astype(np.float32)).max() / np.abs(ref.astype(np.float32)).max()
+    assert err <= 1e-2

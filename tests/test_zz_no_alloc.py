@@ -35,21 +35,28 @@ def _gemm_both(M, N, K, dt, group, seed):
     c_ref = torch.empty(M, N, dtype=torch.float16, device=dev)
     _lib.check(lib.b200q_gemm(a.data_ptr(), K, bq.data_ptr(), sc.data_ptr(), c_ref.data_ptr(), N, M, N, K, dt.code, zp,
                               group, _lib.ACT_F16, ws.data_ptr(), ws.numel(), stream))
-    outs = []
-    for _ in range(2):  # the second call runs on the scratch the first one left behind
-        c = torch.full((M, N), float("nan"), dtype=torch.float16, device=dev)
+    _lib.check(lib.b200q_static_ws_init())  # set-up time: the module with the array is loaded here
+    outs = [torch.full((M, N), float("nan"), dtype=torch.float16, device=dev) for _ in range(2)]
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info(dev)[0]
+    for c in outs:  # the second call runs on the scratch the first one left behind
         _lib.check(lib.b200q_gemm_static_ws(a.data_ptr(), K, bq.data_ptr(), sc.data_ptr(), c.data_ptr(), N, M, N, K,
                                             dt.code, zp, group, _lib.ACT_F16, stream))
-        outs.append(c)
     torch.cuda.synchronize()
+    # nothing was allocated by the calls: the device's free memory is what it was after set-up
+    assert torch.cuda.mem_get_info(dev)[0] == free_before
+    # no bounded wait gave up; the status query reads the built-in scratch (workspace = NULL)
+    status = (ctypes.c_int32 * 4)()
+    assert lib.b200q_device_status(None, ctypes.byref(status), stream) == _lib.ST_OK
+    assert list(status) == [0, 0, 0, 0]
     return c_ref.float().cpu().numpy(), [o.float().cpu().numpy() for o in outs]
 
 
 @pytest.mark.parametrize("M,N,K", [(200, 256, 2048), (40, 256, 2048), (3, 272, 2048)])
 def test_static_workspace_matches_gemm_twice(M, N, K):
-    # (200, 256, 2048) runs the tcgen05 kernel with split-K, the other two the mma.sync kernel with
-    # K cut in chunks / tiles shared between CTAs: in all of them fp32 partial sums and arrival
-    # counters live in the built-in scratch
+    # (200, 256, 2048) and (40, 256, 2048) run the two tcgen05 kernels with split-K, (3, 272, 2048) the
+    # mma.sync kernel with column tiles shared between CTAs: in all of them fp32 partial sums and
+    # arrival counters live in the built-in scratch
     ref, outs = _gemm_both(M, N, K, D.int4b, 128, seed=21)
     scale = np.abs(ref).max()
     for got in outs:

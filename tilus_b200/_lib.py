@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, os.environ.get("B200Q_LIB_NAME", "libb200q.so"))
 
 ST_OK, ST_INVALID_ARG, ST_UNSUPPORTED, ST_WORKSPACE, ST_CUDA, ST_DEVICE_TIMEOUT = range(6)
-ACT_F16 = 0
+ACT_F16, ACT_BF16 = 0, 1
 
 
 class B200QError(RuntimeError):
@@ -50,7 +50,7 @@ class Plan(ctypes.Structure):
         ("warps", ctypes.c_int32),
         ("passes", ctypes.c_int32),
         ("pdl", ctypes.c_int32),
-        ("debug", ctypes.c_int32),
+        ("reserved", ctypes.c_int32),
         ("workspace_bytes", ctypes.c_uint64),
     ]
 
@@ -73,14 +73,15 @@ SYMBOLS = {
     "b200q_gemm_static_ws": (_i, [_vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "b200q_gemm_host": (_i, [_vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _sz, _vp]),
     "b200q_static_workspace_limit": (_sz, []),
-    "b200q_dequantize": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "b200q_static_ws_init": (_i, []),
+    "b200q_dequantize": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "b200q_gemm_gather": (_i, [_vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp, ctypes.POINTER(Gather)]),
     "b200q_peer_alloc": (_i, [_sz, ctypes.POINTER(ctypes.c_void_p)]),
     "b200q_peer_export": (_i, [_vp, ctypes.c_char_p]),
     "b200q_peer_open": (_i, [ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p)]),
     "b200q_peer_close": (_i, [_vp]),
     "b200q_peer_free": (_i, [_vp]),
-    "b200q_quantize": (_i, [_vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "b200q_quantize": (_i, [_vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "b200q_device_status": (_i, [_vp, ctypes.POINTER(ctypes.c_int32 * 4), _vp]),
 }
 

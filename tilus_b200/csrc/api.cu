@@ -21,8 +21,9 @@ namespace b200q {
 B200Q_DECL_SPART(0) B200Q_DECL_SPART(1) B200Q_DECL_SPART(2) B200Q_DECL_SPART(3)
 B200Q_DECL_SPART(4) B200Q_DECL_SPART(5) B200Q_DECL_SPART(6) B200Q_DECL_SPART(7)
 cudaError_t dequant_launch(int var, const DequantParams& p, cudaStream_t stream);
-cudaError_t quantize_launch(const void* w, int w_is_f32, int ldw, void* bq, void* scales, int N, int K, int group,
-                            int kind, int nbits, int ebits, int mbits, float minv, float maxv, cudaStream_t stream);
+cudaError_t quantize_launch(const void* w, int w_dtype, int ldw, void* bq, void* scales, int N, int K, int group,
+                            int kind, int nbits, int ebits, int mbits, float minv, float maxv, int act,
+                            cudaStream_t stream);
 #define B200Q_DECL_UPART(i) \
   cudaError_t umma_launch_part##i(int, const UmmaParams&, const void*, int, cudaStream_t);
 B200Q_DECL_UPART(0) B200Q_DECL_UPART(1) B200Q_DECL_UPART(2) B200Q_DECL_UPART(3)
@@ -111,18 +112,6 @@ static int variant_of(int wtype, int zero_point) {
   return -1;
 }
 
-#ifdef B200Q_TIMELINE
-// side builds only: a buffer of [slots][grid][8] device timestamps, one slot per launch
-static unsigned long long* g_tl_buf = nullptr;
-static int g_tl_slots = 0, g_tl_next = 0;
-extern "C" int b200q_debug_set_timeline(void* buf, int slots) {
-  g_tl_buf = reinterpret_cast<unsigned long long*>(buf);
-  g_tl_slots = slots;
-  g_tl_next = 0;
-  return 0;
-}
-#endif
-
 struct DeviceInfo {
   int sm_count = 0;
   int max_smem = 0;
@@ -149,16 +138,22 @@ static int stream_pitch(int kc) {
   if (bytes % 128 != 64) bytes += (64 - bytes % 128 + 128) % 128;
   return bytes / 2;
 }
-// ---- stream kernel (kernel 2): one CTA per SM, half an SM each ---------------------------------
-// Two consecutive launches share an SM (the second prefetches while the first computes), so a
-// CTA may use half of the SM's shared memory: (228 KB - 2 x 1 KB reserved) / 2.
+// ---- stream kernel (kernel 2) ---------------------------------------------------------------------
+// Up to 8 rows: a CTA takes at most half an SM, so that two consecutive launches share an SM (the
+// second prefetches while the first computes) or two CTAs of one launch do: (228 KB - 2 x 1 KB
+// reserved) / 2 of shared memory.  9..16 rows: one CTA per SM with all of its shared memory, so
+// that a long K chunk of the 16 activation rows fits next to the rings.
 static const int kStreamSmemCap = 113 * 1024;
 static int stream_slot_bytes(int bits) { return stream_gi(bits) * 256 * bits; }
 // 8-row activation tiles per launch: 1 or 2 (the kernel's MT)
 static int stream_mt(int m_pass) { return m_pass <= 8 ? 1 : 2; }
+// CTAs of one launch per SM
+static int stream_per_sm(int m_pass) { return m_pass <= 8 ? 2 : 1; }
 // most activation rows one launch of the stream kernel takes
 static int stream_rows_per_pass(int M) { (void)M; return 16; }
-static int stream_smem_cap(int m_pass, const DeviceInfo& di) { (void)m_pass; (void)di; return kStreamSmemCap; }
+static int stream_smem_cap(int m_pass, const DeviceInfo& di) {
+  return m_pass <= 8 ? kStreamSmemCap : di.max_smem;
+}
 // whole column tiles a CTA owns (their sums live in at most 16 KB of shared memory)
 static int stream_tiles_owned(int m_pass, int NT, int cpc) {
   const int mt = stream_mt(m_pass), cap = 32 / mt;
@@ -167,7 +162,7 @@ static int stream_tiles_owned(int m_pass, int NT, int cpc) {
 }
 static int stream_fixed_smem(int m_pass, int kc, int t_own) {
   const int mt = stream_mt(m_pass);
-  // barriers, own-tile sums, activation chunk (+ 64 zero bytes), group sums as accumulator quads
+  // barriers, scale caches, own-tile sums, activation chunk (+ 64 zero bytes), group sums as accumulator quads
   return 1024 + STREAM_WARPS * STREAM_SC_GROUPS * 32 + t_own * 16 * 8 * mt * 4 + m_pass * stream_pitch(kc) * 2 + 64 +
          (kc / 128) * 16 * mt * 4;
 }
@@ -178,8 +173,8 @@ static int stream_stages_for(int m_pass, int kc, int bits, int t_own, const Devi
   int st = (stream_smem_cap(m_pass, di) - stream_fixed_smem(m_pass, kc, t_own)) / (STREAM_WARPS * stream_slot_bytes(bits));
   return st > 8 ? 8 : st;
 }
-// CTAs per k chunk.  First choice: two CTAs per SM (32 warps hide the latency of the decode /
-// mma chains best) with a count that divides the column tiles evenly, so that no tile is
+// CTAs per k chunk.  First choice (up to 8 rows): two CTAs per SM (32 warps hide the latency of the
+// decode / mma chains best) with a count that divides the column tiles evenly, so that no tile is
 // shared between CTAs and nothing goes through the global scratch; then one CTA per SM with
 // such a count; else one CTA per SM with the left-over tiles shared item-wise.
 static int stream_ctas_per_chunk(int NT, int s, int per_sm, const DeviceInfo& di) {
@@ -191,7 +186,7 @@ static int stream_ctas_per_chunk(int NT, int s, int per_sm, const DeviceInfo& di
     if (NT % c == 0) return c;
   return full > NT ? NT : full;
 }
-static const int kStreamMaxRows = 8;
+static const int kStreamMaxRows = 16;
 static size_t stream_workspace_bytes(int N) { return WS_HEADER_BYTES + ws_counter_bytes(N) + (size_t)16 * N * sizeof(float); }
 // K is cut into the fewest chunks S (a divisor of K/512, at most one per SM) that leave room for
 // three ring slots per warp next to the activation chunk [M, K/S]; the grid is S * CPC.
@@ -201,7 +196,7 @@ static int plan_stream(int m_pass, int N, int K, int bits, const DeviceInfo& di,
   for (int want = 3; want >= 1 && !best_s; --want)
     for (int s = 1; s <= KB && s <= di.sm_count; ++s) {
       if (KB % s) continue;
-      const int cpc = stream_ctas_per_chunk(NT, s, 2, di);
+      const int cpc = stream_ctas_per_chunk(NT, s, stream_per_sm(m_pass), di);
       if (cpc < 1) continue;
       const int st = stream_stages_for(m_pass, (KB / s) * 512, bits, stream_tiles_owned(m_pass, NT, cpc), di);
       if (st >= want) { best_s = s; best_st = st; best_c = cpc; break; }
@@ -217,7 +212,6 @@ static int plan_stream(int m_pass, int N, int K, int bits, const DeviceInfo& di,
   pl->smem_bytes = stream_smem(m_pass, (KB / best_s) * 512, bits, best_st, stream_tiles_owned(m_pass, NT, best_c));
   pl->tile_m = 0;
   pl->pdl = 1;
-  pl->debug = 0;
   return ST_OK;
 }
 
@@ -262,7 +256,6 @@ static void plan_umma(int M, int N, int K, int bits, const DeviceInfo& di, b200q
   pl->warps = 19;
   pl->passes = 1;
   pl->pdl = 0;
-  pl->debug = 0;
 }
 
 // wide tcgen05 kernel (kernel 3): 128-row x 256-column tiles, split-K while the tiles do not fill the SMs
@@ -284,21 +277,17 @@ static void plan_wide(int M, int N, int K, int bits, const DeviceInfo& di, b200q
   pl->warps = 23;
   pl->passes = 1;
   pl->pdl = 0;
-  pl->debug = 0;
 }
 
-static int make_plan(int M, int N, int K, int var, b200q_plan_t* pl, int stream_max_rows = kStreamMaxRows) {
+static int make_plan(int M, int N, int K, int var, b200q_plan_t* pl) {
   const DeviceInfo di = device_info();
   std::memset(pl, 0, sizeof(*pl));
   const int bits = var_bits(var);
-  // up to 8 rows: the mma.sync stream kernel; above, the tcgen05 kernels.  (With more rows the stream
-  // kernel has to cut K in chunks to fit its activations in shared memory, and the fp32 partial sums
-  // then cost more than the decode saves: 34 us at M = 16 and 45 us at M = 32, K = N = 8192.)
-  if (M <= stream_max_rows) {
-    const int rows = stream_rows_per_pass(M);
-    const int m_pass = M < rows ? M : rows;
-    if (plan_stream(m_pass, N, K, bits, di, pl) == ST_OK) {
-      pl->passes = (M + rows - 1) / rows;
+  // up to 16 rows: the mma.sync stream kernel (one weight decode per 16 x 128 tile feeds one or two
+  // 8-row activation tiles); above, the tcgen05 kernels
+  if (M <= kStreamMaxRows) {
+    if (plan_stream(M, N, K, bits, di, pl) == ST_OK) {
+      pl->passes = 1;
       pl->workspace_bytes = stream_workspace_bytes(N);  // fp32 scratch [N][8 or 16]
       return ST_OK;
     }
@@ -311,9 +300,18 @@ static int make_plan(int M, int N, int K, int var, b200q_plan_t* pl, int stream_
   return ST_OK;
 }
 
+// row tiles per raster group of the transposed tcgen05 kernel: as many as keep one group's
+// activation rows (tm x K 16-bit values per tile) within 32 MB, a quarter of L2
+static int umma_m_group(int tm, int K, int m_tiles) {
+  const long long per_tile = (long long)tm * K * 2;
+  long long g = (32ll << 20) / (per_tile > 0 ? per_tile : 1);
+  if (g < 1) g = 1;
+  if (g > m_tiles) g = m_tiles;
+  return (int)g;
+}
 
 static int run_umma(const void* a, int lda, const void* bq, const void* scales, void* c, int ldc, int M, int N, int K,
-                    int var, int group, void* workspace, size_t ws_bytes, cudaStream_t stream,
+                    int var, int group, int act, void* workspace, size_t ws_bytes, cudaStream_t stream,
                     const b200q_plan_t& pl) {
   const int tm = pl.tile_m;
   if (tm != 32 && tm != 64 && tm != 128 && tm != 256) return ST_INVALID_ARG;
@@ -333,7 +331,7 @@ static int run_umma(const void* a, int lda, const void* bq, const void* scales, 
   const cuuint64_t gstride[1] = {(cuuint64_t)lda * 2};
   const cuuint32_t box[2] = {64u, (cuuint32_t)tm};
   const cuuint32_t estr[2] = {1u, 1u};
-  CUresult r = enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(a), gdim, gstride, box, estr,
+  CUresult r = enc(&tmap, act == B200Q_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(a), gdim, gstride, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) { g_last_cuda_error = (int)r; return ST_CUDA; }
@@ -349,11 +347,8 @@ static int run_umma(const void* a, int lda, const void* bq, const void* scales, 
   p.tm = tm; p.m_tiles = m_tiles; p.n_tiles = n_tiles;
   p.splits = pl.splits; p.kblocks_per_split = kblocks / pl.splits;
   p.a_stages = a_stages;
-  p.debug = pl.debug;
-  p.tl = nullptr;
-#ifdef B200Q_TIMELINE
-  p.tl = g_tl_buf;
-#endif
+  p.m_group = umma_m_group(tm, K, m_tiles);
+  p.act = act;
   const int tiles = pl.splits * m_tiles * n_tiles;
   p.grid = tiles < device_info().sm_count ? tiles : device_info().sm_count;
   const int smem = umma_smem_bytes(tm, bits, a_stages);
@@ -364,7 +359,7 @@ static int run_umma(const void* a, int lda, const void* bq, const void* scales, 
 }
 
 static int run_wide(const void* a, int lda, const void* bq, const void* scales, void* c, int ldc, int M, int N, int K,
-                    int var, int group, void* workspace, size_t ws_bytes, cudaStream_t stream,
+                    int var, int group, int act, void* workspace, size_t ws_bytes, cudaStream_t stream,
                     const b200q_plan_t& pl) {
   const int bits = var_bits(var);
   const int m_tiles = (M + 127) / 128, n_tiles = (N + 255) / 256, G = K / 128;
@@ -380,7 +375,7 @@ static int run_wide(const void* a, int lda, const void* bq, const void* scales, 
   const int a_rows = wide_a_rows(M);
   const cuuint32_t box[2] = {64u, (cuuint32_t)a_rows};
   const cuuint32_t estr[2] = {1u, 1u};
-  CUresult r = enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(a), gdim, gstride, box, estr,
+  CUresult r = enc(&tmap, act == B200Q_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(a), gdim, gstride, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) { g_last_cuda_error = (int)r; return ST_CUDA; }
@@ -396,12 +391,8 @@ static int run_wide(const void* a, int lda, const void* bq, const void* scales, 
   p.m_tiles = m_tiles; p.n_tiles = n_tiles;
   p.splits = pl.splits; p.kblocks_per_split = 2 * G / pl.splits;
   p.a_rows = a_rows;
+  p.act = act;
   p.wg_stages = wide_wg_stages(bits, device_info().max_smem, a_rows);
-  p.debug = pl.debug;
-  p.tl = nullptr;
-#ifdef B200Q_TIMELINE
-  p.tl = g_tl_buf;
-#endif
   const int items = pl.splits * m_tiles * n_tiles;
   p.grid = items < device_info().sm_count ? items : device_info().sm_count;
   const int smem = wide_smem_bytes(bits, p.wg_stages, a_rows);
@@ -412,7 +403,7 @@ static int run_wide(const void* a, int lda, const void* bq, const void* scales, 
 }
 
 static int run_stream(const void* a, int lda, const void* bq, const void* scales, void* c, int ldc, int M, int N,
-                      int K, int var, int group, void* workspace, size_t ws_bytes, cudaStream_t stream,
+                      int K, int var, int group, int act, void* workspace, size_t ws_bytes, cudaStream_t stream,
                       const b200q_plan_t& pl, const b200q_gather_t* gather = nullptr) {
   const int bits = var_bits(var);
   const int KB = K / BLOCK_K;
@@ -433,10 +424,15 @@ static int run_stream(const void* a, int lda, const void* bq, const void* scales
   if (p.S * p.CPC > 4 * device_info().sm_count) return ST_INVALID_ARG;
   p.pitch = stream_pitch(p.KBc * 512);
   p.stages = pl.stages;
-  p.debug_skip = pl.debug;
   p.pdl = pl.pdl;
-  p.tl = nullptr;
-  p.tl_slot = -1;
+  p.act = act;
+  {
+    const int ipt = p.KBc * (4 / stream_gi(bits));  // items per column tile inside a k chunk
+    p.ipt_shift = -1;
+    if ((ipt & (ipt - 1)) == 0)
+      for (int sh = 0; sh < 31; ++sh)
+        if ((1 << sh) == ipt) p.ipt_shift = sh;
+  }
   std::memset(&p.ga, 0, sizeof(p.ga));
   if (gather) {
     if (M > 16 || gather->world < 1 || gather->world > 8 || gather->rank < 0 || gather->rank >= gather->world)
@@ -468,10 +464,6 @@ static int run_stream(const void* a, int lda, const void* bq, const void* scales
     p.T_own = stream_tiles_owned(mc, p.NT, p.CPC);
     const int smem = stream_smem(mc, p.KBc * 512, bits, pl.stages, p.T_own);
     if (smem > device_info().max_smem) return ST_UNSUPPORTED;
-#ifdef B200Q_TIMELINE
-    p.tl = g_tl_buf;
-    p.tl_slot = (g_tl_buf && g_tl_next < g_tl_slots) ? g_tl_next++ : -1;
-#endif
     cudaError_t e = stream_launch(var, p, stream_mt(mc), smem, stream);
     if (e != cudaSuccess) { g_last_cuda_error = (int)e; return ST_CUDA; }
   }
@@ -479,20 +471,22 @@ static int run_stream(const void* a, int lda, const void* bq, const void* scales
 }
 
 static int run_gemm(const void* a, int lda, const void* bq, const void* scales, void* c, int ldc, int M, int N, int K,
-                    int var, int group, void* workspace, size_t ws_bytes, cudaStream_t stream,
+                    int var, int group, int act, void* workspace, size_t ws_bytes, cudaStream_t stream,
                     const b200q_plan_t& pl) {
   if (!a || !bq || !scales || !c) return ST_INVALID_ARG;
   if (((uintptr_t)a | (uintptr_t)bq | (uintptr_t)c) & 15) return ST_INVALID_ARG;
   if (((uintptr_t)scales) & 1) return ST_INVALID_ARG;
   if (lda < K || ldc < N || (lda % 8) != 0) return ST_INVALID_ARG;
   if (pl.kernel == 1)
-    return run_umma(a, lda, bq, scales, c, ldc, M, N, K, var, group, workspace, ws_bytes, stream, pl);
+    return run_umma(a, lda, bq, scales, c, ldc, M, N, K, var, group, act, workspace, ws_bytes, stream, pl);
   if (pl.kernel == 2)
-    return run_stream(a, lda, bq, scales, c, ldc, M, N, K, var, group, workspace, ws_bytes, stream, pl);
+    return run_stream(a, lda, bq, scales, c, ldc, M, N, K, var, group, act, workspace, ws_bytes, stream, pl);
   if (pl.kernel == 3)
-    return run_wide(a, lda, bq, scales, c, ldc, M, N, K, var, group, workspace, ws_bytes, stream, pl);
+    return run_wide(a, lda, bq, scales, c, ldc, M, N, K, var, group, act, workspace, ws_bytes, stream, pl);
   return ST_UNSUPPORTED;
 }
+
+static bool act_ok(int act) { return act == B200Q_F16 || act == B200Q_BF16; }
 
 }  // namespace b200q
 
@@ -535,18 +529,18 @@ int b200q_gemm_planned(const void* a, int lda, const void* bq, const void* scale
                        int K, int wtype, int zero_point, int group, int act_dtype, void* workspace,
                        size_t workspace_bytes, void* stream, const b200q_plan_t* plan) {
   if (!plan) return ST_INVALID_ARG;
-  if (act_dtype != B200Q_F16) return ST_UNSUPPORTED;
+  if (!act_ok(act_dtype)) return ST_UNSUPPORTED;
   int var;
   int st = check_problem(M, N, K, wtype, zero_point, group, 128, &var);
   if (st != ST_OK) return st;
-  return run_gemm(a, lda, bq, scales, c, ldc, M, N, K, var, group, workspace, workspace_bytes,
+  return run_gemm(a, lda, bq, scales, c, ldc, M, N, K, var, group, act_dtype, workspace, workspace_bytes,
                   reinterpret_cast<cudaStream_t>(stream), *plan);
 }
 
 int b200q_gemm_gather(const void* a, int lda, const void* bq, const void* scales, int M, int N, int K, int wtype,
                       int zero_point, int group, int act_dtype, void* workspace, size_t workspace_bytes, void* stream,
                       const b200q_gather_t* gather) {
-  if (act_dtype != B200Q_F16) return ST_UNSUPPORTED;
+  if (!act_ok(act_dtype)) return ST_UNSUPPORTED;
   if (!gather || !bq || !scales) return ST_INVALID_ARG;
   if (M > 16) return ST_UNSUPPORTED;  // the tcgen05 kernel has no fused gather: use b200q_gemm + a collective
   if (gather->a_prev_offset < 0 && (!a || ((uintptr_t)a & 15))) return ST_INVALID_ARG;
@@ -557,11 +551,11 @@ int b200q_gemm_gather(const void* a, int lda, const void* bq, const void* scales
   int st = check_problem(M, N, K, wtype, zero_point, group, 128, &var);
   if (st != ST_OK) return st;
   b200q_plan_t pl;
-  st = make_plan(M, N, K, var, &pl, 16);  // the fused gather lives in the stream kernel only
+  st = make_plan(M, N, K, var, &pl);  // the fused gather lives in the stream kernel only
   if (st != ST_OK) return st;
   if (pl.kernel != 2) return ST_UNSUPPORTED;
-  return run_stream(a, lda, bq, scales, nullptr, gather->ldc, M, N, K, var, group, workspace, workspace_bytes,
-                    reinterpret_cast<cudaStream_t>(stream), pl, gather);
+  return run_stream(a, lda, bq, scales, nullptr, gather->ldc, M, N, K, var, group, act_dtype, workspace,
+                    workspace_bytes, reinterpret_cast<cudaStream_t>(stream), pl, gather);
 }
 
 int b200q_peer_alloc(size_t bytes, void** ptr) {
@@ -604,20 +598,24 @@ int b200q_peer_free(void* ptr) {
 int b200q_gemm(const void* a, int lda, const void* bq, const void* scales, void* c, int ldc, int M, int N, int K,
                int wtype, int zero_point, int group, int act_dtype, void* workspace, size_t workspace_bytes,
                void* stream) {
-  if (act_dtype != B200Q_F16) return ST_UNSUPPORTED;
+  if (!act_ok(act_dtype)) return ST_UNSUPPORTED;
   int var;
   int st = check_problem(M, N, K, wtype, zero_point, group, 128, &var);
   if (st != ST_OK) return st;
   b200q_plan_t pl;
   st = make_plan(M, N, K, var, &pl);
   if (st != ST_OK) return st;
-  return run_gemm(a, lda, bq, scales, c, ldc, M, N, K, var, group, workspace, workspace_bytes,
+  return run_gemm(a, lda, bq, scales, c, ldc, M, N, K, var, group, act_dtype, workspace, workspace_bytes,
                   reinterpret_cast<cudaStream_t>(stream), pl);
 }
 
 // ---- GEMM on host buffers ------------------------------------------------------------------------
-// Activations in (pinned) host memory, result back in host memory: the three steps - copy in, GEMM,
-// copy out - are queued on the stream by one call, through staging buffers the caller owns.
+// Activations in (pinned) host memory, result back in host memory, queued on the stream by one
+// call.  The activations are copied into a staging buffer the caller owns (every CTA reads all
+// of them, which must not cross the host link each time).  The result, which every element of
+// is written exactly once, goes straight to the host buffer when that is pinned memory the GPU
+// can address (the kernel's stores are the transfer); otherwise through the second staging
+// buffer and a copy.
 int b200q_gemm_host(const void* a_host, int lda, const void* bq, const void* scales, void* c_host, int ldc, int M,
                     int N, int K, int wtype, int zero_point, int group, int act_dtype, void* a_staging,
                     void* c_staging, void* workspace, size_t workspace_bytes, void* stream) {
@@ -628,6 +626,19 @@ int b200q_gemm_host(const void* a_host, int lda, const void* bq, const void* sca
                            : cudaMemcpy2DAsync(a_staging, (size_t)K * 2, a_host, (size_t)lda * 2, (size_t)K * 2, M,
                                                cudaMemcpyHostToDevice, st);
   if (e != cudaSuccess) { g_last_cuda_error = (int)e; return ST_CUDA; }
+  // small results into mapped pinned memory: no copy-out operation on the stream
+  void* c_direct = nullptr;
+  if ((size_t)M * N * 2 <= (1u << 20) && (ldc % 8) == 0) {
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, c_host) == cudaSuccess && attr.type == cudaMemoryTypeHost &&
+        attr.devicePointer && (((uintptr_t)attr.devicePointer) & 15) == 0)
+      c_direct = attr.devicePointer;
+    else
+      (void)cudaGetLastError();  // an unregistered host pointer is not an error here
+  }
+  if (c_direct)
+    return b200q_gemm(a_staging, K, bq, scales, c_direct, ldc, M, N, K, wtype, zero_point, group, act_dtype, workspace,
+                      workspace_bytes, stream);
   const int status = b200q_gemm(a_staging, K, bq, scales, c_staging, N, M, N, K, wtype, zero_point, group, act_dtype,
                                 workspace, workspace_bytes, stream);
   if (status != ST_OK) return status;
@@ -640,14 +651,15 @@ int b200q_gemm_host(const void* a_host, int lda, const void* bq, const void* sca
 
 // ---- GEMM without a caller-supplied workspace and without any allocation ----------------------
 // The split-K scratch (status header, arrival counters, fp32 partial sums) lives in this
-// file-scope device array instead of a caller buffer.  Every GPU that loads the library holds
-// these bytes until the process exits.  In host code `g_static_ws` is only a handle for the
-// symbol, not a device address: the address each device uses is looked up once with
-// cudaGetSymbolAddress while that device is current.
+// file-scope device array instead of a caller buffer.  Every GPU on which the array's module has
+// been loaded holds these bytes until the process exits.  In host code `g_static_ws` is only a
+// handle for the symbol, not a device address: the address each device uses is looked up once with
+// cudaGetSymbolAddress while that device is current.  Device arrays start zeroed and the kernels
+// leave their scratch zeroed, so nothing is cleared here.
 #define B200Q_STATIC_WS_BYTES (8u << 20)
 static __device__ __align__(256) unsigned char g_static_ws[B200Q_STATIC_WS_BYTES];
 
-static int static_ws_pointer(void** out, cudaStream_t stream) {
+static int static_ws_pointer(void** out) {
   static std::mutex mu;
   static void* ptrs[16] = {nullptr};
   int dev = 0;
@@ -659,9 +671,6 @@ static int static_ws_pointer(void** out, cudaStream_t stream) {
     void* ptr = nullptr;
     e = cudaGetSymbolAddress(&ptr, g_static_ws);  // device `dev` is current
     if (e != cudaSuccess || !ptr) { g_last_cuda_error = (int)e; return ST_CUDA; }
-    // the kernels expect zeros and leave zeros; start from a known state all the same
-    e = cudaMemsetAsync(ptr, 0, B200Q_STATIC_WS_BYTES, stream);
-    if (e != cudaSuccess) { g_last_cuda_error = (int)e; return ST_CUDA; }
     ptrs[dev] = ptr;
   }
   *out = ptrs[dev];
@@ -670,9 +679,14 @@ static int static_ws_pointer(void** out, cudaStream_t stream) {
 
 size_t b200q_static_workspace_limit(void) { return (size_t)B200Q_STATIC_WS_BYTES; }
 
+int b200q_static_ws_init(void) {
+  void* ws = nullptr;
+  return static_ws_pointer(&ws);
+}
+
 int b200q_gemm_static_ws(const void* a, int lda, const void* bq, const void* scales, void* c, int ldc, int M, int N,
                          int K, int wtype, int zero_point, int group, int act_dtype, void* stream) {
-  if (act_dtype != B200Q_F16) return ST_UNSUPPORTED;
+  if (!act_ok(act_dtype)) return ST_UNSUPPORTED;
   int var;
   int st = check_problem(M, N, K, wtype, zero_point, group, 128, &var);
   if (st != ST_OK) return st;
@@ -681,14 +695,15 @@ int b200q_gemm_static_ws(const void* a, int lda, const void* bq, const void* sca
   if (st != ST_OK) return st;
   if (pl.workspace_bytes > (uint64_t)B200Q_STATIC_WS_BYTES) return ST_WORKSPACE;  // beyond the built-in scratch
   void* ws = nullptr;
-  st = static_ws_pointer(&ws, reinterpret_cast<cudaStream_t>(stream));
+  st = static_ws_pointer(&ws);
   if (st != ST_OK) return st;
-  return run_gemm(a, lda, bq, scales, c, ldc, M, N, K, var, group, ws, (size_t)B200Q_STATIC_WS_BYTES,
+  return run_gemm(a, lda, bq, scales, c, ldc, M, N, K, var, group, act_dtype, ws, (size_t)B200Q_STATIC_WS_BYTES,
                   reinterpret_cast<cudaStream_t>(stream), pl);
 }
 
 int b200q_dequantize(const void* bq, const void* scales, void* w, int N, int K, int wtype, int zero_point, int group,
-                     void* stream) {
+                     int act_dtype, void* stream) {
+  if (!act_ok(act_dtype)) return ST_UNSUPPORTED;
   int var;
   int st = check_problem(1, N, K, wtype, zero_point, group, 32, &var);
   if (st != ST_OK) return st;
@@ -699,16 +714,18 @@ int b200q_dequantize(const void* bq, const void* scales, void* w, int N, int K, 
   p.scales = reinterpret_cast<const __half*>(scales);
   p.w = reinterpret_cast<__half*>(w);
   p.N = N; p.K = K; p.group = group; p.KB = K / BLOCK_K; p.NT = N / BLOCK_N;
+  p.act = act_dtype;
   cudaError_t e = dequant_launch(var, p, reinterpret_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) { g_last_cuda_error = (int)e; return ST_CUDA; }
   return ST_OK;
 }
 
 int b200q_quantize(const void* weight, int weight_dtype, int ldw, void* bq, void* scales, int N, int K, int wtype,
-                   int group, void* stream) {
+                   int group, int act_dtype, void* stream) {
+  if (!act_ok(act_dtype)) return ST_UNSUPPORTED;
   if (!weight || !bq || !scales) return ST_INVALID_ARG;
   if (N < 1 || K < 1 || group < 1 || ldw < K) return ST_INVALID_ARG;
-  if (weight_dtype != 0 && weight_dtype != 1) return ST_UNSUPPORTED;
+  if (weight_dtype < 0 || weight_dtype > 2) return ST_UNSUPPORTED;
   const int kind = (wtype >> 16) & 0xff, nbits = (wtype >> 8) & 0xff, e = (wtype >> 4) & 0xf, m = wtype & 0xf;
   if (kind > 2 || nbits < 1 || nbits > 8) return ST_UNSUPPORTED;
   if (kind == 2 && (nbits != 1 + e + m || e < 1 || m < 1)) return ST_UNSUPPORTED;
@@ -723,18 +740,26 @@ int b200q_quantize(const void* weight, int weight_dtype, int ldw, void* bq, void
     minv = -maxv;
   }
   cudaError_t err = quantize_launch(weight, weight_dtype, ldw, bq, scales, N, K, group, kind, nbits, e, m, minv, maxv,
-                                    reinterpret_cast<cudaStream_t>(stream));
+                                    act_dtype, reinterpret_cast<cudaStream_t>(stream));
   if (err != cudaSuccess) { g_last_cuda_error = (int)err; return ST_CUDA; }
   return ST_OK;
 }
 
 int b200q_device_status(void* workspace, int32_t status[4], void* stream) {
-  if (!workspace || !status) return ST_INVALID_ARG;
+  if (!status) return ST_INVALID_ARG;
+  const bool builtin = workspace == nullptr;  // the scratch of b200q_gemm_static_ws
+  if (builtin) {
+    const int st = static_ws_pointer(&workspace);
+    if (st != ST_OK) return st;
+  }
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   cudaError_t e = cudaMemcpyAsync(status, workspace, 16, cudaMemcpyDeviceToHost, s);
   if (e == cudaSuccess) e = cudaStreamSynchronize(s);
   if (e == cudaSuccess && status[0] != 0) {
-    e = cudaMemsetAsync(workspace, 0, 16, s);
+    // a launch that gave up may have left partial sums and arrival counters behind: the built-in
+    // scratch is put back to zero as a whole (its owner cannot do it), a caller's workspace only
+    // loses the report (the caller clears the rest, whose size only it knows)
+    e = cudaMemsetAsync(workspace, 0, builtin ? (size_t)B200Q_STATIC_WS_BYTES : 16, s);
     if (e == cudaSuccess) e = cudaStreamSynchronize(s);
   }
   if (e != cudaSuccess) { g_last_cuda_error = (int)e; return ST_CUDA; }

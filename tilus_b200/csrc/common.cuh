@@ -1,6 +1,7 @@
 // Shared definitions of the b200q kernels: status codes, workspace layout, launch
 // parameter blocks and small PTX helpers.
 #pragma once
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -54,7 +55,7 @@ struct GatherArgs {
 };
 
 struct StreamParams {
-  const __half* a;       // [M, K] row-major, leading dimension lda
+  const __half* a;       // [M, K] row-major, leading dimension lda (16-bit elements: fp16 or bf16, see act)
   const void* bq;        // b200 layout
   const __half* scales;  // [K/group, N], 16-byte aligned
   __half* c;             // [M, N], leading dimension ldc
@@ -69,10 +70,9 @@ struct StreamParams {
   int T_own;             // whole column tiles per CTA (<= NT / CPC); the rest is shared item-wise
   int pitch;             // shared-memory row pitch of the activation chunk, in halfs
   int stages;            // ring slots per warp (<= 8)
-  int debug_skip;        // diagnosis: 1 stream the weights but skip the math, 2 skip the loop, 3 and the staging
   int pdl;               // launch with programmatic stream serialization
-  unsigned long long* tl;  // timeline experiments (side builds with B200Q_TIMELINE only), else null
-  int tl_slot;
+  int ipt_shift;         // log2 of the items per column tile inside a k chunk when that is a power of two, else -1
+  int act;               // activation / scale / output dtype: 0 fp16, 1 bf16
   GatherArgs ga;
 };
 
@@ -93,8 +93,8 @@ struct UmmaParams {
   int kblocks_per_split; // 64-row k blocks per tile (even)
   int a_stages;          // activation stages in shared memory
   int grid;              // persistent CTAs: min(tiles, SMs)
-  int debug;             // timing experiments: 1 no decode, 2 no activation copies, 4 no stores, 8 no tcgen05.st
-  unsigned long long* tl;  // wait accounting (side builds with B200Q_TIMELINE only), else null
+  int m_group;           // row tiles per raster group: tiles of m_group row tiles x all column tiles run together
+  int act;               // activation / scale / output dtype: 0 fp16, 1 bf16
 };
 
 // ---- wide tcgen05 kernel (a few dozen rows): weights on the 256-column side of the MMA ---------
@@ -114,18 +114,28 @@ struct WideParams {
   int wg_stages;         // packed 128-row weight groups in the shared-memory ring
   int a_rows;            // rows per activation copy: 32, 64 or 128
   int grid;              // persistent CTAs: min(work items, SMs)
-  int debug;             // timing experiments (results are wrong): 2 no activation copies, 4 no operand
-                         // stores, 16 one contiguous weight copy per group, 32 no MMAs
-  unsigned long long* tl;  // wait accounting (side builds with B200Q_TIMELINE only), else null
+  int act;               // activation / scale / output dtype: 0 fp16, 1 bf16
 };
 
 // ---- dequantize kernel -----------------------------------------------------------------------
 struct DequantParams {
   const uint4* bq;
   const __half* scales;
-  __half* w;  // [K, N] row-major
+  __half* w;  // [K, N] row-major (16-bit elements of the activation dtype)
   int N, K, group, KB, NT;
+  int act;    // 0 fp16, 1 bf16
 };
+
+// two fp32 values rounded to the activation dtype (ACT 0: fp16, 1: bf16), low half first
+template <int ACT>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  if constexpr (ACT == 0) {
+    return bits_from_h2(__floats2half2_rn(lo, hi));
+  } else {
+    const __nv_bfloat162 b = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&b);
+  }
+}
 
 __device__ __forceinline__ uint4 ld_stream_u4(const uint4* p) {
   uint4 v;

@@ -184,6 +184,7 @@ B200Q_HD constexpr int pair_target() {
 }  // namespace b200q
 
 #if defined(__CUDACC__)
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 namespace b200q {
 
@@ -213,11 +214,29 @@ __device__ __forceinline__ __half2 pair_value(const uint32_t* w) {
   }
 }
 
-template <int VAR, int H>
+// pair H times the scale, in the arithmetic of the activation dtype.  ACT 0: one fp16 multiply,
+// fp16_rn(value * s).  ACT 1: the value (at most 8 significant bits, so exact in bf16) is
+// converted fp16 -> fp32 -> bf16 without rounding and multiplied once in bf16, bf16_rn(value * s):
+// the reference's cast to the activation dtype followed by its elementwise multiply
+// (examples/quantization/matmul_a16wx.py:316-320).  `scale2` holds the 16-bit scale in both halves.
+template <int VAR, int H, int ACT>
+__device__ __forceinline__ uint32_t pair_scaled(const uint32_t* w, uint32_t scale2) {
+  const __half2 v = pair_value<VAR, H>(w);
+  if constexpr (ACT == 0) {
+    return bits_from_h2(__hmul2(v, h2_from_bits(scale2)));
+  } else {
+    const float2 f = __half22float2(v);
+    const __nv_bfloat162 b = __floats2bfloat162_rn(f.x, f.y);
+    const __nv_bfloat162 r = __hmul2(b, *reinterpret_cast<const __nv_bfloat162*>(&scale2));
+    return *reinterpret_cast<const uint32_t*>(&r);
+  }
+}
+
+template <int VAR, int H, int ACT>
 struct UnitLoop {
-  static __device__ __forceinline__ void run(const uint32_t* w, __half2 scale, uint32_t* out) {
-    out[H] = bits_from_h2(__hmul2(pair_value<VAR, H>(w), scale));
-    if constexpr (H + 1 < 16) UnitLoop<VAR, H + 1>::run(w, scale, out);
+  static __device__ __forceinline__ void run(const uint32_t* w, uint32_t scale2, uint32_t* out) {
+    out[H] = pair_scaled<VAR, H, ACT>(w, scale2);
+    if constexpr (H + 1 < 16) UnitLoop<VAR, H + 1, ACT>::run(w, scale2, out);
   }
 };
 
@@ -234,10 +253,11 @@ __device__ __forceinline__ void unit_decode_linear(const uint32_t* w, uint32_t* 
   UnitLinLoop<VAR, 0>::run(w, out);
 }
 
-// out[h] = fp16_rn(value(k0+2h) * s) | fp16_rn(value(k0+2h+1) * s) << 16, h = 0..15
-template <int VAR>
-__device__ __forceinline__ void unit_decode_scaled(const uint32_t* w, __half2 scale, uint32_t* out) {
-  UnitLoop<VAR, 0>::run(w, scale, out);
+// out[h] = rn(value(k0+2h) * s) | rn(value(k0+2h+1) * s) << 16, h = 0..15, in fp16 (ACT 0) or bf16 (ACT 1);
+// scale2 = the 16-bit scale pattern in both halves
+template <int VAR, int ACT = 0>
+__device__ __forceinline__ void unit_decode_scaled(const uint32_t* w, uint32_t scale2, uint32_t* out) {
+  UnitLoop<VAR, 0, ACT>::run(w, scale2, out);
 }
 
 }  // namespace b200q

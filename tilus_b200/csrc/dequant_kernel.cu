@@ -1,4 +1,5 @@
-// Bit-exact dequantization W[K, N] = fp16_rn(value(q[k, n]) * s[k / group, n]) of a
+// Bit-exact dequantization W[K, N] = rn(value(q[k, n]) * s[k / group, n]) (one rounding, in the
+// activation dtype: fp16 or bf16) of a
 // b200-packed weight matrix.  Uses the same unit decoder as the GEMM kernels, so a
 // bit-for-bit match of this output with the CPU oracle pins the weight values the
 // GEMMs multiply by (reference semantics: examples/quantization/matmul_a16wx.py:316-320,
@@ -11,10 +12,10 @@
 
 namespace b200q {
 
-template <int VAR>
+template <int VAR, int ACT>
 __global__ void __launch_bounds__(128) dequant_kernel(const DequantParams p) {
   constexpr int B = var_bits(VAR);
-  __shared__ __half tile[4][128][16 + 2];  // per warp: one 128-row group x 16 columns
+  __shared__ unsigned short tile[4][128][16 + 2];  // per warp: one 128-row group x 16 columns
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int r = lane >> 2, j = lane & 3;
   const long long blk = (long long)blockIdx.x * 4 + warp;
@@ -32,20 +33,19 @@ __global__ void __launch_bounds__(128) dequant_kernel(const DequantParams p) {
       for (int q = 0; q < B; ++q) w[q] = __ldg(src + q);
       const int n = nt * 16 + h * 8 + r;
       const int k0 = kb * 512 + c * 128 + j * 32;
-      const __half s = p.scales[(size_t)(k0 / p.group) * p.N + n];
-      unit_decode_scaled<VAR>(w, __half2half2(s), out);
+      const uint32_t sbits = reinterpret_cast<const unsigned short*>(p.scales)[(size_t)(k0 / p.group) * p.N + n];
+      unit_decode_scaled<VAR, ACT>(w, sbits * 0x00010001u, out);
 #pragma unroll
       for (int pair = 0; pair < 16; ++pair) {
-        const __half2 x = h2_from_bits(out[pair]);
-        tile[warp][j * 32 + 2 * pair][h * 8 + r] = __low2half(x);
-        tile[warp][j * 32 + 2 * pair + 1][h * 8 + r] = __high2half(x);
+        tile[warp][j * 32 + 2 * pair][h * 8 + r] = (unsigned short)(out[pair] & 0xffffu);
+        tile[warp][j * 32 + 2 * pair + 1][h * 8 + r] = (unsigned short)(out[pair] >> 16);
       }
     }
     __syncwarp();
     // 128 rows x 16 columns -> global; each lane writes 16-byte half rows
     for (int idx = lane; idx < 128 * 2; idx += 32) {
       const int row = idx >> 1, hh = idx & 1;
-      __half tmp[8];
+      __align__(16) unsigned short tmp[8];
 #pragma unroll
       for (int q = 0; q < 8; ++q) tmp[q] = tile[warp][row][hh * 8 + q];
       const size_t k = (size_t)kb * 512 + c * 128 + row;
@@ -59,7 +59,8 @@ template <int VAR>
 static cudaError_t dq_launch_var(int var, const DequantParams& p, cudaStream_t stream) {
   if (var == VAR) {
     const long long nblk = (long long)p.NT * p.KB;
-    dequant_kernel<VAR><<<(unsigned)((nblk + 3) / 4), 128, 0, stream>>>(p);
+    if (p.act == 0) dequant_kernel<VAR, 0><<<(unsigned)((nblk + 3) / 4), 128, 0, stream>>>(p);
+    else dequant_kernel<VAR, 1><<<(unsigned)((nblk + 3) / 4), 128, 0, stream>>>(p);
     return cudaGetLastError();
   }
   if constexpr (VAR + 1 < VAR_COUNT) return dq_launch_var<VAR + 1>(var, p, stream);

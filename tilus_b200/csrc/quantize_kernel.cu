@@ -4,7 +4,8 @@
 // The arithmetic is QuantizedLinear.load_and_quantize of the reference
 // (examples/quantization/matmul_a16wx.py:470-528), operation for operation so that the codes
 // and scales come out bit-identical to the host path (tilus_b200/quantize.py):
-//   scales[g, n] = fp16_rn(max(absmax(w[n, group g]) / max_value, 1e-6))        (fp32 division)
+//   scales[g, n] = rn(max(absmax(w[n, group g]) / max_value, 1e-6))             (fp32 division, rounded to
+//                                                                                 the activation dtype)
 //   q            = clamp(w / float(scales), min_value, max_value)               (fp32 division)
 //   integer types: code = rint(q) & mask   (round half to even, as torch.round)
 //   float types:   code = the reference's fp32 -> sub-byte encode: round to nearest even at the
@@ -19,19 +20,25 @@
 namespace b200q {
 
 struct QuantParams {
-  const void* w;   // [N, K] row-major (row = output feature), leading dimension ldw, fp16 or fp32
-  int w_is_f32;
+  const void* w;   // [N, K] row-major (row = output feature), leading dimension ldw
+  int w_dtype;     // 0 fp16, 1 fp32, 2 bf16
   int ldw;
   uint32_t* bq;    // packed output, K*N*nbits/8 bytes
-  __half* scales;  // [K/group, N]
+  unsigned short* scales;  // [K/group, N], 16-bit patterns of the activation dtype
+  int act;         // 0 fp16, 1 bf16
   int N, K, KB, group;
   int kind, nbits, ebits, mbits;  // kind: 0 unsigned, 1 two's complement, 2 float
   float minv, maxv;
 };
 
 __device__ __forceinline__ float load_w(const QuantParams& p, size_t idx) {
-  return p.w_is_f32 ? reinterpret_cast<const float*>(p.w)[idx]
-                    : __half2float(reinterpret_cast<const __half*>(p.w)[idx]);
+  if (p.w_dtype == 1) return reinterpret_cast<const float*>(p.w)[idx];
+  if (p.w_dtype == 2) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.w)[idx]);
+  return __half2float(reinterpret_cast<const __half*>(p.w)[idx]);
+}
+__device__ __forceinline__ float load_scale(const QuantParams& p, size_t idx) {
+  const unsigned short b = p.scales[idx];
+  return p.act == 0 ? __half2float(__ushort_as_half(b)) : __uint_as_float((uint32_t)b << 16);
 }
 
 __global__ void __launch_bounds__(256) quant_scales_kernel(const QuantParams p) {
@@ -45,7 +52,11 @@ __global__ void __launch_bounds__(256) quant_scales_kernel(const QuantParams p) 
   for (int i = lane; i < p.group; i += 32) m = fmaxf(m, fabsf(load_w(p, base + i)));
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-  if (lane == 0) p.scales[(size_t)g * p.N + n] = __float2half_rn(fmaxf(__fdiv_rn(m, p.maxv), 1e-6f));
+  if (lane == 0) {
+    const float sc = fmaxf(__fdiv_rn(m, p.maxv), 1e-6f);
+    p.scales[(size_t)g * p.N + n] = p.act == 0 ? __half_as_ushort(__float2half_rn(sc))
+                                               : __bfloat16_as_ushort(__float2bfloat16_rn(sc));
+  }
 }
 
 // fp32 -> sub-byte float code (sign / e exponent bits / m mantissa bits)
@@ -84,7 +95,7 @@ __global__ void __launch_bounds__(128) quant_pack_kernel(const QuantParams p) {
   const int r = lane >> 2, j = lane & 3;
   const int n = nt * 16 + half * 8 + r;
   const int k0 = kb * 512 + c * 128 + j * 32;
-  const float s = __half2float(p.scales[(size_t)(k0 / p.group) * p.N + n]);
+  const float s = load_scale(p, (size_t)(k0 / p.group) * p.N + n);
   const uint32_t mask = (1u << p.nbits) - 1u;
   const uint32_t flip = p.kind == 1 ? (1u << (p.nbits - 1)) : 0u;  // offset binary for signed integers
   uint32_t words[8];
@@ -114,12 +125,14 @@ __global__ void __launch_bounds__(128) quant_pack_kernel(const QuantParams p) {
   for (int v = 0; v < p.nbits; ++v) dst[v] = words[v];
 }
 
-cudaError_t quantize_launch(const void* w, int w_is_f32, int ldw, void* bq, void* scales, int N, int K, int group,
-                            int kind, int nbits, int ebits, int mbits, float minv, float maxv, cudaStream_t stream) {
+cudaError_t quantize_launch(const void* w, int w_dtype, int ldw, void* bq, void* scales, int N, int K, int group,
+                            int kind, int nbits, int ebits, int mbits, float minv, float maxv, int act,
+                            cudaStream_t stream) {
   QuantParams p;
-  p.w = w; p.w_is_f32 = w_is_f32; p.ldw = ldw;
+  p.w = w; p.w_dtype = w_dtype; p.ldw = ldw;
   p.bq = reinterpret_cast<uint32_t*>(bq);
-  p.scales = reinterpret_cast<__half*>(scales);
+  p.scales = reinterpret_cast<unsigned short*>(scales);
+  p.act = act;
   p.N = N; p.K = K; p.KB = K / BLOCK_K; p.group = group;
   p.kind = kind; p.nbits = nbits; p.ebits = ebits; p.mbits = mbits;
   p.minv = minv; p.maxv = maxv;

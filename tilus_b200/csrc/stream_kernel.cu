@@ -57,23 +57,6 @@
 
 namespace b200q {
 
-#ifndef B200Q_DIAG_MODE
-#define B200Q_DIAG_MODE 0  // side builds: 4 no tensor-core work, 5 no decode, 6 normal numbers for subnormals
-#endif
-
-#ifdef B200Q_TIMELINE
-// Side builds only: per-launch, per-CTA %globaltimer stamps for timeline experiments.
-#define TL_STAMP(k)                                                                   \
-  do {                                                                                \
-    if (tl_base && lane == 0 && warp == 0) {                                          \
-      unsigned long long t_;                                                          \
-      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                          \
-      tl_base[k] = t_;                                                                \
-    }                                                                                 \
-  } while (0)
-#else
-#define TL_STAMP(k) do { } while (0)
-#endif
 
 // the B words of one unit, from shared memory (plain loads: the compiler may predicate and schedule them)
 template <int B>
@@ -95,17 +78,38 @@ __device__ __forceinline__ void ld_unit_words(const unsigned char* ptr, uint32_t
     for (int q = 0; q < B; ++q) w[q] = reinterpret_cast<const uint32_t*>(ptr)[q];
   }
 }
+
+// 16-bit pattern of an output value in the activation dtype (ACT 0: fp16, 1: bf16)
+template <int ACT>
+__device__ __forceinline__ unsigned short out_bits(float v) {
+  if constexpr (ACT == 0) return __half_as_ushort(__float2half_rn(v));
+  else return __bfloat16_as_ushort(__float2bfloat16_rn(v));
+}
 // One output value.  Plain launches write C; launches with a fused all-gather write the value
 // into the full output row of every rank (peer-mapped pointers, stores only).
-template <bool GATHER>
+template <bool GATHER, int ACT>
 __device__ __forceinline__ void store_out(const StreamParams& p, size_t gather_buf, int m, int n, float v) {
-  const __half h = __float2half_rn(v);
+  const unsigned short h = out_bits<ACT>(v);
   if constexpr (!GATHER) {
-    p.c[(size_t)m * p.ldc + n] = h;
+    reinterpret_cast<unsigned short*>(p.c)[(size_t)m * p.ldc + n] = h;
   } else {
     const size_t off = gather_buf + (size_t)m * p.ldc + p.ga.col_off + n;
-    for (int g = 0; g < p.ga.G; ++g) p.ga.out[g][off] = h;
+    for (int g = 0; g < p.ga.G; ++g) reinterpret_cast<unsigned short*>(p.ga.out[g])[off] = h;
   }
+}
+// a scale of the activation dtype (raw 16 bits in the shared-memory cache) as fp32
+template <int ACT>
+__device__ __forceinline__ float scale_f32(unsigned short bits) {
+  if constexpr (ACT == 0) return __half2float(__ushort_as_half(bits));
+  else return __uint_as_float((uint32_t)bits << 16);
+}
+// Two bf16 activations (one 32-bit word) as fp16: exact for every bf16 value whose magnitude lies in
+// fp16's range (bf16 carries 8 significant bits, fp16 11); larger magnitudes saturate at +-65504,
+// magnitudes below 2^-24 round to zero.  The mma.sync path multiplies in fp16.
+__device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t w) {
+  const float lo = fminf(fmaxf(__uint_as_float(w << 16), -65504.f), 65504.f);
+  const float hi = fminf(fmaxf(__uint_as_float(w & 0xffff0000u), -65504.f), 65504.f);
+  return bits_from_h2(__floats2half2_rn(lo, hi));
 }
 
 // one non-blocking look at an mbarrier phase
@@ -124,11 +128,16 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
 // Shared-memory layout (byte offsets from the dynamic smem base):
 //   [0, 1024)    mbarriers [warp][stage]   (16 warps x up to 8 stages)
 //   [1024, ...)  rings [warp][stage][ITEM_BYTES] of packed weights
-//   then         scale caches [warp][STREAM_SC_GROUPS][16] halfs: the scales of the warp's next groups
+//   then         scale caches [warp][STREAM_SC_GROUPS][16] 16-bit scales: those of the warp's next groups
 //   then         tile sums of the CTA's own column tiles [T_own][16 columns][8*MT rows] floats
 //   then         activation chunk [M][pitch] halfs, then group sums [groups][8*MT] floats
-template <int VAR, int MT, bool GATHER>
-__global__ void __launch_bounds__(STREAM_WARPS * 32, 2) stream_kernel(const StreamParams p) {
+//
+// MT = 1 (up to 8 rows): at most half an SM per CTA, so that two CTAs - of this launch or of the next
+// one in the stream - share an SM.  MT = 2 (up to 16 rows): one CTA per SM with all of its registers
+// and shared memory, which keeps the two 8-row accumulator sets in registers and a K chunk of the
+// 16 activation rows next to the rings.
+template <int VAR, int MT, bool GATHER, int ACT>
+__global__ void __launch_bounds__(STREAM_WARPS * 32, MT == 1 ? 2 : 1) stream_kernel(const StreamParams p) {
   constexpr int B = var_bits(VAR);
   constexpr int MP = 8 * MT;
   constexpr int BIAS = var_bias(VAR);
@@ -139,6 +148,13 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, 2) stream_kernel(const Stre
   constexpr int NWARPS = STREAM_WARPS;
   constexpr int SCG = STREAM_SC_GROUPS;
   constexpr float F = (float)(1u << lin_factor_log2(VAR));
+  // Where the linear pattern of a pair sits in the fp16 mantissa (bit T, decode.cuh int_target) sets a
+  // factor 2^T on its products.  8-bit integers and the float types have one T for all pairs.  4-bit
+  // integers have two (T = 0 for even pairs, 4 for odd ones): even and odd pairs go to separate
+  // accumulation chains and the odd chain is scaled by 2^-4 once per group.  Every other width has
+  // more than two, and its activations are pre-multiplied by 2^-T when they are staged.
+  constexpr bool CLASS2 = !var_is_float(VAR) && B == 4;
+  constexpr bool PRESCALE = !var_is_float(VAR) && B != 4 && B != 8;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const int NST = p.stages;
   const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem_raw);
@@ -155,13 +171,22 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, 2) stream_kernel(const Stre
   const int chunk = blockIdx.x % p.S, ci = blockIdx.x / p.S;
   const int kb_base = chunk * p.KBc;
   const int IPT = p.KBc * NI;  // items per column tile inside a k chunk
+  // x / IPT and x % IPT: a shift when IPT is a power of two (the host says so), which keeps integer
+  // divisions out of the start of every warp
+  const int ipt_shift = p.ipt_shift;
+  auto div_ipt = [&](int x, int& rem) -> int {
+    if (ipt_shift >= 0) { rem = x & (IPT - 1); return x >> ipt_shift; }
+    const int qd = x / IPT;
+    rem = x - qd * IPT;
+    return qd;
+  };
   // The CTA owns T_own whole column tiles; the NT - CPC * T_own tiles left over are cut into
   // equal item runs, one per CTA.  A CTA works through its left-over run first.
   const int own_tile0 = ci * p.T_own;
   const int left_tile0 = p.CPC * p.T_own;
-  const long long left_items = (long long)(p.NT - left_tile0) * IPT;
   int l0 = 0, l1 = 0;
-  if (left_items > 0) {  // 32-bit division where the products fit (64-bit division costs ~100 instructions)
+  if (left_tile0 < p.NT) {  // 32-bit division where the products fit (64-bit division costs ~100 instructions)
+    const long long left_items = (long long)(p.NT - left_tile0) * IPT;
     if (left_items <= 0x7fffffffLL / p.CPC) {
       l0 = (int)((unsigned)left_items * (unsigned)ci / (unsigned)p.CPC);
       l1 = (int)((unsigned)left_items * (unsigned)(ci + 1) / (unsigned)p.CPC);
@@ -175,17 +200,12 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, 2) stream_kernel(const Stre
   const int v0 = (int)((unsigned)n_total * (unsigned)warp / NWARPS), v1 = (int)((unsigned)n_total * (unsigned)(warp + 1) / NWARPS);
   // this warp's two item runs: cA items of left-over tiles, then cB items of the CTA's own tiles
   const int cA = v0 < n_left ? min(v1, n_left) - v0 : 0;
-  const int tileA = left_tile0 + (l0 + v0) / IPT, qA = (l0 + v0) % IPT;
+  int qA = 0, qB = 0;
+  const int tileA = cA > 0 ? left_tile0 + div_ipt(l0 + v0, qA) : 0;
   const int oB = max(v0, n_left) - n_left;
   const int cB = max(v1 - max(v0, n_left), 0);
-  const int tileB = own_tile0 + oB / IPT, qB = oB % IPT;
+  const int tileB = own_tile0 + div_ipt(oB, qB);
   const int n_items = cA + cB;
-
-#ifdef B200Q_TIMELINE
-  unsigned long long* tl_base = nullptr;
-  if (p.tl && p.tl_slot >= 0) tl_base = p.tl + ((size_t)p.tl_slot * gridDim.x + blockIdx.x) * 32;
-#endif
-  TL_STAMP(0);
   // the next kernel of the stream may become resident as soon as there is room for it
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
@@ -223,31 +243,17 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, 2) stream_kernel(const Stre
     const int itx = gidx / GI, gi = gidx - itx * GI;
     int tile, q;
     if (itx < cA) {
-      const int gg = l0 + v0 + itx;
-      tile = left_tile0 + gg / IPT; q = gg % IPT;
+      tile = left_tile0 + div_ipt(l0 + v0 + itx, q);
     } else {
-      const int o = oB + itx - cA;
-      tile = own_tile0 + o / IPT; q = o % IPT;
+      tile = own_tile0 + div_ipt(oB + itx - cA, q);
     }
     const int row = p.gshift >= 0 ? ((kb_base * 4 + q * GI + gi) >> p.gshift) : 0;
-    return reinterpret_cast<const uint4*>(p.scales + (size_t)row * p.N + tile * 16) + (lane & 1);
+    return reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(p.scales) + (size_t)row * p.N + tile * 16) + (lane & 1);
   };
   auto fill_scales = [&](int first) {
     const int gidx = first + (lane >> 1);
-    if (gidx < n_items * GI) {
-      const int itx = gidx / GI, gi = gidx - itx * GI;
-      int tile, q;
-      if (itx < cA) {
-        const int gg = l0 + v0 + itx;
-        tile = left_tile0 + gg / IPT; q = gg % IPT;
-      } else {
-        const int o = oB + itx - cA;
-        tile = own_tile0 + o / IPT; q = o % IPT;
-      }
-      const int row = p.gshift >= 0 ? ((kb_base * 4 + q * GI + gi) >> p.gshift) : 0;
-      const uint4 v = __ldg(reinterpret_cast<const uint4*>(p.scales + (size_t)row * p.N + tile * 16) + (lane & 1));
-      *reinterpret_cast<uint4*>(sc_warp + (gidx % SCG) * 32 + (lane & 1) * 16) = v;
-    }
+    if (gidx < n_items * GI)
+      *reinterpret_cast<uint4*>(sc_warp + (gidx % SCG) * 32 + (lane & 1) * 16) = __ldg(scale_src(gidx));
   };
   if (lane == 0) {
     for (int s = 0; s < NST; ++s) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar0 + s * 8) : "memory");
@@ -255,33 +261,31 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, 2) stream_kernel(const Stre
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   __syncwarp();
-  if (lane == 0 && p.debug_skip < 2)
+  if (lane == 0)
     for (int s = 0; s < NST && issued < n_items; ++s) issue_next(bar0 + s * 8, ring_s + s * SLOT_BYTES);
   // the first fill of the scale cache: requested now, stored after the activations have been
   // requested as well (a CTA that starts after its predecessor has finished then waits for the
   // two round trips at the same time, not one after the other)
   uint4 sc_first = make_uint4(0u, 0u, 0u, 0u);
-  const bool sc_first_valid = p.debug_skip < 2 && (lane >> 1) < n_items * GI;
+  const bool sc_first_valid = (lane >> 1) < n_items * GI;
   if (sc_first_valid) sc_first = __ldg(scale_src(lane >> 1));
   for (int idx = tid; idx < p.T_own * 16 * MP; idx += NWARPS * 32) sAcc[idx] = 0.f;
-
-  TL_STAMP(1);
   // everything below may read what the previous kernel of the stream wrote
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  TL_STAMP(2);
 
   // ---- fused all-gather: this launch is fused call number E + 1 of the rank (E is kept on the
   // device, so that the same launch can be replayed from a CUDA graph).  It may start once every
   // rank has finished call E: then the activations - if they are call E's gathered output - are
   // complete and nobody still reads the row buffer this call overwrites (bounded wait on this
   // rank's flags, one thread per source rank). ----
-  const __half* a_base = p.a;
+  const unsigned short* a_base = reinterpret_cast<const unsigned short*>(p.a);
   size_t gather_buf = 0;  // element offset of the row buffer this call writes, inside every rank's region
   unsigned epoch = 0;
   if (GATHER) {
     epoch = *reinterpret_cast<volatile const unsigned*>(p.ga.epoch);
     gather_buf = ((epoch + 1) & 1u) ? p.ga.buf_elems : 0;
-    if (p.ga.a_prev_off >= 0) a_base = p.ga.out[p.ga.rank] + ((epoch & 1u) ? p.ga.buf_elems : 0) + p.ga.a_prev_off;
+    if (p.ga.a_prev_off >= 0)
+      a_base = reinterpret_cast<const unsigned short*>(p.ga.out[p.ga.rank]) + ((epoch & 1u) ? p.ga.buf_elems : 0) + p.ga.a_prev_off;
     if (epoch != 0) {
       if (tid < p.ga.G) {
         uint64_t t0 = 0;
@@ -305,8 +309,9 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, 2) stream_kernel(const Stre
     }
   }
 
-  // ---- stage the activation chunk A[0:M, kb_base*512 : +KBc*512], pre-scaled ----
-  if (p.debug_skip < 3) {
+  // ---- stage the activation chunk A[0:M, kb_base*512 : +KBc*512] as fp16 (pre-scaled where the
+  // weight type needs it), and the zero-point term of every 128-row group ----
+  {
     const int kc = p.KBc * 512;
     const int vec_per_row = kc / 8;  // multiple of 64
     const int total = p.M * vec_per_row;
@@ -330,8 +335,12 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, 2) stream_kernel(const Stre
       while (vv >= vec_per_row) { vv -= vec_per_row; ++m; }
       const int kk = vv * 8;
       vv += NWARPS * 32;
-      uint4 v = GATHER ? *reinterpret_cast<const uint4*>(a_base + (size_t)m * p.lda + (size_t)kb_base * 512 + kk)
-                       : __ldg(reinterpret_cast<const uint4*>(a_base + (size_t)m * p.lda + (size_t)kb_base * 512 + kk));
+      const uint4* src = reinterpret_cast<const uint4*>(a_base + (size_t)m * p.lda + (size_t)kb_base * 512 + kk);
+      uint4 v = GATHER ? *src : __ldg(src);
+      if constexpr (ACT == 1) {
+        v.x = bf16x2_to_f16x2(v.x); v.y = bf16x2_to_f16x2(v.y);
+        v.z = bf16x2_to_f16x2(v.z); v.w = bf16x2_to_f16x2(v.w);
+      }
       __half2 x0 = h2_from_bits(v.x), x1 = h2_from_bits(v.y), x2 = h2_from_bits(v.z), x3 = h2_from_bits(v.w);
       if constexpr (BIAS != 0) {
         const float2 f0 = __half22float2(x0), f1 = __half22float2(x1), f2 = __half22float2(x2),
@@ -342,13 +351,13 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, 2) stream_kernel(const Stre
         sum += __shfl_xor_sync(0xffffffffu, sum, 4);
         sum += __shfl_xor_sync(0xffffffffu, sum, 8);
         if ((lane & 15) == 0) {
-          const float v = -(float)BIAS * sum * (1.0f / F);
+          const float nbv = -(float)BIAS * sum * (1.0f / F);
           float* q4 = sNb + (((kk >> 7) * MT + (m >> 3)) * 4 + ((m & 7) >> 1)) * 4 + (m & 1);
-          q4[0] = v;
-          q4[2] = v;
+          q4[0] = nbv;
+          q4[2] = nbv;
         }
       }
-      if constexpr (!var_is_float(VAR)) {
+      if constexpr (PRESCALE) {
         x0 = __hmul2(x0, mult[0]); x1 = __hmul2(x1, mult[1]);
         x2 = __hmul2(x2, mult[2]); x3 = __hmul2(x3, mult[3]);
       }
@@ -358,11 +367,10 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, 2) stream_kernel(const Stre
   }
   if (sc_first_valid) *reinterpret_cast<uint4*>(sc_warp + ((lane >> 1) % SCG) * 32 + (lane & 1) * 16) = sc_first;
   __syncthreads();  // activations staged, tile sums cleared, first scales cached
-  TL_STAMP(3);
 
   const int items_per_tile_total = p.KB * NI;
   bool ok = true;
-  if (n_items > 0 && p.debug_skip < 2) {
+  if (n_items > 0) {
     float acc[MT][4];
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
@@ -397,17 +405,9 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, 2) stream_kernel(const Stre
       const int run = min(IPT - q, seg_left);  // items of this column tile
       for (int e = 0; e < run; ++e, ++it, ++q) {
         const int g0 = q * GI;  // first 128-row group of the item, counted inside the chunk
-#ifdef B200Q_TIMELINE
-        if (it < 6) TL_STAMP(8 + 4 * it);
-#endif
         if (!__all_sync(0xffffffffu, mbar_test(bar, parity) ? 1 : 0)) {  // not there yet: bounded wait
           if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar, parity) ? 1 : 0)) { ok = false; break; }
         }
-#ifdef B200Q_TIMELINE
-        if (it == 0) TL_STAMP(4);
-        if (it == n_items - 1) TL_STAMP(5);
-        if (it < 6) TL_STAMP(9 + 4 * it);
-#endif
         const unsigned char* slot = ring_g + slot_off;
         if (it != 0 && (it * GI) % SCG == 0) {  // the cache has been used up: next SCG groups
           __syncwarp();
@@ -418,9 +418,9 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, 2) stream_kernel(const Stre
         float sf0[GI], sf1[GI];
 #pragma unroll
         for (int gi = 0; gi < GI; ++gi) {
-          const __half* sp = reinterpret_cast<const __half*>(sc_warp + ((it * GI + gi) % SCG) * 32) + r;
-          sf0[gi] = __half2float(sp[0]);
-          sf1[gi] = __half2float(sp[8]);
+          const unsigned short* sp = reinterpret_cast<const unsigned short*>(sc_warp + ((it * GI + gi) % SCG) * 32) + r;
+          sf0[gi] = scale_f32<ACT>(sp[0]);
+          sf1[gi] = scale_f32<ACT>(sp[8]);
         }
 #pragma unroll
         for (int gi = 0; gi < GI; ++gi) {
@@ -428,26 +428,13 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, 2) stream_kernel(const Stre
           ld_unit_words<B>(slot + w_lane + gi * (256 * B), w0);
           ld_unit_words<B>(slot + w_lane + gi * (256 * B) + 128 * B, w1);
           uint32_t W0[16], W1[16];
-          if (B200Q_DIAG_MODE == 5) {  // diagnosis: no decode
-#pragma unroll
-            for (int h = 0; h < 16; ++h) { W0[h] = w0[h % B] & 0x03ff03ffu; W1[h] = w1[h % B] & 0x03ff03ffu; }
-          } else {
-            unit_decode_linear<VAR>(w0, W0);
-            unit_decode_linear<VAR>(w1, W1);
-          }
+          unit_decode_linear<VAR>(w0, W0);
+          unit_decode_linear<VAR>(w1, W1);
           if (gi == GI - 1) {
-            // every lane has turned its copy of the last group into operands: refill the slot
+            // every lane has turned its copy of the item's last group into operands (the loads have
+            // returned, their values were used): lane 0 refills the slot
             __syncwarp();
-#ifdef B200Q_TIMELINE
-            if (it < 6) TL_STAMP(10 + 4 * it);
-#endif
-            if (lane == 0 && issued < n_items) {
-              asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-              issue_next(bar, ring_s + slot_off);
-            }
-#ifdef B200Q_TIMELINE
-            if (it < 6) TL_STAMP(11 + 4 * it);
-#endif
+            if (lane == 0 && issued < n_items) issue_next(bar, ring_s + slot_off);
           }
           const uint32_t koff = (uint32_t)((g0 + gi) * 320);  // bytes: 128 columns + 4 x 8 of padding per group
           // two accumulation chains per 8-row tile; the first starts from the zero-point term of the group
@@ -458,34 +445,30 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, 2) stream_kernel(const Stre
             if constexpr (BIAS != 0) nb = nb4[((g0 + gi) * MT + mt) * 4];
             d[mt][0][0] = nb.x; d[mt][0][1] = nb.y; d[mt][0][2] = nb.z; d[mt][0][3] = nb.w;
           }
-          if (B200Q_DIAG_MODE != 4) {
+          // pairs h = 4*sp .. 4*sp+3 of both units against the same four pairs of activations; with two
+          // mantissa positions (CLASS2) the even pairs feed chain 0 and the odd pairs chain 1
+          constexpr int P01 = CLASS2 ? 2 : 1;  // second pair of chain 0's MMA
+          constexpr int P10 = CLASS2 ? 1 : 2;  // first pair of chain 1's MMA
 #pragma unroll
-            for (int sp = 0; sp < 4; ++sp) {
+          for (int sp = 0; sp < 4; ++sp) {
 #pragma unroll
-              for (int mt = 0; mt < MT; ++mt) {
-                const uint4 av = *reinterpret_cast<const uint4*>(a_ptr[mt] + (koff & kmask[mt]) + sp * 16);
-                mma_m16n8k16(d[mt][0], W0[4 * sp], W1[4 * sp], W0[4 * sp + 1], W1[4 * sp + 1], av.x, av.y);
-                if (sp == 0)
-                  mma_m16n8k16_init(d[mt][1], W0[2], W1[2], W0[3], W1[3], av.z, av.w);
-                else
-                  mma_m16n8k16(d[mt][1], W0[4 * sp + 2], W1[4 * sp + 2], W0[4 * sp + 3], W1[4 * sp + 3], av.z, av.w);
-              }
+            for (int mt = 0; mt < MT; ++mt) {
+              const uint4 av = *reinterpret_cast<const uint4*>(a_ptr[mt] + (koff & kmask[mt]) + sp * 16);
+              const uint32_t b00 = av.x, b01 = CLASS2 ? av.z : av.y, b10 = CLASS2 ? av.y : av.z, b11 = av.w;
+              mma_m16n8k16(d[mt][0], W0[4 * sp], W1[4 * sp], W0[4 * sp + P01], W1[4 * sp + P01], b00, b01);
+              if (sp == 0)
+                mma_m16n8k16_init(d[mt][1], W0[P10], W1[P10], W0[3], W1[3], b10, b11);
+              else
+                mma_m16n8k16(d[mt][1], W0[4 * sp + P10], W1[4 * sp + P10], W0[4 * sp + 3], W1[4 * sp + 3], b10, b11);
             }
-          } else {  // diagnosis: no tensor-core work
-#pragma unroll
-            for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-              for (int e2 = 0; e2 < 4; ++e2) {
-                d[mt][0][e2] += __uint_as_float((W0[e2] ^ W1[e2 + 4]) & 0x007fffffu);
-                d[mt][1][e2] = __uint_as_float((W0[e2 + 8] ^ W1[e2 + 12]) & 0x007fffffu);
-              }
           }
+          constexpr float C1 = CLASS2 ? 0.0625f : 1.0f;  // chain 1 of a 4-bit type holds 2^4 x its products
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt) {
-            acc[mt][0] = fmaf(sf0[gi], d[mt][0][0] + d[mt][1][0], acc[mt][0]);
-            acc[mt][1] = fmaf(sf0[gi], d[mt][0][1] + d[mt][1][1], acc[mt][1]);
-            acc[mt][2] = fmaf(sf1[gi], d[mt][0][2] + d[mt][1][2], acc[mt][2]);
-            acc[mt][3] = fmaf(sf1[gi], d[mt][0][3] + d[mt][1][3], acc[mt][3]);
+            acc[mt][0] = fmaf(sf0[gi], fmaf(d[mt][1][0], C1, d[mt][0][0]), acc[mt][0]);
+            acc[mt][1] = fmaf(sf0[gi], fmaf(d[mt][1][1], C1, d[mt][0][1]), acc[mt][1]);
+            acc[mt][2] = fmaf(sf1[gi], fmaf(d[mt][1][2], C1, d[mt][0][2]), acc[mt][2]);
+            acc[mt][3] = fmaf(sf1[gi], fmaf(d[mt][1][3], C1, d[mt][0][3]), acc[mt][3]);
           }
         }
         slot_off += SLOT_BYTES; bar += 8;
@@ -538,8 +521,8 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, 2) stream_kernel(const Stre
                 const float2 v = __ldcg(src);
                 __stcg(src, make_float2(0.f, 0.f));
                 const int n = cur_tile * 16 + r + h * 8;
-                store_out<GATHER>(p, gather_buf, m0, n, v.x);
-                if (m0 + 1 < p.M) store_out<GATHER>(p, gather_buf, m0 + 1, n, v.y);
+                store_out<GATHER, ACT>(p, gather_buf, m0, n, v.x);
+                if (m0 + 1 < p.M) store_out<GATHER, ACT>(p, gather_buf, m0 + 1, n, v.y);
               }
             }
           }
@@ -555,7 +538,6 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, 2) stream_kernel(const Stre
       }
     }
   }
-  TL_STAMP(6);
   if (!ok) {
     // a bulk copy never completed: report it and give the copies still in flight a bounded
     // chance to land (the CTA must not retire under them)
@@ -574,7 +556,7 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, 2) stream_kernel(const Stre
     const int n0 = own_tile0 * 16, ncols = p.T_own * 16;
     if (p.S == 1) {  // all of K was here: write C
       for (int m = 0; m < p.M; ++m)
-        for (int n = tid; n < ncols; n += NWARPS * 32) store_out<GATHER>(p, gather_buf, m, n0 + n, sAcc[n * MP + m]);
+        for (int n = tid; n < ncols; n += NWARPS * 32) store_out<GATHER, ACT>(p, gather_buf, m, n0 + n, sAcc[n * MP + m]);
     } else {
       // other k chunks hold the rest: meet in the global scratch; the last chunk to arrive converts
       for (int idx = tid * 4; idx < ncols * MP; idx += NWARPS * 32 * 4)
@@ -604,10 +586,10 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, 2) stream_kernel(const Stre
           float4* src = reinterpret_cast<float4*>(p.partial + (size_t)n0 * MP + idx);
           const float4 v = __ldcg(src);
           __stcg(src, make_float4(0.f, 0.f, 0.f, 0.f));
-          store_out<GATHER>(p, gather_buf, m, n, v.x);
-          if (m + 1 < p.M) store_out<GATHER>(p, gather_buf, m + 1, n, v.y);
-          if (m + 2 < p.M) store_out<GATHER>(p, gather_buf, m + 2, n, v.z);
-          if (m + 3 < p.M) store_out<GATHER>(p, gather_buf, m + 3, n, v.w);
+          store_out<GATHER, ACT>(p, gather_buf, m, n, v.x);
+          if (m + 1 < p.M) store_out<GATHER, ACT>(p, gather_buf, m + 1, n, v.y);
+          if (m + 2 < p.M) store_out<GATHER, ACT>(p, gather_buf, m + 2, n, v.z);
+          if (m + 3 < p.M) store_out<GATHER, ACT>(p, gather_buf, m + 3, n, v.w);
         }
         if ((idx % (16 * MP)) == 0) p.counters[own_tile0 + t] = 0;
       }
@@ -633,9 +615,9 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, 2) stream_kernel(const Stre
   }
 }
 
-template <int VAR, int MT, bool GATHER>
+template <int VAR, int MT, bool GATHER, int ACT>
 static cudaError_t launch_one(const StreamParams& p, int smem_bytes, cudaStream_t stream) {
-  auto kern = stream_kernel<VAR, MT, GATHER>;
+  auto kern = stream_kernel<VAR, MT, GATHER, ACT>;
   static int configured_smem[16] = {0};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -660,13 +642,19 @@ static cudaError_t launch_one(const StreamParams& p, int smem_bytes, cudaStream_
   return cudaLaunchKernelEx(&cfg, kern, p);
 }
 
+template <int VAR, int MT, bool GATHER>
+static cudaError_t launch_act(const StreamParams& p, int smem_bytes, cudaStream_t stream) {
+  return p.act == 0 ? launch_one<VAR, MT, GATHER, 0>(p, smem_bytes, stream)
+                    : launch_one<VAR, MT, GATHER, 1>(p, smem_bytes, stream);
+}
+
 template <int VAR>
 static cudaError_t launch_var(int var, const StreamParams& p, int mt, int smem_bytes, cudaStream_t stream) {
   if constexpr (VAR % B200Q_NPARTS == B200Q_PART) {
     if (var == VAR) {
       if (p.ga.G > 0)
-        return mt == 1 ? launch_one<VAR, 1, true>(p, smem_bytes, stream) : launch_one<VAR, 2, true>(p, smem_bytes, stream);
-      return mt == 1 ? launch_one<VAR, 1, false>(p, smem_bytes, stream) : launch_one<VAR, 2, false>(p, smem_bytes, stream);
+        return mt == 1 ? launch_act<VAR, 1, true>(p, smem_bytes, stream) : launch_act<VAR, 2, true>(p, smem_bytes, stream);
+      return mt == 1 ? launch_act<VAR, 1, false>(p, smem_bytes, stream) : launch_act<VAR, 2, false>(p, smem_bytes, stream);
     }
   }
   if constexpr (VAR + 1 < VAR_COUNT) return launch_var<VAR + 1>(var, p, mt, smem_bytes, stream);

@@ -5,17 +5,6 @@
 
 namespace b200q {
 
-#ifdef B200Q_TIMELINE
-// Side builds only: cycles spent in each kind of wait, per role, written to p.tl[cta][16].
-#define WAIT_ACC(acc, call) ([&]() { const long long t_ = clock64(); const bool r_ = (call); acc += clock64() - t_; return r_; }())
-#define TL_DECL(n) long long n = 0
-#define TL_WRITE(slot, val) do { if (p.tl) p.tl[(size_t)blockIdx.x * 16 + (slot)] = (unsigned long long)(val); } while (0)
-#else
-#define WAIT_ACC(acc, call) (call)
-#define TL_DECL(n) do { } while (0)
-#define TL_WRITE(slot, val) do { } while (0)
-#endif
-
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
@@ -54,9 +43,12 @@ __device__ __forceinline__ uint64_t umma_smem_desc(uint32_t smem_addr) {
   d |= (uint64_t)2 << 61;                        // SWIZZLE_128B
   return d;
 }
-// instruction descriptor: D fp32, A/B fp16, both K-major, M = 128, N = tm
-__device__ __forceinline__ uint32_t umma_idesc(int tm) {
-  return (1u << 4) | ((uint32_t)(tm >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+// instruction descriptor of kind::f16: D fp32 (bit 4), A and B formats (bits 7-9 and 10-12: 0 fp16,
+// 1 bf16), both K-major, N = n (bits 17-22, in units of 8), M = 128 (bits 24-28, in units of 16)
+template <int ACT>
+__device__ __forceinline__ uint32_t umma_idesc(int n) {
+  return (1u << 4) | ((uint32_t)ACT << 7) | ((uint32_t)ACT << 10) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(128 >> 4) << 24);
 }
 
 // the 2*B words of two consecutive units, from a shared-memory byte address (8-byte aligned;
@@ -74,6 +66,33 @@ __device__ __forceinline__ void lds_two_units(uint32_t addr, uint32_t (&w)[2 * B
     for (int q = 0; q < B; ++q)
       asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(w[2 * q]), "=r"(w[2 * q + 1]) : "r"(addr + q * 8));
   }
+}
+
+// 32 consecutive tensor-memory columns of this thread's lane -> 32 registers (waits for the data)
+__device__ __forceinline__ void tmem_ld_32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, "
+      "%14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]),
+        "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]),
+        "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]),
+        "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// 16 consecutive tensor-memory columns of this thread's lane -> 16 registers (waits for the data)
+__device__ __forceinline__ void tmem_ld_16(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, "
+      "%14, %15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
 // 32 registers -> 32 consecutive tensor-memory columns of this thread's lane

@@ -47,6 +47,10 @@
 
 namespace b200q {
 
+#ifndef B200Q_EPI_EARLY
+#define B200Q_EPI_EARLY 1
+#endif
+
 constexpr int UMMA_THREADS = 608;   // 8 dequant warps, 8 epilogue warps, 2 producers, MMA warp
 constexpr int UMMA_SA_MAX = 6;      // activation stages (most)
 constexpr int UMMA_SW = 8;          // weight stages in tensor memory (32 columns each)
@@ -66,7 +70,7 @@ struct UmmaBarriers {
 
 __host__ __device__ constexpr int umma_wstage_bytes(int bits) { return 2048 * bits + 256; }
 
-template <int VAR>
+template <int VAR, int ACT>
 __global__ void __launch_bounds__(UMMA_THREADS, 1)
 umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
   constexpr int B = var_bits(VAR);
@@ -115,13 +119,25 @@ umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = bars->tmem_base;
 
-  // tile t -> (split, n_tile, m_tile), m fastest: CTAs that run together share weight columns
-#define TILE_COORDS(t)                                        \
-  const int m_tile = (t) % p.m_tiles;                         \
-  const int n_tile = ((t) / p.m_tiles) % p.n_tiles;           \
-  const int split = (t) / (p.m_tiles * p.n_tiles);            \
-  const int kk0 = split * nkk;                                \
-  const int m0 = m_tile * TM;                                 \
+  // tile t -> (split, n_tile, m_tile).  Inside a split the row tiles are taken in groups of MG: all
+  // column tiles of one group (row tile fastest) before the next group, so that the CTAs running
+  // together share weight columns and the activation rows of one group stay in L2 while the weights
+  // stream past them.  The last group holds the m_tiles % MG left-over row tiles.
+  const int MG = p.m_group;
+  const int tiles_per_split = p.m_tiles * p.n_tiles;
+  const int full_group_tiles = (p.m_tiles / MG) * MG * p.n_tiles;
+#define TILE_COORDS(t)                                                        \
+  const int split = (t) / tiles_per_split;                                    \
+  const int t_in = (t) - split * tiles_per_split;                             \
+  const bool in_full = t_in < full_group_tiles;                               \
+  const int gsz = in_full ? MG : p.m_tiles % MG;                              \
+  const int t_g = in_full ? t_in : t_in - full_group_tiles;                   \
+  const int grp_i = in_full ? t_g / (MG * p.n_tiles) : p.m_tiles / MG;        \
+  const int t_w = in_full ? t_g - grp_i * (MG * p.n_tiles) : t_g;             \
+  const int n_tile = t_w / gsz;                                               \
+  const int m_tile = grp_i * MG + (t_w - n_tile * gsz);                       \
+  const int kk0 = split * nkk;                                                \
+  const int m0 = m_tile * TM;                                                 \
   (void)m_tile; (void)n_tile; (void)split; (void)kk0; (void)m0;
 
   if (warp < 8) {
@@ -133,16 +149,12 @@ umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
     const uint32_t taddr_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16) + UMMA_WCOL0;
     int g_run = 0;  // groups consumed so far (all tiles)
     bool good = true;
-    TL_DECL(acc_g); TL_DECL(acc_w);
-#ifdef B200Q_TIMELINE
-    const long long t_begin = clock64();
-#endif
     for (int t = blockIdx.x; t < total_tiles && good; t += gridDim.x) {
       TILE_COORDS(t)
       const bool nvalid = n_tile * 128 + nl < p.N;
       for (int g = 0; g < ngrp; ++g, ++g_run) {
         const int gs = g_run % UMMA_WG;
-        if (!WAIT_ACC(acc_g, mbar_wait_abortable(BAR_ADDR(g_full, gs), (uint32_t)(g_run / UMMA_WG) & 1u, abort_flag))) { good = false; break; }
+        if (!mbar_wait_abortable(BAR_ADDR(g_full, gs), (uint32_t)(g_run / UMMA_WG) & 1u, abort_flag)) { good = false; break; }
         uint32_t w[2 * B];
         const uint32_t st = wring_s + (uint32_t)gs * WSTAGE;
         lds_two_units<B>(st + lane_off, w);
@@ -154,23 +166,17 @@ umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
           sbits = 0;
         }
         uint32_t out[32];
-        const __half2 s2 = __half2half2(__ushort_as_half(sbits));
-        if (p.debug & 1) {  // timing experiments: no decode
-#pragma unroll
-          for (int q = 0; q < 32; ++q) out[q] = w[q % (2 * B)];
-        } else {
-          unit_decode_scaled<VAR>(w, s2, out);
-          unit_decode_scaled<VAR>(w + B, s2, out + 16);
-        }
+        const uint32_t s2 = (uint32_t)sbits * 0x00010001u;  // the 16-bit scale in both halves
+        unit_decode_scaled<VAR, ACT>(w, s2, out);
+        unit_decode_scaled<VAR, ACT>(w + B, s2, out + 16);
         // the ring stage has been read (its values fed the arithmetic above)
         __syncwarp();
         if (lane == 0) mbar_arrive(BAR_ADDR(g_empty, gs));
         const int wi = 2 * g_run + grp;  // running 64-block index
         const int sw = wi % UMMA_SW;
-        if (!WAIT_ACC(acc_w, mbar_wait_abortable(BAR_ADDR(w_empty, sw), ((uint32_t)(wi / UMMA_SW) & 1u) ^ 1u, abort_flag))) { good = false; break; }
+        if (!mbar_wait_abortable(BAR_ADDR(w_empty, sw), ((uint32_t)(wi / UMMA_SW) & 1u) ^ 1u, abort_flag)) { good = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t taddr = taddr_lane + (uint32_t)(sw * 32);
-        if (!(p.debug & 8))
         asm volatile(
             "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, "
             "%14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(
@@ -187,13 +193,6 @@ umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
         if (lane == 0) mbar_arrive(BAR_ADDR(w_full, sw));
       }
     }
-#ifdef B200Q_TIMELINE
-    if (lane == 0 && (warp == 0 || warp == 4)) {
-      TL_WRITE(warp == 0 ? 0 : 3, clock64() - t_begin);
-      TL_WRITE(warp == 0 ? 1 : 4, acc_g);
-      TL_WRITE(warp == 0 ? 2 : 5, acc_w);
-    }
-#endif
   } else if (warp < 16) {
     // ================= epilogue: read D, write C (or add into the split-K scratch) =================
     // two warps per lane quadrant of tensor memory; they take alternate 32-column chunks of D
@@ -203,53 +202,49 @@ umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
     const uint32_t daddr = tmem + ((uint32_t)(ew * 32) << 16);
     int tile_it = 0;
     bool good = true;
-    TL_DECL(acc_d); TL_DECL(acc_epi);
     for (int t = blockIdx.x; t < total_tiles && good; t += gridDim.x, ++tile_it) {
       TILE_COORDS(t)
       const int n = n_tile * 128 + nl;
       const bool nvalid = n < p.N;
-      if (!WAIT_ACC(acc_d, mbar_wait_abortable(BAR_ADDR(d_full, 0), (uint32_t)tile_it & 1u, abort_flag))) { good = false; break; }
-#ifdef B200Q_TIMELINE
-      const long long t_epi = clock64();
-#endif
+      if (!mbar_wait_abortable(BAR_ADDR(d_full, 0), (uint32_t)tile_it & 1u, abort_flag)) { good = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      if (chunk0 * 32 >= TM) {  // nothing of this tile is this warp's (TM = 32): hand D back at once
+      if (p.splits == 1 && B200Q_EPI_EARLY) {
+        // Lane l holds column n of the tile, one accumulator row per tensor-memory column.  All of this
+        // warp's 32-row chunks are read and rounded to the output dtype first (two rows per register)
+        // and D is handed back at once, so that the next tile's MMAs run under the transposition and
+        // the stores below.
+        uint32_t hb[4][16];  // chunk ci, rows (2i, 2i+1) of column n
+#pragma unroll
+        for (int ci = 0; ci < 4; ++ci) {
+          const int c0 = chunk0 * 32 + ci * 64;
+          if (c0 < TM) {
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {  // 16 columns at a time: few registers live next to hb
+              uint32_t v[16];
+              tmem_ld_16(daddr + (uint32_t)(c0 + 16 * hh), v);
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                hb[ci][8 * hh + i] = pack2<ACT>(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+            }
+          }
+        }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncwarp();
         if (lane == 0) mbar_arrive(BAR_ADDR(d_empty, 0));
-      }
-      for (int c0 = chunk0 * 32; c0 < TM; c0 += 64) {
-        uint32_t v[32];
-        asm volatile(
-            "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, "
-            "%14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-            : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-              "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]),
-              "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]),
-              "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]),
-              "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-            : "r"(daddr + (uint32_t)c0)
-            : "memory");
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (c0 + 64 >= TM) {
-          // this warp's last chunk of D is in registers: the next tile's MMAs may overwrite it
-          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-          __syncwarp();
-          if (lane == 0) mbar_arrive(BAR_ADDR(d_empty, 0));
-        }
-        if (m0 + c0 < p.M && !(p.debug & 4)) {
-          if (p.splits == 1) {
-            // Lane l holds column n of 32 rows.  Three exchange rounds (lanes l ^ 1, l ^ 2, l ^ 4)
-            // transpose 8 x 8 blocks, so that a lane ends with 8 consecutive columns of 4 rows and
-            // writes each as one 16-byte store: a quarter of the store instructions of 4-byte stores.
-            const bool b0 = lane & 1, b1 = lane & 2, b2 = lane & 4;
-            uint32_t h[16];  // round 1: columns (n & ~1, +1) as half2, row 2 i + b0
+        // Three exchange rounds (lanes l ^ 1, l ^ 2, l ^ 4) transpose 8 x 8 blocks, so that a lane ends
+        // with 8 consecutive columns of 4 rows and writes each as one 16-byte store.
+        const bool b0 = lane & 1, b1 = lane & 2, b2 = lane & 4;
+        const int n8 = n_tile * 128 + (nl & ~7);
+#pragma unroll
+        for (int ci = 0; ci < 4; ++ci) {
+          const int c0 = chunk0 * 32 + ci * 64;
+          if (c0 < TM && m0 + c0 < p.M) {
+            uint32_t h[16];  // round 1: columns (n & ~1, +1), row 2 i + b0
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-              const uint32_t mine = b0 ? v[2 * i + 1] : v[2 * i];
-              const uint32_t give = b0 ? v[2 * i] : v[2 * i + 1];
-              const uint32_t got = __shfl_xor_sync(0xffffffffu, give, 1);
-              h[i] = bits_from_h2(__floats2half2_rn(__uint_as_float(b0 ? got : mine), __uint_as_float(b0 ? mine : got)));
+              const uint32_t got = __shfl_xor_sync(0xffffffffu, hb[ci][i], 1);
+              // even lane: (own row 2i, partner's row 2i); odd lane: (partner's row 2i+1, own row 2i+1)
+              h[i] = b0 ? __byte_perm(hb[ci][i], got, 0x3276) : __byte_perm(hb[ci][i], got, 0x5410);
             }
             uint32_t w2[8][2];  // round 2: columns (n & ~3 .. +3), row 4 j + 2 b1 + b0
 #pragma unroll
@@ -260,7 +255,6 @@ umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
               w2[j][0] = b1 ? got : mine;
               w2[j][1] = b1 ? mine : got;
             }
-            const int n8 = n_tile * 128 + (nl & ~7);
 #pragma unroll
             for (int k = 0; k < 4; ++k) {  // round 3: columns (n & ~7 .. +7), row 8 k + (lane & 7)
               const uint32_t m0r = b2 ? w2[2 * k + 1][0] : w2[2 * k][0], m1r = b2 ? w2[2 * k + 1][1] : w2[2 * k][1];
@@ -273,7 +267,56 @@ umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
                 *reinterpret_cast<uint4*>(p.c + (size_t)m * p.ldc + n8) = o;
               }
             }
-          } else {
+          }
+        }
+      } else {
+        if (chunk0 * 32 >= TM) {  // nothing of this tile is this warp's (TM = 32): hand D back at once
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive(BAR_ADDR(d_empty, 0));
+        }
+        for (int c0 = chunk0 * 32; c0 < TM; c0 += 64) {
+          uint32_t v[32];
+          tmem_ld_32(daddr + (uint32_t)c0, v);
+          if (c0 + 64 >= TM) {
+            // this warp's last chunk of D is in registers: the next tile's MMAs may overwrite it
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(BAR_ADDR(d_empty, 0));
+          }
+          if (m0 + c0 < p.M && p.splits == 1) {
+            const bool b0 = lane & 1, b1 = lane & 2, b2 = lane & 4;
+            uint32_t h[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const uint32_t mine = b0 ? v[2 * i + 1] : v[2 * i];
+              const uint32_t give = b0 ? v[2 * i] : v[2 * i + 1];
+              const uint32_t got = __shfl_xor_sync(0xffffffffu, give, 1);
+              h[i] = pack2<ACT>(__uint_as_float(b0 ? got : mine), __uint_as_float(b0 ? mine : got));
+            }
+            uint32_t w2[8][2];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const uint32_t mine = b1 ? h[2 * j + 1] : h[2 * j];
+              const uint32_t give = b1 ? h[2 * j] : h[2 * j + 1];
+              const uint32_t got = __shfl_xor_sync(0xffffffffu, give, 2);
+              w2[j][0] = b1 ? got : mine;
+              w2[j][1] = b1 ? mine : got;
+            }
+            const int n8 = n_tile * 128 + (nl & ~7);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const uint32_t m0r = b2 ? w2[2 * k + 1][0] : w2[2 * k][0], m1r = b2 ? w2[2 * k + 1][1] : w2[2 * k][1];
+              const uint32_t g0r = b2 ? w2[2 * k][0] : w2[2 * k + 1][0], g1r = b2 ? w2[2 * k][1] : w2[2 * k + 1][1];
+              const uint32_t r0 = __shfl_xor_sync(0xffffffffu, g0r, 4), r1 = __shfl_xor_sync(0xffffffffu, g1r, 4);
+              const int m = m0 + c0 + 8 * k + (lane & 7);
+              if (m < p.M && n8 < p.N) {
+                uint4 o;
+                o.x = b2 ? r0 : m0r; o.y = b2 ? r1 : m1r; o.z = b2 ? m0r : r0; o.w = b2 ? m1r : r1;
+                *reinterpret_cast<uint4*>(p.c + (size_t)m * p.ldc + n8) = o;
+              }
+            }
+          } else if (m0 + c0 < p.M) {
             // split-K: lanes 2i and 2i+1 exchange so that each adds two columns (8 bytes) of a row
             const bool odd = lane & 1;
 #pragma unroll
@@ -318,7 +361,7 @@ umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
               const int nn = n_tile * 128 + (idx & 63) * 2, m = m0 + (idx >> 6);
               if (idx < 64 * TM && nn < p.N && m < p.M) {
                 float2* src = reinterpret_cast<float2*>(p.partial + (size_t)m * p.N + nn);
-                *reinterpret_cast<__half2*>(p.c + (size_t)m * p.ldc + nn) = __floats2half2_rn(x[u].x, x[u].y);
+                *reinterpret_cast<uint32_t*>(p.c + (size_t)m * p.ldc + nn) = pack2<ACT>(x[u].x, x[u].y);
                 __stcg(src, make_float2(0.f, 0.f));
               }
             }
@@ -327,26 +370,18 @@ umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
         }
         asm volatile("bar.sync 1, 256;" ::: "memory");  // last_flag may be rewritten by the next tile
       }
-#ifdef B200Q_TIMELINE
-      acc_epi += clock64() - t_epi;
-#endif
     }
-#ifdef B200Q_TIMELINE
-    if (warp == 8 && lane == 0) { TL_WRITE(6, acc_d); TL_WRITE(7, acc_epi); }
-#endif
   } else if (warp == 16) {
     // ================= TMA producer: activations =================
     if (lane == 0) {
       int ai = 0;
       bool good = true;
-      TL_DECL(acc_ae);
       for (int t = blockIdx.x; t < total_tiles && good; t += gridDim.x) {
         TILE_COORDS(t)
         for (int i = 0; i < nkk; ++i, ++ai) {
           const int sa = ai % SA;
-          if (!WAIT_ACC(acc_ae, mbar_wait_abortable(BAR_ADDR(a_empty, sa), ((uint32_t)(ai / SA) & 1u) ^ 1u, abort_flag))) { good = false; break; }
+          if (!mbar_wait_abortable(BAR_ADDR(a_empty, sa), ((uint32_t)(ai / SA) & 1u) ^ 1u, abort_flag)) { good = false; break; }
           const uint32_t bar = BAR_ADDR(a_full, sa);
-          if (p.debug & 2) { mbar_arrive(bar); continue; }  // timing experiments: no activation traffic
           asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(stage_bytes)
                        : "memory");
           const int kx = (kk0 + i) * 64;
@@ -356,13 +391,11 @@ umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
               : "memory");
         }
       }
-      TL_WRITE(8, acc_ae);
     }
   } else if (warp == 17) {
     // ================= bulk-copy producer: packed weights and scales =================
     int g_run = 0;
     bool good = true;
-    TL_DECL(acc_ge);
     const unsigned char* bq = reinterpret_cast<const unsigned char*>(p.bq);
     for (int t = blockIdx.x; t < total_tiles && good; t += gridDim.x) {
       TILE_COORDS(t)
@@ -371,7 +404,7 @@ umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
       for (int g = 0; g < ngrp; ++g, ++g_run) {
         const int gs = g_run % UMMA_WG;
         int ok = 1;
-        if (lane == 0) ok = WAIT_ACC(acc_ge, mbar_wait_abortable(BAR_ADDR(g_empty, gs), ((uint32_t)(g_run / UMMA_WG) & 1u) ^ 1u, abort_flag)) ? 1 : 0;
+        if (lane == 0) ok = mbar_wait_abortable(BAR_ADDR(g_empty, gs), ((uint32_t)(g_run / UMMA_WG) & 1u) ^ 1u, abort_flag) ? 1 : 0;
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) { good = false; break; }
         const uint32_t bar = BAR_ADDR(g_full, gs);
@@ -401,25 +434,20 @@ umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
         }
       }
     }
-    if (lane == 0) TL_WRITE(9, acc_ge);
   } else {
     // ================= MMA issuer =================
     if (lane == 0) {
-      const uint32_t idesc = umma_idesc(TM);
+      const uint32_t idesc = umma_idesc<ACT>(TM);
       bool good = true;
       int ai = 0, tile_it = 0;
-      TL_DECL(acc_de); TL_DECL(acc_af); TL_DECL(acc_wf);
-#ifdef B200Q_TIMELINE
-      const long long t_begin = clock64();
-#endif
       for (int t = blockIdx.x; t < total_tiles && good; t += gridDim.x, ++tile_it) {
         // D must have been read out by the epilogue of the previous tile
-        if (!WAIT_ACC(acc_de, mbar_wait_abortable(BAR_ADDR(d_empty, 0), ((uint32_t)tile_it & 1u) ^ 1u, abort_flag))) { good = false; break; }
+        if (!mbar_wait_abortable(BAR_ADDR(d_empty, 0), ((uint32_t)tile_it & 1u) ^ 1u, abort_flag)) { good = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         for (int i = 0; i < nkk; ++i, ++ai) {
           const int sa = ai % SA, sw = ai % UMMA_SW;
-          good = WAIT_ACC(acc_af, mbar_wait_abortable(BAR_ADDR(a_full, sa), (uint32_t)(ai / SA) & 1u, abort_flag)) &&
-                 WAIT_ACC(acc_wf, mbar_wait_abortable(BAR_ADDR(w_full, sw), (uint32_t)(ai / UMMA_SW) & 1u, abort_flag));
+          good = mbar_wait_abortable(BAR_ADDR(a_full, sa), (uint32_t)(ai / SA) & 1u, abort_flag) &&
+                 mbar_wait_abortable(BAR_ADDR(w_full, sw), (uint32_t)(ai / UMMA_SW) & 1u, abort_flag);
           if (!good) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint64_t bdesc = umma_smem_desc(smem_base + (uint32_t)sa * stage_bytes);
@@ -448,9 +476,6 @@ umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
                            BAR_ADDR(d_full, 0))
                        : "memory");
       }
-#ifdef B200Q_TIMELINE
-      TL_WRITE(10, clock64() - t_begin); TL_WRITE(11, acc_de); TL_WRITE(12, acc_af); TL_WRITE(13, acc_wf);
-#endif
     }
   }
 
@@ -472,10 +497,10 @@ umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
 #undef TILE_COORDS
 }
 
-template <int VAR>
+template <int VAR, int ACT>
 static cudaError_t umma_launch_one(const UmmaParams& p, const CUtensorMap& tmap, int smem_bytes,
                                    cudaStream_t stream) {
-  auto kern = umma_kernel<VAR>;
+  auto kern = umma_kernel<VAR, ACT>;
   static int configured_smem[16] = {0};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -492,7 +517,9 @@ template <int VAR>
 static cudaError_t umma_launch_var(int var, const UmmaParams& p, const CUtensorMap& tmap, int smem_bytes,
                                    cudaStream_t stream) {
   if constexpr (VAR % B200Q_NPARTS == B200Q_PART) {
-    if (var == VAR) return umma_launch_one<VAR>(p, tmap, smem_bytes, stream);
+    if (var == VAR)
+      return p.act == 0 ? umma_launch_one<VAR, 0>(p, tmap, smem_bytes, stream)
+                        : umma_launch_one<VAR, 1>(p, tmap, smem_bytes, stream);
   }
   if constexpr (VAR + 1 < VAR_COUNT) return umma_launch_var<VAR + 1>(var, p, tmap, smem_bytes, stream);
   else return cudaErrorInvalidValue;

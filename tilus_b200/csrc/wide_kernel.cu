@@ -64,7 +64,7 @@ struct WideBarriers {
 
 __host__ __device__ constexpr int wide_wstage_bytes(int bits) { return 4096 * bits + 512; }
 
-template <int VAR>
+template <int VAR, int ACT>
 __global__ void __launch_bounds__(WIDE_THREADS, 1)
 wide_kernel(const WideParams p, const __grid_constant__ CUtensorMap tmap_a) {
   constexpr int B = var_bits(VAR);
@@ -90,9 +90,6 @@ wide_kernel(const WideParams p, const __grid_constant__ CUtensorMap tmap_a) {
 #define BAR_ADDR(field, i) (bars_s + (uint32_t)offsetof(WideBarriers, field) + (uint32_t)(i) * 8u)
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-#ifdef B200Q_TIMELINE
-  const long long t_kernel = clock64();
-#endif
   const int total_items = p.splits * p.n_tiles * p.m_tiles;
   const int nkk = p.kblocks_per_split;  // 64-blocks per work item (even)
   const int ngrp = nkk >> 1;
@@ -149,22 +146,18 @@ wide_kernel(const WideParams p, const __grid_constant__ CUtensorMap tmap_a) {
     const uint32_t usw = B == 4 ? (uint32_t)((nl >> 1) & 1) : (B == 8 ? (uint32_t)(nl & 1) : 0u);
     int g_run = 0;  // groups passed so far (all work items)
     bool good = true;
-    TL_DECL(acc_g); TL_DECL(acc_be);
-#ifdef B200Q_TIMELINE
-    const long long t_begin = clock64();
-#endif
     for (int w = blockIdx.x; w < total_items && good; w += gridDim.x) {
       ITEM_COORDS(w)
       const bool nvalid = n_tile * 256 + nl < p.N;
       for (int g = 0; g < ngrp && good; ++g, ++g_run) {
         if ((g_run & 1) != set) continue;  // the other set's group
         const int gs = g_run % WG;
-        if (!WAIT_ACC(acc_g, mbar_wait_abortable(BAR_ADDR(g_full, gs), (uint32_t)(g_run / WG) & 1u, abort_flag))) { good = false; break; }
+        if (!mbar_wait_abortable(BAR_ADDR(g_full, gs), (uint32_t)(g_run / WG) & 1u, abort_flag)) { good = false; break; }
         const uint32_t st = w_s + (uint32_t)gs * WSTAGE;
         unsigned short sbits;
         asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sbits) : "r"(st + 4096u * B + (uint32_t)nl * 2u));
         if (!nvalid) sbits = 0;
-        const __half2 s2 = __half2half2(__ushort_as_half(sbits));
+        const uint32_t s2 = (uint32_t)sbits * 0x00010001u;  // the 16-bit scale in both halves
         // all of this column's codes of the group go to registers first, so that the ring stage is
         // free for the next copy while the decode and the stores below run
         // Adjacent columns lie 16 * B bytes apart in the ring stage, so lanes reading the same unit of
@@ -199,13 +192,12 @@ wide_kernel(const WideParams p, const __grid_constant__ CUtensorMap tmap_a) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {  // the two 64-row blocks of the group
           uint32_t out[32];
-          unit_decode_scaled<VAR>(wq[h][0], s2, out);
-          unit_decode_scaled<VAR>(wq[h][1], s2, out + 16);
+          unit_decode_scaled<VAR, ACT>(wq[h][0], s2, out);
+          unit_decode_scaled<VAR, ACT>(wq[h][1], s2, out + 16);
           const int bi = 2 * g_run + h;  // running 64-block index
           const int sb = bi % WIDE_SB;
-          if (!WAIT_ACC(acc_be, mbar_wait_abortable(BAR_ADDR(b_empty, sb), ((uint32_t)(bi / WIDE_SB) & 1u) ^ 1u, abort_flag))) { good = false; break; }
+          if (!mbar_wait_abortable(BAR_ADDR(b_empty, sb), ((uint32_t)(bi / WIDE_SB) & 1u) ^ 1u, abort_flag)) { good = false; break; }
           const uint32_t dst = b_s + (uint32_t)sb * BSTAGE + row_off;
-          if (!(p.debug & 4))
 #pragma unroll
           for (int c = 0; c < 8; ++c)  // out[0..15] is unit usw (chunks 4 * usw ..), out[16..31] the other one
             asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst + (((uint32_t)c ^ sw ^ (usw << 2)) << 4)),
@@ -218,9 +210,6 @@ wide_kernel(const WideParams p, const __grid_constant__ CUtensorMap tmap_a) {
         }
       }
     }
-#ifdef B200Q_TIMELINE
-    if (tid == 0) { TL_WRITE(5, clock64() - t_begin); TL_WRITE(6, acc_g); TL_WRITE(7, acc_be); }
-#endif
   } else if (warp < 20) {
     // ================= epilogue: read D, write C (or add into the split-K scratch) =================
     asm volatile("griddepcontrol.wait;" ::: "memory");  // writes C and the split-K scratch
@@ -258,10 +247,10 @@ wide_kernel(const WideParams p, const __grid_constant__ CUtensorMap tmap_a) {
             for (int q = 0; q < 32; q += 8) {
               if (q < ncols) {
                 uint4 o;
-                o.x = bits_from_h2(__floats2half2_rn(__uint_as_float(v[q]), __uint_as_float(v[q + 1])));
-                o.y = bits_from_h2(__floats2half2_rn(__uint_as_float(v[q + 2]), __uint_as_float(v[q + 3])));
-                o.z = bits_from_h2(__floats2half2_rn(__uint_as_float(v[q + 4]), __uint_as_float(v[q + 5])));
-                o.w = bits_from_h2(__floats2half2_rn(__uint_as_float(v[q + 6]), __uint_as_float(v[q + 7])));
+                o.x = pack2<ACT>(__uint_as_float(v[q]), __uint_as_float(v[q + 1]));
+                o.y = pack2<ACT>(__uint_as_float(v[q + 2]), __uint_as_float(v[q + 3]));
+                o.z = pack2<ACT>(__uint_as_float(v[q + 4]), __uint_as_float(v[q + 5]));
+                o.w = pack2<ACT>(__uint_as_float(v[q + 6]), __uint_as_float(v[q + 7]));
                 *reinterpret_cast<uint4*>(dst + q) = o;
               }
             }
@@ -316,10 +305,10 @@ wide_kernel(const WideParams p, const __grid_constant__ CUtensorMap tmap_a) {
                 const int mm = m0 + idx / per_row, nn = n_tile * 256 + (idx % per_row) * 8;
                 float4* src = reinterpret_cast<float4*>(p.partial + (size_t)mm * p.N + nn);
                 uint4 o;
-                o.x = bits_from_h2(__floats2half2_rn(x[u][0].x, x[u][0].y));
-                o.y = bits_from_h2(__floats2half2_rn(x[u][0].z, x[u][0].w));
-                o.z = bits_from_h2(__floats2half2_rn(x[u][1].x, x[u][1].y));
-                o.w = bits_from_h2(__floats2half2_rn(x[u][1].z, x[u][1].w));
+                o.x = pack2<ACT>(x[u][0].x, x[u][0].y);
+                o.y = pack2<ACT>(x[u][0].z, x[u][0].w);
+                o.z = pack2<ACT>(x[u][1].x, x[u][1].y);
+                o.w = pack2<ACT>(x[u][1].z, x[u][1].w);
                 *reinterpret_cast<uint4*>(p.c + (size_t)mm * p.ldc + nn) = o;
                 __stcg(src, make_float4(0.f, 0.f, 0.f, 0.f));
                 __stcg(src + 1, make_float4(0.f, 0.f, 0.f, 0.f));
@@ -344,10 +333,9 @@ wide_kernel(const WideParams p, const __grid_constant__ CUtensorMap tmap_a) {
           if (!mbar_wait_abortable(BAR_ADDR(a_empty, sa), ((uint32_t)(ai / WIDE_SA) & 1u) ^ 1u, abort_flag)) { good = false; break; }
           const uint32_t bar = BAR_ADDR(a_full, sa);
           asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar),
-                       "r"((p.debug & 2) ? 0u : ASTAGE)
+                       "r"(ASTAGE)
                        : "memory");
           const int kx = (kk0 + i) * 64;
-          if (!(p.debug & 2))
           asm volatile(
               "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
               ::"r"(a_s + (uint32_t)sa * ASTAGE), "l"(&tmap_a), "r"(bar), "r"(kx), "r"(m0)
@@ -379,16 +367,7 @@ wide_kernel(const WideParams p, const __grid_constant__ CUtensorMap tmap_a) {
                        : "memory");
         __syncwarp();
         const int G = (kk0 >> 1) + g;  // 128-row group of K
-        if (p.debug & 16) {
-          if (lane == 0) {
-            const unsigned char* src = bq + ((size_t)nt0 * p.KB + (G >> 2) * 4) * (size_t)(1024 * B) +
-                                       (size_t)(G & 3) * (4096 * B);
-            asm volatile(
-                "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-                "l"(src), "r"((uint32_t)pieces * 256u * B), "r"(bar)
-                : "memory");
-          }
-        } else if (lane < pieces) {
+        if (lane < pieces) {
           const unsigned char* src = bq + ((size_t)(nt0 + lane) * p.KB + (G >> 2)) * (size_t)(1024 * B) +
                                      (size_t)(G & 3) * (256 * B);
           asm volatile(
@@ -411,29 +390,23 @@ wide_kernel(const WideParams p, const __grid_constant__ CUtensorMap tmap_a) {
   } else {
     // ================= MMA issuer =================
     if (lane == 0) {
-      // instruction descriptor: D fp32, A/B fp16, both K-major, M = 128, N = 256
-      const uint32_t idesc = (1u << 4) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+      const uint32_t idesc = umma_idesc<ACT>(256);  // M = 128, N = 256
       bool good = true;
       int bi = 0, it = 0;
-      TL_DECL(acc_de); TL_DECL(acc_af); TL_DECL(acc_bf);
-#ifdef B200Q_TIMELINE
-      const long long t_begin = clock64();
-#endif
       for (int w = blockIdx.x; w < total_items && good; w += gridDim.x, ++it) {
         const int buf = it & 1;
         // the accumulator must have been read out by the epilogue two items ago
-        if (!WAIT_ACC(acc_de, mbar_wait_abortable(BAR_ADDR(d_empty, buf), ((uint32_t)(it >> 1) & 1u) ^ 1u, abort_flag))) { good = false; break; }
+        if (!mbar_wait_abortable(BAR_ADDR(d_empty, buf), ((uint32_t)(it >> 1) & 1u) ^ 1u, abort_flag)) { good = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t d_tmem = tmem + (uint32_t)(buf * 256);
         for (int i = 0; i < nkk; ++i, ++bi) {
           const int sa = bi % WIDE_SA, sb = bi % WIDE_SB;
-          good = WAIT_ACC(acc_af, mbar_wait_abortable(BAR_ADDR(a_full, sa), (uint32_t)(bi / WIDE_SA) & 1u, abort_flag)) &&
-                 WAIT_ACC(acc_bf, mbar_wait_abortable(BAR_ADDR(b_full, sb), (uint32_t)(bi / WIDE_SB) & 1u, abort_flag));
+          good = mbar_wait_abortable(BAR_ADDR(a_full, sa), (uint32_t)(bi / WIDE_SA) & 1u, abort_flag) &&
+                 mbar_wait_abortable(BAR_ADDR(b_full, sb), (uint32_t)(bi / WIDE_SB) & 1u, abort_flag);
           if (!good) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint64_t adesc = umma_smem_desc(a_s + (uint32_t)sa * ASTAGE);
           const uint64_t bdesc = umma_smem_desc(b_s + (uint32_t)sb * BSTAGE);
-          if (!(p.debug & 32))
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks) {
             const uint32_t accumulate = (i > 0 || ks > 0) ? 1u : 0u;
@@ -458,10 +431,6 @@ wide_kernel(const WideParams p, const __grid_constant__ CUtensorMap tmap_a) {
                            BAR_ADDR(d_full, buf))
                        : "memory");
       }
-#ifdef B200Q_TIMELINE
-      TL_WRITE(0, clock64() - t_begin); TL_WRITE(1, acc_de); TL_WRITE(2, acc_af); TL_WRITE(3, acc_bf);
-      TL_WRITE(4, t_begin - t_kernel);
-#endif
     }
   }
 
@@ -479,16 +448,13 @@ wide_kernel(const WideParams p, const __grid_constant__ CUtensorMap tmap_a) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(WIDE_TMEM_COLS) : "memory");
   }
-#ifdef B200Q_TIMELINE
-  if (tid == 0) TL_WRITE(8, clock64() - t_kernel);
-#endif
 #undef BAR_ADDR
 #undef ITEM_COORDS
 }
 
-template <int VAR>
+template <int VAR, int ACT>
 static cudaError_t wide_launch_one(const WideParams& p, const CUtensorMap& tmap, int smem_bytes, cudaStream_t stream) {
-  auto kern = wide_kernel<VAR>;
+  auto kern = wide_kernel<VAR, ACT>;
   static int configured_smem[16] = {0};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -514,7 +480,9 @@ template <int VAR>
 static cudaError_t wide_launch_var(int var, const WideParams& p, const CUtensorMap& tmap, int smem_bytes,
                                    cudaStream_t stream) {
   if constexpr (VAR % B200Q_NPARTS == B200Q_PART) {
-    if (var == VAR) return wide_launch_one<VAR>(p, tmap, smem_bytes, stream);
+    if (var == VAR)
+      return p.act == 0 ? wide_launch_one<VAR, 0>(p, tmap, smem_bytes, stream)
+                        : wide_launch_one<VAR, 1>(p, tmap, smem_bytes, stream);
   }
   if constexpr (VAR + 1 < VAR_COUNT) return wide_launch_var<VAR + 1>(var, p, tmap, smem_bytes, stream);
   else return cudaErrorInvalidValue;

@@ -19,7 +19,9 @@ import torch
 from torch import nn
 
 from . import ops, packing, quantize
-from .dtypes import KIND_UINT, act_dtype, float16, weight_dtype
+from .dtypes import KIND_UINT, act_dtype, weight_dtype
+
+_TORCH_ACT = {"float16": torch.float16, "bfloat16": torch.bfloat16}
 
 
 class QuantizedLinear(nn.Module):
@@ -28,8 +30,7 @@ class QuantizedLinear(nn.Module):
         super().__init__()
         x_dtype = act_dtype(x_dtype)
         w_dtype = weight_dtype(w_dtype)
-        if x_dtype is not float16:
-            raise NotImplementedError("only float16 activations are implemented")
+        self.act_torch_dtype = _TORCH_ACT[x_dtype.name]  # float16 or bfloat16, as the reference (matmul_a16wx.py:418-419)
         # The reference class demands float or signed types ("symmetric quantization",
         # matmul_a16wx.py:421-423) while its kernel takes any 1-8 bit type (:163-165).
         # Unsigned types are accepted here with an explicit zero point.
@@ -54,7 +55,7 @@ class QuantizedLinear(nn.Module):
             torch.empty(out_features * in_features * w_dtype.nbits // 8, dtype=torch.uint8), requires_grad=False
         )
         self.scales = nn.Parameter(
-            torch.empty(in_features // group_size, out_features, dtype=torch.float16), requires_grad=False
+            torch.empty(in_features // group_size, out_features, dtype=self.act_torch_dtype), requires_grad=False
         )
         self.register_buffer("layout_version", torch.tensor(packing.LAYOUT_VERSION, dtype=torch.int32))
         self._ws_need = {}  # workspace bytes per batch size M (filled on first use)
@@ -68,10 +69,11 @@ class QuantizedLinear(nn.Module):
                              "(unsigned codes come in through load_codes / load_packed)")
         dev = self.quantized_weight.device
         if dev.type == "cuda":  # one fused pass on the GPU: scales, codes, packing
-            packed, scales = quantize.quantize_and_pack(weight.to(dev), self.w_dtype, self.group_size)
+            packed, scales = quantize.quantize_and_pack(weight.to(dev), self.w_dtype, self.group_size,
+                                                        self.act_torch_dtype)
             self.load_packed(packed, scales, layout="b200")
             return
-        codes, scales = quantize.quantize_weight(weight.to(dev), self.w_dtype, self.group_size)
+        codes, scales = quantize.quantize_weight(weight.to(dev), self.w_dtype, self.group_size, self.act_torch_dtype)
         self.load_codes(codes, scales)
 
     def load_codes(self, codes: torch.Tensor, scales: torch.Tensor):
@@ -131,7 +133,7 @@ class QuantizedLinear(nn.Module):
         return packing.deinterleave(self.quantized_weight.data, self.w_dtype, self.in_features, self.out_features)
 
     def dequantized_weight(self) -> torch.Tensor:
-        """fp16 [in_features, out_features]: the weights forward() multiplies by."""
+        """[in_features, out_features] in the activation dtype: the weights forward() multiplies by."""
         return ops.dequantize(self.quantized_weight.data, self.scales.data, self.w_dtype, self.group_size,
                               self.zero_point)
 
@@ -150,11 +152,12 @@ class QuantizedLinear(nn.Module):
         not given).  Copy-in, GEMM and copy-out are queued on the layer's current stream by one
         library call (b200q_gemm_host); synchronise the stream before reading the result."""
         if out_host is None:
-            out_host = torch.empty(x_host.shape[0], self.out_features, dtype=torch.float16).pin_memory()
+            out_host = torch.empty(x_host.shape[0], self.out_features, dtype=self.act_torch_dtype).pin_memory()
         return ops.linear_forward_host(x_host, out_host, self.quantized_weight.data, self.scales.data,
                                        self.w_dtype.code, self.zero_point, self.group_size, self.in_features,
                                        self.out_features, self._ws_need)
 
     def extra_repr(self) -> str:
-        return (f"in_features={self.in_features}, out_features={self.out_features}, w_dtype={self.w_dtype.name}, "
+        return (f"in_features={self.in_features}, out_features={self.out_features}, x_dtype={self.x_dtype.name}, "
+                f"w_dtype={self.w_dtype.name}, "
                 f"group_size={self.group_size}, zero_point={self.zero_point}")

@@ -19,6 +19,15 @@ from .packing import BLOCK_K, BLOCK_N
 _workspaces = {}
 
 
+def act_code(dtype: torch.dtype) -> int:
+    """Activation dtype tag of the C ABI (B200Q_F16 / B200Q_BF16)."""
+    if dtype == torch.float16:
+        return _lib.ACT_F16
+    if dtype == torch.bfloat16:
+        return _lib.ACT_BF16
+    raise TypeError(f"activations, scales and outputs are float16 or bfloat16, got {dtype}")
+
+
 def _stream_ptr(device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
@@ -58,8 +67,9 @@ def quantized_matmul(a: torch.Tensor, bq: torch.Tensor, scales: torch.Tensor, w_
     dt = weight_dtype(w_dtype)
     if not (a.is_cuda and bq.is_cuda and scales.is_cuda):
         raise ValueError("quantized_matmul needs CUDA tensors (there is no CPU path)")
-    if a.dtype != torch.float16 or scales.dtype != torch.float16:
-        raise TypeError("activations and scales must be float16")
+    act = act_code(a.dtype)
+    if scales.dtype != a.dtype:
+        raise TypeError("activations and scales must have the same dtype (float16 or bfloat16)")
     if a.dim() != 2 or a.stride(1) != 1:
         raise ValueError("a must be a 2-D tensor with unit inner stride")
     M, K = a.shape
@@ -76,7 +86,7 @@ def quantized_matmul(a: torch.Tensor, bq: torch.Tensor, scales: torch.Tensor, w_
         if workspace is None:
             workspace = get_workspace(a.device, workspace_bytes(M, N, K, dt, zero_point, group_size))
         args = (a.data_ptr(), a.stride(0), bq.data_ptr(), scales.data_ptr(), out.data_ptr(), out.stride(0),
-                M, N, K, dt.code, zero_point, group_size, _lib.ACT_F16, workspace.data_ptr(), workspace.numel(),
+                M, N, K, dt.code, zero_point, group_size, act, workspace.data_ptr(), workspace.numel(),
                 _stream_ptr(a.device))
         if plan_override is None:
             st = lib.b200q_gemm(*args)
@@ -97,11 +107,12 @@ def linear_forward(x2: torch.Tensor, bq: torch.Tensor, scales: torch.Tensor, cod
     (``ws_need``), so that a decode step spends its host time in the launch, not in checks."""
     if not x2.is_cuda:
         raise ValueError("QuantizedLinear needs CUDA tensors (there is no CPU path)")
-    if x2.dtype != torch.float16 or x2.stride(1) != 1:
-        raise TypeError("activations must be float16 with unit inner stride")
+    if x2.dtype != scales.dtype or x2.stride(1) != 1:
+        raise TypeError(f"activations must be {scales.dtype} with unit inner stride")
+    act = act_code(x2.dtype)
     lib = _lib.load()
     M = x2.shape[0]
-    out = torch.empty(M, N, dtype=torch.float16, device=x2.device)
+    out = torch.empty(M, N, dtype=x2.dtype, device=x2.device)
     if M == 0:
         return out
     dev = x2.device
@@ -123,7 +134,7 @@ def linear_forward(x2: torch.Tensor, bq: torch.Tensor, scales: torch.Tensor, cod
             ws = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=dev)
             _workspaces[key] = ws
         st = lib.b200q_gemm(x2.data_ptr(), x2.stride(0), bq.data_ptr(), scales.data_ptr(), out.data_ptr(), N, M, N, K,
-                            code, zero_point, group_size, _lib.ACT_F16, ws.data_ptr(), ws.numel(), stream)
+                            code, zero_point, group_size, act, ws.data_ptr(), ws.numel(), stream)
     finally:
         if switch:
             torch.cuda.set_device(prev)
@@ -142,8 +153,9 @@ def linear_forward_host(x_host: torch.Tensor, out_host: torch.Tensor, bq: torch.
     stream of the layer's device; the caller synchronises that stream before reading ``out_host``."""
     if x_host.is_cuda or out_host.is_cuda:
         raise ValueError("forward_host takes host tensors (use forward for device tensors)")
-    if x_host.dtype != torch.float16 or out_host.dtype != torch.float16:
-        raise TypeError("activations and result must be float16")
+    if x_host.dtype != scales.dtype or out_host.dtype != scales.dtype:
+        raise TypeError(f"activations and result must be {scales.dtype}")
+    act = act_code(x_host.dtype)
     if x_host.dim() != 2 or x_host.stride(1) != 1 or x_host.shape[1] != K:
         raise ValueError(f"x_host must be [M, {K}] with unit inner stride")
     M = x_host.shape[0]
@@ -168,11 +180,11 @@ def linear_forward_host(x_host: torch.Tensor, out_host: torch.Tensor, bq: torch.
             _workspaces[key] = ws
         stage = _host_staging.get(key)
         if stage is None or stage[0].numel() < M * K or stage[1].numel() < M * N:
-            stage = (torch.empty(M * K, dtype=torch.float16, device=dev), torch.empty(M * N, dtype=torch.float16, device=dev))
+            stage = (torch.empty(M * K, dtype=torch.int16, device=dev), torch.empty(M * N, dtype=torch.int16, device=dev))
             _host_staging[key] = stage
         st = lib.b200q_gemm_host(x_host.data_ptr(), x_host.stride(0), bq.data_ptr(), scales.data_ptr(),
                                  out_host.data_ptr(), out_host.stride(0), M, N, K, code, zero_point, group_size,
-                                 _lib.ACT_F16, stage[0].data_ptr(), stage[1].data_ptr(), ws.data_ptr(), ws.numel(),
+                                 act, stage[0].data_ptr(), stage[1].data_ptr(), ws.data_ptr(), ws.numel(),
                                  stream)
     if st != 0:
         _lib.check(st)
@@ -180,8 +192,8 @@ def linear_forward_host(x_host: torch.Tensor, out_host: torch.Tensor, bq: torch.
 
 
 def dequantize(bq: torch.Tensor, scales: torch.Tensor, w_dtype, group_size: int, zero_point: int = 0) -> torch.Tensor:
-    """W[K, N] fp16, the weights the GEMM multiplies by (bit-exact with the reference's
-    cast-then-scale)."""
+    """W[K, N] in the dtype of ``scales`` (float16 or bfloat16): the weights the GEMM multiplies by
+    (bit-exact with the reference's cast-then-scale)."""
     lib = _lib.load()
     dt = weight_dtype(w_dtype)
     G, N = scales.shape
@@ -190,16 +202,21 @@ def dequantize(bq: torch.Tensor, scales: torch.Tensor, w_dtype, group_size: int,
         raise ValueError("dequantize needs CUDA tensors (there is no CPU path)")
     if bq.dtype != torch.uint8 or bq.numel() * 8 != K * N * dt.nbits:
         raise ValueError("bq must be a uint8 tensor of K*N*nbits/8 bytes")
-    w = torch.empty(K, N, dtype=torch.float16, device=bq.device)
+    w = torch.empty(K, N, dtype=scales.dtype, device=bq.device)
     with torch.cuda.device(bq.device):
         _lib.check(lib.b200q_dequantize(bq.data_ptr(), scales.contiguous().data_ptr(), w.data_ptr(), N, K, dt.code,
-                                        zero_point, group_size, _stream_ptr(bq.device)))
+                                        zero_point, group_size, act_code(scales.dtype), _stream_ptr(bq.device)))
     return w
 
 
-def device_status(workspace: torch.Tensor) -> list:
+def device_status(workspace: torch.Tensor | None, device=None) -> list:
+    """Status header of a workspace ([0, 0, 0, 0] when no bounded device-side wait gave up); clears
+    it.  ``workspace=None`` reads the library's built-in scratch (b200q_gemm_static_ws) of ``device``."""
     arr = (ctypes.c_int32 * 4)()
-    st = _lib.load().b200q_device_status(workspace.data_ptr(), ctypes.byref(arr), _stream_ptr(workspace.device))
+    dev = workspace.device if workspace is not None else torch.device(device if device is not None else "cuda")
+    with torch.cuda.device(dev):
+        st = _lib.load().b200q_device_status(workspace.data_ptr() if workspace is not None else None,
+                                             ctypes.byref(arr), _stream_ptr(dev))
     if st not in (_lib.ST_OK, _lib.ST_DEVICE_TIMEOUT):
         _lib.check(st)
     return list(arr)

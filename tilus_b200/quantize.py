@@ -46,10 +46,10 @@ def encode_float(x: torch.Tensor, dt: WeightDType) -> torch.Tensor:
     return (out & ((1 << nbits) - 1)).to(torch.uint8)
 
 
-def quantize_weight(weight: torch.Tensor, w_dtype, group_size: int):
-    """weight[out, in] -> (codes uint8[K=in, N=out], scales fp16[K/group, N]).
+def quantize_weight(weight: torch.Tensor, w_dtype, group_size: int, x_dtype: torch.dtype = torch.float16):
+    """weight[out, in] -> (codes uint8[K=in, N=out], scales x_dtype[K/group, N]).
 
-    Symmetric: scales = max(absmax / max_value, 1e-6) per (group, column), cast to fp16;
+    Symmetric: scales = max(absmax / max_value, 1e-6) per (group, column), cast to the activation dtype;
     q = clamp(w / scales, min, max); integers round half to even (torch.round), floats
     are rounded by the encode.
     """
@@ -58,7 +58,7 @@ def quantize_weight(weight: torch.Tensor, w_dtype, group_size: int):
     w = weight.float().transpose(1, 0).contiguous().view(in_f // group_size, group_size, out_f)
     absmax = w.abs().max(dim=1, keepdim=True)[0]
     scales = torch.max(absmax / float(dt.max_value), torch.tensor(1e-6, dtype=w.dtype, device=w.device))
-    scales = scales.to(torch.float16)
+    scales = scales.to(x_dtype)
     q = torch.clamp(w / scales, float(dt.min_value), float(dt.max_value))
     if dt.kind == KIND_FLOAT:
         codes = encode_float(q, dt)
@@ -67,24 +67,26 @@ def quantize_weight(weight: torch.Tensor, w_dtype, group_size: int):
     return codes.view(in_f, out_f), scales.view(in_f // group_size, out_f)
 
 
-def quantize_and_pack(weight: torch.Tensor, w_dtype, group_size: int):
-    """weight[out, in] on a CUDA device (fp16 or fp32) -> (packed b200 bytes uint8[K*N*b/8],
-    scales fp16[K/group, N]) in one library call (two kernels): the same arithmetic as
+def quantize_and_pack(weight: torch.Tensor, w_dtype, group_size: int, x_dtype: torch.dtype = torch.float16):
+    """weight[out, in] on a CUDA device (fp16, bf16 or fp32) -> (packed b200 bytes uint8[K*N*b/8],
+    scales x_dtype[K/group, N]) in one library call (two kernels): the same arithmetic as
     quantize_weight followed by packing.interleave, bit for bit."""
     from . import _lib
+    from .ops import act_code
 
     dt = weight_dtype(w_dtype)
     if not weight.is_cuda:
         raise ValueError("quantize_and_pack needs a CUDA tensor (use quantize_weight + packing.interleave on the host)")
-    if weight.dtype not in (torch.float16, torch.float32):
+    if weight.dtype not in (torch.float16, torch.float32, torch.bfloat16):
         weight = weight.float()
+    wcode = {torch.float16: 0, torch.float32: 1, torch.bfloat16: 2}[weight.dtype]
     weight = weight.contiguous()
     out_f, in_f = weight.shape
     bq = torch.empty(in_f * out_f * dt.nbits // 8, dtype=torch.uint8, device=weight.device)
-    scales = torch.empty(in_f // group_size, out_f, dtype=torch.float16, device=weight.device)
+    scales = torch.empty(in_f // group_size, out_f, dtype=x_dtype, device=weight.device)
     with torch.cuda.device(weight.device):
-        st = _lib.load().b200q_quantize(weight.data_ptr(), 1 if weight.dtype == torch.float32 else 0, in_f,
+        st = _lib.load().b200q_quantize(weight.data_ptr(), wcode, in_f,
                                         bq.data_ptr(), scales.data_ptr(), out_f, in_f, dt.code, group_size,
-                                        torch.cuda.current_stream(weight.device).cuda_stream)
+                                        act_code(x_dtype), torch.cuda.current_stream(weight.device).cuda_stream)
     _lib.check(st)
     return bq, scales

@@ -130,7 +130,9 @@ class PeerGather:
         self.world, self.rank, self.ptrs = world, rank, list(ptrs)
         self.max_rows, self.max_cols = max_rows, max_cols
         self.device = torch.device(device)
-        self._owned = None
+        self._owned = None     # this rank's region, if allocated by create()
+        self._opened = []      # peers' regions mapped by create()
+        self.dtype = torch.float16  # dtype of the latest call's output rows
 
     @staticmethod
     def region_bytes(max_rows: int, max_cols: int) -> int:
@@ -162,7 +164,24 @@ class PeerGather:
                     ptrs.append(peer.value)
         ctx = cls(world, rank, ptrs, max_rows, max_cols, device)
         ctx._owned = mine.value
+        ctx._opened = [p for g, p in enumerate(ptrs) if g != rank]
+        ctx._group = group
         return ctx
+
+    def close(self):
+        """Unmaps the peers' regions and frees this rank's own (only what create() made).  Every rank
+        must have finished its fused calls: a barrier precedes the release when a process group is up."""
+        if self._owned is None:
+            return
+        lib = _lib.load()
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize(self.device)
+            if dist.is_initialized() and self.world > 1:
+                dist.barrier(group=getattr(self, "_group", None))
+            for p in self._opened:
+                _lib.check(lib.b200q_peer_close(ctypes.c_void_p(p)))
+            _lib.check(lib.b200q_peer_free(ctypes.c_void_p(self._owned)))
+        self._opened, self._owned = [], None
 
     def _view(self, byte_off: int, nbytes: int) -> torch.Tensor:
         return torch.as_tensor(_RawCudaBuffer(self.ptrs[self.rank] + byte_off, nbytes), device=self.device)
@@ -180,8 +199,8 @@ class PeerGather:
                 raise ValueError(f"expected {K} input features, got {x.width}")
             g.a_prev_offset = x.col_start
         else:
-            if x.dtype != torch.float16 or x.stride(1) != 1 or x.shape[1] != K:
-                raise TypeError(f"activations must be float16 [M, {K}] with unit inner stride")
+            if x.dtype != local.scales.dtype or x.stride(1) != 1 or x.shape[1] != K:
+                raise TypeError(f"activations must be {local.scales.dtype} [M, {K}] with unit inner stride")
             M, lda, a_ptr = x.shape[0], x.stride(0), x.data_ptr()
             g.a_prev_offset = -1
         if M > self.max_rows or N_full > self.max_cols or M > 16:
@@ -197,9 +216,11 @@ class PeerGather:
         with torch.cuda.device(self.device):
             ws = ops.get_workspace(self.device, ops.workspace_bytes(M, N_loc, K, dt, zp, grp))
             st = lib.b200q_gemm_gather(a_ptr, lda, local.quantized_weight.data_ptr(), local.scales.data_ptr(), M,
-                                       N_loc, K, dt.code, zp, grp, _lib.ACT_F16, ws.data_ptr(), ws.numel(),
+                                       N_loc, K, dt.code, zp, grp, ops.act_code(local.scales.dtype), ws.data_ptr(),
+                                       ws.numel(),
                                        torch.cuda.current_stream(self.device).cuda_stream, ctypes.byref(g))
         _lib.check(st)
+        self.dtype = local.scales.dtype
         return GatheredRow(M, N_full, 0, N_full)
 
     def calls_completed(self) -> int:
@@ -207,10 +228,28 @@ class PeerGather:
         torch.cuda.current_stream(self.device).synchronize()
         return int(self._view(self.EPOCH_OFF, 4).view(torch.int32).item())
 
+    def wait_all_ranks(self, timeout_s: float = 2.0) -> int:
+        """Waits until every rank's columns of this rank's latest call have landed here: this rank's
+        own stream is synchronised, then its flag words - one per source rank, raised over NVLink by
+        that rank's kernel - are polled until all have reached the call counter (bounded)."""
+        import time
+
+        epoch = self.calls_completed()
+        flags = self._view(self.FLAGS_OFF, 4 * self.world).view(torch.int32)
+        t0 = time.perf_counter()
+        while True:
+            seen = flags.cpu()
+            if bool(((seen - epoch) >= 0).all()):
+                return epoch
+            if time.perf_counter() - t0 > timeout_s:
+                raise _lib.B200QError(_lib.ST_DEVICE_TIMEOUT, f"fused gather: flags {seen.tolist()} never reached call {epoch}")
+            time.sleep(0.0005)
+
     def fetch(self, row: GatheredRow) -> torch.Tensor:
-        """The latest call's gathered output (or the column range `row` of it) as a new tensor."""
-        parity = self.calls_completed() & 1
+        """The latest call's gathered output (or the column range `row` of it) as a new tensor, once
+        every rank's columns are in place."""
+        parity = self.wait_all_ranks() & 1
         nbytes = self.max_rows * self.max_cols * 2
-        buf = self._view(self.ROWS_OFF + parity * nbytes, nbytes).view(torch.float16)
+        buf = self._view(self.ROWS_OFF + parity * nbytes, nbytes).view(self.dtype)
         full = buf[: row.rows * row.row_stride].view(row.rows, row.row_stride)
         return full[:, row.col_start : row.col_start + row.width].clone()
