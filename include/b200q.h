@@ -198,6 +198,39 @@ int b200q_dequantize(const void* bq, const void* scales, void* w, int N, int K, 
 int b200q_quantize(const void* weight, int weight_dtype, int ldw, void* bq, void* scales, int N, int K, int wtype,
                    int group, int act_dtype, void* stream);
 
+/* ---- the step behind the gate_up projection: SwiGLU and the per-token FP8 cast -----------------------
+ * Per token and group of `group` channels (a multiple of 128, at most 512): scale = absmax / 448
+ * (1 if the group is all zero), out = e4m3(value * (448 / absmax)) rounded to nearest even and
+ * saturated, out_sf = scale (fp32 [tokens, hidden / group]).  x is fp16 or bf16 (act_dtype), row
+ * stride ldx elements; out is e4m3 bytes, row stride ldo.
+ *
+ * b200q_per_token_cast: value = x[tokens, hidden].  Replaces the reference's PerTokenCast script
+ * (examples/quantization/per_token_cast.py:22-97).
+ *
+ * b200q_swiglu_per_token_cast: x is [tokens, 2 * hidden]; value = silu(x[:, :hidden]) * x[:, hidden:]
+ * in fp32 with silu(l) = l / (exp(-l) + 1); with use_clamp l is clamped from above and r on both
+ * sides to clamp_value; a row whose pos_to_token_topk entry p is >= 0 is multiplied by
+ * topk_weights[p]; a row whose pos_to_expert entry is negative is skipped (nothing is written for
+ * it).  Each of the three index arrays may be NULL (no weights / no skipping).  Replaces
+ * SwiGLUForwardAndPerTokenCast (examples/quantization/swiglu_forward_and_per_token_cast.py:28-166).
+ *
+ * b200q_gemm_swiglu_cast: the gate_up projection followed by the SwiGLU cast in one call:
+ * gate_up[M, N] = A x dequant(Bq) as b200q_gemm (N = 2 * hidden, gate columns first), then the
+ * cast kernel - launched with programmatic stream serialization, so that it is resident and
+ * waiting when the GEMM retires - reads gate_up and writes out / out_sf.  The two kernels are
+ * not merged: the decode kernel spreads one token's 128-channel group over several CTAs and the
+ * tcgen05 kernels keep a channel's gate and up columns in different warps, so the group maximum
+ * is taken in a kernel of its own. */
+int b200q_per_token_cast(const void* x, int ldx, void* out, int ldo, float* out_sf, int tokens, int hidden, int group,
+                         int act_dtype, void* stream);
+int b200q_swiglu_per_token_cast(const void* x, int ldx, void* out, int ldo, float* out_sf, int tokens, int hidden,
+                                int group, int act_dtype, const int32_t* pos_to_token_topk, const float* topk_weights,
+                                const int32_t* pos_to_expert, int use_clamp, float clamp_value, void* stream);
+int b200q_gemm_swiglu_cast(const void* a, int lda, const void* bq, const void* scales, void* gate_up, int ldg,
+                           void* out, int ldo, float* out_sf, int M, int N, int K, int wtype, int zero_point, int group,
+                           int act_dtype, int cast_group, int use_clamp, float clamp_value, void* workspace,
+                           size_t workspace_bytes, void* stream);
+
 /* Reads the device status header of a workspace (synchronises `stream`): status[0] is 0 or
  * B200Q_ERR_DEVICE_TIMEOUT, status[1..3] say which wait gave up (1: 2 = tcgen05 prefill pipeline,
  * 3 = decode kernel's weight ring, 5 = wait for a peer's columns, 6 = tcgen05 small-batch pipeline;

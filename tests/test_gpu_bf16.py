@@ -75,7 +75,7 @@ def test_bf16_large_activations_do_not_overflow_the_decode_path():
     dev = torch.device("cuda:0")
     N, K, g, dt = 64, 512, 128, D.int4b
     prob = synth.make_problem(40, N, K, dt, g, seed=3)
-    a = (prob["a"] * 1.0e5).to(torch.bfloat16)  # |a| up to ~4e5, beyond fp16
+    a = (prob["a"].float() * 1.0e5).to(torch.bfloat16)  # |a| up to ~4e5, beyond fp16
     scales = prob["scales"].to(torch.bfloat16)
     bq = packing.interleave(prob["codes"], dt).to(dev)
     c = ops.quantized_matmul(a.to(dev), bq, scales.to(dev), dt, g, 0)

@@ -82,6 +82,10 @@ SYMBOLS = {
     "b200q_peer_close": (_i, [_vp]),
     "b200q_peer_free": (_i, [_vp]),
     "b200q_quantize": (_i, [_vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "b200q_per_token_cast": (_i, [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _vp]),
+    "b200q_swiglu_per_token_cast": (_i, [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _i, ctypes.c_float, _vp]),
+    "b200q_gemm_swiglu_cast": (_i, [_vp, _i, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i,
+                                    ctypes.c_float, _vp, _sz, _vp]),
     "b200q_device_status": (_i, [_vp, ctypes.POINTER(ctypes.c_int32 * 4), _vp]),
 }
 

@@ -45,6 +45,7 @@ def _jobs():
         jobs.append(("umma_kernel.cu", f"umma_part{part}.o", [f"-DB200Q_NPARTS={NPARTS}", f"-DB200Q_PART={part}"]))
     jobs.append(("dequant_kernel.cu", "dequant.o", []))
     jobs.append(("quantize_kernel.cu", "quantize.o", []))
+    jobs.append(("cast_kernel.cu", "cast.o", []))
     jobs.append(("api.cu", "api.o", [f"-DB200Q_NPARTS={NPARTS}"]))
     return jobs
 

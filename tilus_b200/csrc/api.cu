@@ -21,6 +21,7 @@ namespace b200q {
 B200Q_DECL_SPART(0) B200Q_DECL_SPART(1) B200Q_DECL_SPART(2) B200Q_DECL_SPART(3)
 B200Q_DECL_SPART(4) B200Q_DECL_SPART(5) B200Q_DECL_SPART(6) B200Q_DECL_SPART(7)
 cudaError_t dequant_launch(int var, const DequantParams& p, cudaStream_t stream);
+cudaError_t cast_launch(const CastParams& p, int act, bool swiglu, cudaStream_t stream);
 cudaError_t quantize_launch(const void* w, int w_dtype, int ldw, void* bq, void* scales, int N, int K, int group,
                             int kind, int nbits, int ebits, int mbits, float minv, float maxv, int act,
                             cudaStream_t stream);
@@ -148,11 +149,14 @@ static int stream_slot_bytes(int bits) { return stream_gi(bits) * 256 * bits; }
 // 8-row activation tiles per launch: 1 or 2 (the kernel's MT)
 static int stream_mt(int m_pass) { return m_pass <= 8 ? 1 : 2; }
 // CTAs of one launch per SM
-static int stream_per_sm(int m_pass) { return m_pass <= 8 ? 2 : 1; }
+#ifndef B200Q_MT2_PER_SM
+#define B200Q_MT2_PER_SM 1
+#endif
+static int stream_per_sm(int m_pass) { return m_pass <= 8 ? 2 : B200Q_MT2_PER_SM; }
 // most activation rows one launch of the stream kernel takes
 static int stream_rows_per_pass(int M) { (void)M; return 16; }
 static int stream_smem_cap(int m_pass, const DeviceInfo& di) {
-  return m_pass <= 8 ? kStreamSmemCap : di.max_smem;
+  return (m_pass <= 8 || B200Q_MT2_PER_SM == 2) ? kStreamSmemCap : di.max_smem;
 }
 // whole column tiles a CTA owns (their sums live in at most 16 KB of shared memory)
 static int stream_tiles_owned(int m_pass, int NT, int cpc) {
@@ -743,6 +747,55 @@ int b200q_quantize(const void* weight, int weight_dtype, int ldw, void* bq, void
                                     act_dtype, reinterpret_cast<cudaStream_t>(stream));
   if (err != cudaSuccess) { g_last_cuda_error = (int)err; return ST_CUDA; }
   return ST_OK;
+}
+
+static int run_cast(const void* x, int ldx, void* out, int ldo, float* out_sf, int tokens, int hidden, int group,
+                    int act_dtype, bool swiglu, const int32_t* pos_to_token_topk, const float* topk_weights,
+                    const int32_t* pos_to_expert, int use_clamp, float clamp_value, void* stream) {
+  if (!act_ok(act_dtype)) return ST_UNSUPPORTED;
+  if (!x || !out || !out_sf) return ST_INVALID_ARG;
+  if (tokens < 1 || hidden < 1 || group < 1) return ST_INVALID_ARG;
+  if (group % 128 != 0 || group > 512 || hidden % group != 0) return ST_UNSUPPORTED;
+  if (ldx < (swiglu ? 2 * hidden : hidden) || ldo < hidden || (ldx % 8) != 0 || (ldo % 8) != 0) return ST_INVALID_ARG;
+  if ((((uintptr_t)x) & 15) || (((uintptr_t)out) & 7) || (((uintptr_t)out_sf) & 3)) return ST_INVALID_ARG;
+  CastParams p;
+  p.x = reinterpret_cast<const unsigned short*>(x);
+  p.out = reinterpret_cast<unsigned char*>(out);
+  p.out_sf = out_sf;
+  p.T = tokens; p.H = hidden; p.ldx = ldx; p.ldo = ldo; p.group = group;
+  p.pos_to_token_topk = pos_to_token_topk;
+  p.topk_weights = topk_weights;
+  p.pos_to_expert = pos_to_expert;
+  p.clamp = clamp_value;
+  p.use_clamp = use_clamp ? 1 : 0;
+  cudaError_t e = cast_launch(p, act_dtype, swiglu, reinterpret_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) { g_last_cuda_error = (int)e; return ST_CUDA; }
+  return ST_OK;
+}
+
+int b200q_per_token_cast(const void* x, int ldx, void* out, int ldo, float* out_sf, int tokens, int hidden, int group,
+                         int act_dtype, void* stream) {
+  return run_cast(x, ldx, out, ldo, out_sf, tokens, hidden, group, act_dtype, false, nullptr, nullptr, nullptr, 0, 0.f,
+                  stream);
+}
+
+int b200q_swiglu_per_token_cast(const void* x, int ldx, void* out, int ldo, float* out_sf, int tokens, int hidden,
+                                int group, int act_dtype, const int32_t* pos_to_token_topk, const float* topk_weights,
+                                const int32_t* pos_to_expert, int use_clamp, float clamp_value, void* stream) {
+  return run_cast(x, ldx, out, ldo, out_sf, tokens, hidden, group, act_dtype, true, pos_to_token_topk, topk_weights,
+                  pos_to_expert, use_clamp, clamp_value, stream);
+}
+
+int b200q_gemm_swiglu_cast(const void* a, int lda, const void* bq, const void* scales, void* gate_up, int ldg,
+                           void* out, int ldo, float* out_sf, int M, int N, int K, int wtype, int zero_point, int group,
+                           int act_dtype, int cast_group, int use_clamp, float clamp_value, void* workspace,
+                           size_t workspace_bytes, void* stream) {
+  if ((N & 1) != 0) return ST_INVALID_ARG;
+  const int st = b200q_gemm(a, lda, bq, scales, gate_up, ldg, M, N, K, wtype, zero_point, group, act_dtype, workspace,
+                            workspace_bytes, stream);
+  if (st != ST_OK) return st;
+  return run_cast(gate_up, ldg, out, ldo, out_sf, M, N / 2, cast_group, act_dtype, true, nullptr, nullptr, nullptr,
+                  use_clamp, clamp_value, stream);
 }
 
 int b200q_device_status(void* workspace, int32_t status[4], void* stream) {

@@ -34,7 +34,10 @@ constexpr size_t WS_HEADER_BYTES = 256;
 inline size_t ws_counter_bytes(int N) { return (((size_t)(N / BLOCK_N) * 4) + 255) / 256 * 256; }
 
 // ---- stream kernel (up to 16 rows per launch; the default for M <= 8): item-balanced, ring-fed --
-constexpr int STREAM_WARPS = 16;
+#ifndef B200Q_STREAM_WARPS
+#define B200Q_STREAM_WARPS 16
+#endif
+constexpr int STREAM_WARPS = B200Q_STREAM_WARPS;
 constexpr int STREAM_SC_GROUPS = 16;  // groups per warp in the shared-memory scale cache (32 bytes each)
 // 128-row groups per ring item: items of 1..2 KB for every bit width
 constexpr int stream_gi(int bits) { return bits <= 2 ? 4 : bits <= 5 ? 2 : 1; }
@@ -124,6 +127,19 @@ struct DequantParams {
   __half* w;  // [K, N] row-major (16-bit elements of the activation dtype)
   int N, K, group, KB, NT;
   int act;    // 0 fp16, 1 bf16
+};
+
+// ---- per-token FP8 cast kernels ------------------------------------------------------------------
+struct CastParams {
+  const unsigned short* x;   // [T, H] (cast) or [T, 2H] (SwiGLU), row stride ldx elements, fp16 or bf16
+  unsigned char* out;        // e4m3 [T, H], row stride ldo bytes
+  float* out_sf;             // [T, H / group]
+  int T, H, ldx, ldo, group;
+  const int* pos_to_token_topk;  // [T] or null
+  const float* topk_weights;     // flat, or null
+  const int* pos_to_expert;      // [T] or null
+  float clamp;
+  int use_clamp;
 };
 
 // two fp32 values rounded to the activation dtype (ACT 0: fp16, 1: bf16), low half first

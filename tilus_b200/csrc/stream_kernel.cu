@@ -125,6 +125,47 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+#ifndef B200Q_S_CLASS2
+#define B200Q_S_CLASS2 1
+#endif
+#ifndef B200Q_S_FENCE
+#define B200Q_S_FENCE 0
+#endif
+#ifndef B200Q_S_QUAD
+#define B200Q_S_QUAD 1
+#endif
+#ifndef B200Q_MT2_PER_SM
+#define B200Q_MT2_PER_SM 1
+#endif
+
+// The 8 k16 steps of one 128-row group, four pairs of codes at a time: pairs 4*SP .. 4*SP+3 of the
+// lane's two units (columns r and r+8) are turned into operands right before the two MMAs that take
+// them, so that only eight operand registers are live at a time.  d[mt][0] and d[mt][1] are the two
+// accumulation chains of 8-row tile mt.
+template <int VAR, int MT, bool CLASS2, int SP>
+struct GroupSteps {
+  static __device__ __forceinline__ void run(const uint32_t* w0, const uint32_t* w1,
+                                             const unsigned char* const (&a_ptr)[MT], const uint32_t (&kmask)[MT],
+                                             uint32_t koff, float (&d)[MT][2][4]) {
+    constexpr int H = 4 * SP;
+    constexpr int P01 = CLASS2 ? 2 : 1;  // second pair of chain 0's MMA
+    constexpr int P10 = CLASS2 ? 1 : 2;  // first pair of chain 1's MMA
+    const uint32_t x00 = pair_lin<VAR, H>(w0), y00 = pair_lin<VAR, H>(w1);
+    const uint32_t x01 = pair_lin<VAR, H + P01>(w0), y01 = pair_lin<VAR, H + P01>(w1);
+    const uint32_t x10 = pair_lin<VAR, H + P10>(w0), y10 = pair_lin<VAR, H + P10>(w1);
+    const uint32_t x11 = pair_lin<VAR, H + 3>(w0), y11 = pair_lin<VAR, H + 3>(w1);
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+      const uint4 av = *reinterpret_cast<const uint4*>(a_ptr[mt] + (koff & kmask[mt]) + SP * 16);
+      const uint32_t b00 = av.x, b01 = CLASS2 ? av.z : av.y, b10 = CLASS2 ? av.y : av.z, b11 = av.w;
+      mma_m16n8k16(d[mt][0], x00, y00, x01, y01, b00, b01);
+      if constexpr (SP == 0) mma_m16n8k16_init(d[mt][1], x10, y10, x11, y11, b10, b11);
+      else mma_m16n8k16(d[mt][1], x10, y10, x11, y11, b10, b11);
+    }
+    if constexpr (SP < 3) GroupSteps<VAR, MT, CLASS2, SP + 1>::run(w0, w1, a_ptr, kmask, koff, d);
+  }
+};
+
 // Shared-memory layout (byte offsets from the dynamic smem base):
 //   [0, 1024)    mbarriers [warp][stage]   (16 warps x up to 8 stages)
 //   [1024, ...)  rings [warp][stage][ITEM_BYTES] of packed weights
@@ -137,7 +178,7 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
 // and shared memory, which keeps the two 8-row accumulator sets in registers and a K chunk of the
 // 16 activation rows next to the rings.
 template <int VAR, int MT, bool GATHER, int ACT>
-__global__ void __launch_bounds__(STREAM_WARPS * 32, MT == 1 ? 2 : 1) stream_kernel(const StreamParams p) {
+__global__ void __launch_bounds__(STREAM_WARPS * 32, MT == 1 ? 2 : B200Q_MT2_PER_SM) stream_kernel(const StreamParams p) {
   constexpr int B = var_bits(VAR);
   constexpr int MP = 8 * MT;
   constexpr int BIAS = var_bias(VAR);
@@ -153,8 +194,8 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, MT == 1 ? 2 : 1) stream_ker
   // integers have two (T = 0 for even pairs, 4 for odd ones): even and odd pairs go to separate
   // accumulation chains and the odd chain is scaled by 2^-4 once per group.  Every other width has
   // more than two, and its activations are pre-multiplied by 2^-T when they are staged.
-  constexpr bool CLASS2 = !var_is_float(VAR) && B == 4;
-  constexpr bool PRESCALE = !var_is_float(VAR) && B != 4 && B != 8;
+  constexpr bool CLASS2 = B200Q_S_CLASS2 && !var_is_float(VAR) && B == 4;
+  constexpr bool PRESCALE = !var_is_float(VAR) && !CLASS2 && B != 8;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const int NST = p.stages;
   const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem_raw);
@@ -282,12 +323,22 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, MT == 1 ? 2 : 1) stream_ker
   size_t gather_buf = 0;  // element offset of the row buffer this call writes, inside every rank's region
   unsigned epoch = 0;
   if (GATHER) {
-    epoch = *reinterpret_cast<volatile const unsigned*>(p.ga.epoch);
+    // The rank's own flag slot holds the number of its completed fused calls (its last CTA raises it
+    // with the others), so one round of loads brings both the epoch and the peers' progress.
+    __shared__ unsigned s_epoch_word;
+    unsigned* s_epoch = &s_epoch_word;
+    unsigned mine = 0;
+    if (tid < p.ga.G) {
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(mine) : "l"(p.ga.flags + tid) : "memory");
+      if (tid == p.ga.rank) *s_epoch = mine;
+    }
+    __syncthreads();
+    epoch = *s_epoch;
     gather_buf = ((epoch + 1) & 1u) ? p.ga.buf_elems : 0;
     if (p.ga.a_prev_off >= 0)
       a_base = reinterpret_cast<const unsigned short*>(p.ga.out[p.ga.rank]) + ((epoch & 1u) ? p.ga.buf_elems : 0) + p.ga.a_prev_off;
     if (epoch != 0) {
-      if (tid < p.ga.G) {
+      if (tid < p.ga.G && (int)(mine - epoch) < 0) {  // a peer has not finished call `epoch` yet: bounded wait
         uint64_t t0 = 0;
         for (int spin = 0;; ++spin) {
           unsigned v;
@@ -427,14 +478,24 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, MT == 1 ? 2 : 1) stream_ker
           uint32_t w0[B], w1[B];
           ld_unit_words<B>(slot + w_lane + gi * (256 * B), w0);
           ld_unit_words<B>(slot + w_lane + gi * (256 * B) + 128 * B, w1);
+#if !B200Q_S_QUAD
           uint32_t W0[16], W1[16];
           unit_decode_linear<VAR>(w0, W0);
           unit_decode_linear<VAR>(w1, W1);
+#endif
           if (gi == GI - 1) {
-            // every lane has turned its copy of the item's last group into operands (the loads have
-            // returned, their values were used): lane 0 refills the slot
+            // every lane holds its copy of the item's last group in registers (the loads have
+            // returned: a shuffle of their values orders them before the copy that lane 0 issues
+            // into the slot)
+            uint32_t dep = w0[0] ^ w1[B - 1];
+            asm volatile("" : "+r"(dep));
             __syncwarp();
-            if (lane == 0 && issued < n_items) issue_next(bar, ring_s + slot_off);
+            if (lane == 0 && issued < n_items) {
+#if B200Q_S_FENCE
+              asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+#endif
+              issue_next(bar, ring_s + slot_off);
+            }
           }
           const uint32_t koff = (uint32_t)((g0 + gi) * 320);  // bytes: 128 columns + 4 x 8 of padding per group
           // two accumulation chains per 8-row tile; the first starts from the zero-point term of the group
@@ -445,6 +506,9 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, MT == 1 ? 2 : 1) stream_ker
             if constexpr (BIAS != 0) nb = nb4[((g0 + gi) * MT + mt) * 4];
             d[mt][0][0] = nb.x; d[mt][0][1] = nb.y; d[mt][0][2] = nb.z; d[mt][0][3] = nb.w;
           }
+#if B200Q_S_QUAD
+          GroupSteps<VAR, MT, CLASS2, 0>::run(w0, w1, a_ptr, kmask, koff, d);
+#else
           // pairs h = 4*sp .. 4*sp+3 of both units against the same four pairs of activations; with two
           // mantissa positions (CLASS2) the even pairs feed chain 0 and the odd pairs chain 1
           constexpr int P01 = CLASS2 ? 2 : 1;  // second pair of chain 0's MMA
@@ -462,6 +526,7 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, MT == 1 ? 2 : 1) stream_ker
                 mma_m16n8k16(d[mt][1], W0[4 * sp + P10], W1[4 * sp + P10], W0[4 * sp + 3], W1[4 * sp + 3], b10, b11);
             }
           }
+#endif
           constexpr float C1 = CLASS2 ? 0.0625f : 1.0f;  // chain 1 of a 4-bit type holds 2^4 x its products
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt) {
@@ -603,13 +668,16 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, MT == 1 ? 2 : 1) stream_ker
   if (GATHER) {
     __syncthreads();
     if (tid == 0) {
-      __threadfence();  // cumulative over the CTA's stores to the peers (ordered by the barrier above)
-      if (atomicAdd(p.ga.done, 1u) == gridDim.x - 1) {
+      // release at GPU scope what this CTA's threads stored (ordered before by the barrier), acquire
+      // what the CTAs that arrived earlier released
+      unsigned arrived;
+      asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(arrived) : "l"(p.ga.done) : "memory");
+      if (arrived == gridDim.x - 1) {
         atomicExch(p.ga.done, 0u);
-        __threadfence_system();
+        asm volatile("fence.acq_rel.sys;" ::: "memory");  // one system-scope fence, then plain flag stores
         for (int g = 0; g < p.ga.G; ++g)
-          asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.ga.flag_slot[g]), "r"(epoch + 1) : "memory");
-        *p.ga.epoch = epoch + 1;  // read by this rank's next fused launch, after it has waited for this one
+          asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p.ga.flag_slot[g]), "r"(epoch + 1) : "memory");
+        *p.ga.epoch = epoch + 1;  // for the host (PeerGather.calls_completed)
       }
     }
   }

@@ -157,6 +157,33 @@ class QuantizedLinear(nn.Module):
                                        self.w_dtype.code, self.zero_point, self.group_size, self.in_features,
                                        self.out_features, self._ws_need)
 
+    def forward_swiglu_cast(self, x: torch.Tensor, num_per_channels: int = 128, swiglu_clamp_value=None):
+        """For a gate_up projection (out_features = 2 * hidden, gate columns first): this layer's GEMM
+        followed by SwiGLU and the per-token FP8 cast, queued by one library call
+        (b200q_gemm_swiglu_cast).  Returns (out float8_e4m3fn [M, hidden], out_sf float32
+        [M, hidden / num_per_channels], gate_up [M, out_features])."""
+        from . import _lib
+
+        x2 = x if x.dim() == 2 else x.reshape(-1, self.in_features)
+        if not x2.is_cuda or x2.dtype != self.act_torch_dtype or x2.stride(1) != 1:
+            raise ValueError(f"activations must be CUDA {self.act_torch_dtype} with unit inner stride")
+        M, N, K = x2.shape[0], self.out_features, self.in_features
+        H = N // 2
+        dev = x2.device
+        gate_up = torch.empty(M, N, dtype=x2.dtype, device=dev)
+        out = torch.empty(M, H, dtype=torch.float8_e4m3fn, device=dev)
+        sf = torch.empty(M, H // num_per_channels, dtype=torch.float32, device=dev)
+        with torch.cuda.device(dev):
+            ws = ops.get_workspace(dev, ops.workspace_bytes(M, N, K, self.w_dtype, self.zero_point, self.group_size))
+            st = _lib.load().b200q_gemm_swiglu_cast(
+                x2.data_ptr(), x2.stride(0), self.quantized_weight.data_ptr(), self.scales.data_ptr(),
+                gate_up.data_ptr(), N, out.data_ptr(), H, sf.data_ptr(), M, N, K, self.w_dtype.code, self.zero_point,
+                self.group_size, ops.act_code(x2.dtype), num_per_channels, 0 if swiglu_clamp_value is None else 1,
+                0.0 if swiglu_clamp_value is None else float(swiglu_clamp_value), ws.data_ptr(), ws.numel(),
+                torch.cuda.current_stream(dev).cuda_stream)
+        _lib.check(st)
+        return out, sf, gate_up
+
     def extra_repr(self) -> str:
         return (f"in_features={self.in_features}, out_features={self.out_features}, x_dtype={self.x_dtype.name}, "
                 f"w_dtype={self.w_dtype.name}, "

@@ -220,3 +220,56 @@ def device_status(workspace: torch.Tensor | None, device=None) -> list:
     if st not in (_lib.ST_OK, _lib.ST_DEVICE_TIMEOUT):
         _lib.check(st)
     return list(arr)
+
+
+# ---- the step behind the gate_up projection: SwiGLU and the per-token FP8 cast ----------------------
+def per_token_cast(x: torch.Tensor, num_per_channels: int = 128):
+    """x [tokens, hidden] (float16 / bfloat16, CUDA) -> (out float8_e4m3fn [tokens, hidden],
+    out_sf float32 [tokens, hidden / num_per_channels]): the reference's PerTokenCast
+    (examples/quantization/per_token_cast.py:22-97)."""
+    if not x.is_cuda:
+        raise ValueError("per_token_cast needs a CUDA tensor (there is no CPU path)")
+    if x.dim() != 2 or x.stride(1) != 1:
+        raise ValueError("x must be a 2-D tensor with unit inner stride")
+    T, H = x.shape
+    out = torch.empty(T, H, dtype=torch.float8_e4m3fn, device=x.device)
+    sf = torch.empty(T, H // num_per_channels, dtype=torch.float32, device=x.device)
+    if T == 0:
+        return out, sf
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.load().b200q_per_token_cast(x.data_ptr(), x.stride(0), out.data_ptr(), H, sf.data_ptr(), T, H,
+                                                    num_per_channels, act_code(x.dtype), _stream_ptr(x.device)))
+    return out, sf
+
+
+def swiglu_forward_and_per_token_cast(x: torch.Tensor, num_per_channels: int = 128, pos_to_token_topk=None,
+                                      topk_weights=None, pos_to_expert=None, swiglu_clamp_value=None):
+    """x [tokens, 2 * hidden] -> (out float8_e4m3fn [tokens, hidden], out_sf float32 [tokens, hidden / g]):
+    silu(x[:, :hidden]) * x[:, hidden:], optional clamp, routing weight and expert mask, then the
+    per-token cast - the reference's SwiGLUForwardAndPerTokenCast
+    (examples/quantization/swiglu_forward_and_per_token_cast.py:28-166).  Rows whose pos_to_expert
+    entry is negative are left unwritten."""
+    if not x.is_cuda:
+        raise ValueError("swiglu_forward_and_per_token_cast needs a CUDA tensor (there is no CPU path)")
+    if x.dim() != 2 or x.stride(1) != 1 or x.shape[1] % 2:
+        raise ValueError("x must be [tokens, 2 * hidden] with unit inner stride")
+    T, H = x.shape[0], x.shape[1] // 2
+    out = torch.empty(T, H, dtype=torch.float8_e4m3fn, device=x.device)
+    sf = torch.empty(T, H // num_per_channels, dtype=torch.float32, device=x.device)
+    if T == 0:
+        return out, sf
+
+    def ptr(t, dtype):
+        if t is None:
+            return None
+        if not t.is_cuda or t.dtype != dtype or not t.is_contiguous():
+            raise ValueError(f"index / weight tensors must be contiguous CUDA tensors of {dtype}")
+        return t.data_ptr()
+
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.load().b200q_swiglu_per_token_cast(
+            x.data_ptr(), x.stride(0), out.data_ptr(), H, sf.data_ptr(), T, H, num_per_channels, act_code(x.dtype),
+            ptr(pos_to_token_topk, torch.int32), ptr(topk_weights, torch.float32), ptr(pos_to_expert, torch.int32),
+            0 if swiglu_clamp_value is None else 1, 0.0 if swiglu_clamp_value is None else float(swiglu_clamp_value),
+            _stream_ptr(x.device)))
+    return out, sf
