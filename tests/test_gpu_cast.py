@@ -66,15 +66,15 @@ def test_swiglu_forward_and_per_token_cast(tokens, hidden, num_tokens, topk):
     expert = torch.ones(tokens, dtype=torch.int32)
     expert[::17] = -1
     sentinel = 0x55
-    out, sf = ops.swiglu_forward_and_per_token_cast(x.cuda(), 128, pos.cuda(), w.cuda(), expert.cuda(), 6.0)
+    xd, posd, wd, expd = x.cuda(), pos.cuda(), w.cuda(), expert.cuda()
+    out, sf = ops.swiglu_forward_and_per_token_cast(xd, 128, posd, wd, expd, 6.0)
     # run again into pre-filled buffers to see that masked rows are left alone
     out.view(torch.uint8).fill_(sentinel)
     sf.fill_(-1.0)
     from tilus_b200 import _lib
     _lib.check(_lib.load().b200q_swiglu_per_token_cast(
-        x.cuda().data_ptr(), hidden * 2, out.data_ptr(), hidden, sf.data_ptr(), tokens, hidden, 128, _lib.ACT_F16,
-        pos.cuda().data_ptr(), w.cuda().data_ptr(), expert.cuda().data_ptr(), 1, 6.0,
-        torch.cuda.current_stream().cuda_stream))
+        xd.data_ptr(), hidden * 2, out.data_ptr(), hidden, sf.data_ptr(), tokens, hidden, 128, _lib.ACT_F16,
+        posd.data_ptr(), wd.data_ptr(), expd.data_ptr(), 1, 6.0, torch.cuda.current_stream().cuda_stream))
     torch.cuda.synchronize()
     want_codes, want_sf, valid = co.swiglu_forward_and_per_token_cast(x.float().numpy(), pos.numpy(), w.numpy(),
                                                                       expert.numpy(), 6.0, 128)

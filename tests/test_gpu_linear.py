@@ -116,3 +116,23 @@ def test_gpu_quantize_and_pack_bit_exact(dt, group, wdtype):
     np.testing.assert_array_equal(scales.cpu().numpy().view(np.uint16), scales_ref.view(np.uint16))
     want = packing.interleave(torch.from_numpy(codes_ref), dt)
     assert torch.equal(packed.cpu(), want)
+
+
+@pytest.mark.parametrize("k,group", [(640, 64), (1152, 128), (384, 32)])
+def test_load_and_quantize_general_k(k, group):
+    """GPU-side load_and_quantize and forward for in_features that are multiples of 128 only and
+    scale groups below 128: codes, scales and dequantized weights bit-identical to the oracle."""
+    torch.manual_seed(1)
+    n, m, dt = 96, 5, D.int4b
+    layer = QuantizedLinear(x_dtype=float16, w_dtype=dt, group_size=group, in_features=k, out_features=n).cuda()
+    a = ((torch.rand(m, k) - 0.5) / np.sqrt(k)).to(torch.float16)
+    b = ((torch.rand(k, n) - 0.5) / np.sqrt(k)).to(torch.float16)
+    layer.load_and_quantize(b.T.contiguous())
+    codes, scales = qo.quantize_weight(b.T.contiguous().numpy(), dt, group)
+    np.testing.assert_array_equal(layer.codes().cpu().numpy(), codes)
+    np.testing.assert_array_equal(layer.scales.data.cpu().numpy().view(np.uint16), scales.view(np.uint16))
+    w = qo.dequantize(codes, scales, dt, group)
+    np.testing.assert_array_equal(layer.dequantized_weight().cpu().numpy().view(np.uint16), w.view(np.uint16))
+    got = layer(a.cuda()).cpu().numpy().astype(np.float64)
+    ref = qo.gemm_fp16(a.numpy(), w).astype(np.float64)
+    assert np.abs(got - ref).max() / np.abs(ref).max() <= 1e-2

@@ -207,6 +207,26 @@ def test_stream_kernel_two_row_tiles_default_plan(M, N, K):
     assert _rel_err(c, ref) <= REL_TOL
 
 
+@pytest.mark.parametrize("M", [1, 16, 40, 200, 300])
+@pytest.mark.parametrize("K,group", [(640, 128), (1152, 64), (1024, 32), (1152, 384), (2048, 64), (896, 896)])
+@pytest.mark.parametrize("dt,zp", [(D.int4b, 0), (D.float6_e3m2, 0), (D.uint3b, 4)], ids=lambda x: getattr(x, "name", str(x)))
+def test_gemm_general_k_and_small_groups(M, K, group, dt, zp):
+    """The reference operator takes K % 16 == 0 and scale groups that are multiples of 32
+    (examples/quantization/matmul_a16wx.py:66-71, :207).  Here: K any multiple of 128, groups of 32, 64
+    or any multiple of 128.  What the decode kernel does not take (K not in whole 512-row blocks,
+    groups below 128) runs on the tensor-core kernels for every M."""
+    N = 272
+    prob = synth.make_problem(M, N, K, dt, group, seed=K + group + M)
+    prob["zero_point"] = zp
+    c, bq, sc = _run(prob)
+    want_w = qo.dequantize(prob["codes"].numpy(), prob["scales"].numpy(), dt, group, zp)
+    if M == 1:  # the weights the kernels multiply by, bit for bit (general K layout, small groups)
+        w = ops.dequantize(bq, sc, dt, group, zp).cpu().numpy()
+        np.testing.assert_array_equal(w.view(np.uint16), want_w.view(np.uint16))
+    ref = qo.gemm_fp16(prob["a"].numpy(), want_w)
+    assert _rel_err(c, ref) <= REL_TOL
+
+
 def test_config0_m16_k4096_n4096_u4():
     prob = synth.make_problem(16, 4096, 4096, D.uint4b, 128, seed=0)
     c, bq, sc = _run(prob)

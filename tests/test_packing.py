@@ -83,7 +83,7 @@ def test_b200_column_shards_are_contiguous():
 
 def test_shape_check():
     with pytest.raises(ValueError):
-        P.interleave(torch.zeros(256, 16, dtype=torch.uint8), D.uint4b)
+        P.interleave(torch.zeros(192, 16, dtype=torch.uint8), D.uint4b)  # K not a multiple of 128
     with pytest.raises(ValueError):
         P.interleave(torch.zeros(512, 24, dtype=torch.uint8), D.uint4b)
 

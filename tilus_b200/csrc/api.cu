@@ -149,14 +149,11 @@ static int stream_slot_bytes(int bits) { return stream_gi(bits) * 256 * bits; }
 // 8-row activation tiles per launch: 1 or 2 (the kernel's MT)
 static int stream_mt(int m_pass) { return m_pass <= 8 ? 1 : 2; }
 // CTAs of one launch per SM
-#ifndef B200Q_MT2_PER_SM
-#define B200Q_MT2_PER_SM 1
-#endif
-static int stream_per_sm(int m_pass) { return m_pass <= 8 ? 2 : B200Q_MT2_PER_SM; }
+static int stream_per_sm(int m_pass) { return m_pass <= 8 ? 2 : 1; }
 // most activation rows one launch of the stream kernel takes
 static int stream_rows_per_pass(int M) { (void)M; return 16; }
 static int stream_smem_cap(int m_pass, const DeviceInfo& di) {
-  return (m_pass <= 8 || B200Q_MT2_PER_SM == 2) ? kStreamSmemCap : di.max_smem;
+  return m_pass <= 8 ? kStreamSmemCap : di.max_smem;
 }
 // whole column tiles a CTA owns (their sums live in at most 16 KB of shared memory)
 static int stream_tiles_owned(int m_pass, int NT, int cpc) {
@@ -167,14 +164,16 @@ static int stream_tiles_owned(int m_pass, int NT, int cpc) {
 static int stream_fixed_smem(int m_pass, int kc, int t_own) {
   const int mt = stream_mt(m_pass);
   // barriers, scale caches, own-tile sums, activation chunk (+ 64 zero bytes), group sums as accumulator quads
-  return 1024 + STREAM_WARPS * STREAM_SC_GROUPS * 32 + t_own * 16 * 8 * mt * 4 + m_pass * stream_pitch(kc) * 2 + 64 +
+  return stream_header_bytes(mt) + stream_warps(mt) * STREAM_SC_GROUPS * 32 + t_own * 16 * 8 * mt * 4 +
+         m_pass * stream_pitch(kc) * 2 + 64 +
          (kc / 128) * 16 * mt * 4;
 }
 static int stream_smem(int m_pass, int kc, int bits, int stages, int t_own) {
-  return stream_fixed_smem(m_pass, kc, t_own) + STREAM_WARPS * stages * stream_slot_bytes(bits);
+  return stream_fixed_smem(m_pass, kc, t_own) + stream_warps(stream_mt(m_pass)) * stages * stream_slot_bytes(bits);
 }
 static int stream_stages_for(int m_pass, int kc, int bits, int t_own, const DeviceInfo& di) {
-  int st = (stream_smem_cap(m_pass, di) - stream_fixed_smem(m_pass, kc, t_own)) / (STREAM_WARPS * stream_slot_bytes(bits));
+  int st = (stream_smem_cap(m_pass, di) - stream_fixed_smem(m_pass, kc, t_own)) /
+           (stream_warps(stream_mt(m_pass)) * stream_slot_bytes(bits));
   return st > 8 ? 8 : st;
 }
 // CTAs per k chunk.  First choice (up to 8 rows): two CTAs per SM (32 warps hide the latency of the
@@ -211,7 +210,7 @@ static int plan_stream(int m_pass, int N, int K, int bits, const DeviceInfo& di,
   pl->splits = best_s;
   pl->cluster = 1;
   pl->ctas_per_split = best_c;
-  pl->warps = STREAM_WARPS;
+  pl->warps = stream_warps(stream_mt(m_pass));
   pl->stages = best_st;
   pl->smem_bytes = stream_smem(m_pass, (KB / best_s) * 512, bits, best_st, stream_tiles_owned(m_pass, NT, best_c));
   pl->tile_m = 0;
@@ -219,22 +218,27 @@ static int plan_stream(int m_pass, int N, int K, int bits, const DeviceInfo& di,
   return ST_OK;
 }
 
-// group_mult: 128 for the GEMM kernels (one scale per 128-row group and column), 32 for
-// the dequantize kernel
-static int check_problem(int M, int N, int K, int wtype, int zero_point, int group, int group_mult, int* var) {
+// Shapes every kernel takes: K a multiple of 128 (the packed layout's row group), N a multiple of 16,
+// one scale per `group` rows with group = 32, 64 or a multiple of 128 that divides K.  The reference
+// asks for K % 16 == 0, N % 16 == 0 and group % block_k == 0 with block_k = 32 as shipped
+// (examples/quantization/matmul_a16wx.py:66-71, :207).  for_gemm = false: the dequantize kernel, which
+// takes any multiple of 32.
+static int check_problem(int M, int N, int K, int wtype, int zero_point, int group, bool for_gemm, int* var) {
   if (M < 1 || N < 1 || K < 1 || group < 1) return ST_INVALID_ARG;
   *var = variant_of(wtype, zero_point);
   if (*var < 0) return ST_UNSUPPORTED;
-  if (K % BLOCK_K != 0 || N % BLOCK_N != 0) return ST_UNSUPPORTED;
-  if (group % group_mult != 0 || K % group != 0) return ST_UNSUPPORTED;
-  // the GEMM kernels index scale rows with a shift: group = 128 * 2^s, or one group per column
-  if (group_mult == 128 && group != K && ((group / 128) & (group / 128 - 1)) != 0) return ST_UNSUPPORTED;
+  if (K % 128 != 0 || N % BLOCK_N != 0) return ST_UNSUPPORTED;
+  if (group % 32 != 0 || K % group != 0) return ST_UNSUPPORTED;
+  if (for_gemm && group != 32 && group != 64 && group % 128 != 0) return ST_UNSUPPORTED;
   return ST_OK;
 }
-static int gshift_of(int group, int K) {
-  if (group == K) return -1;
+// the decode kernel works in whole 512-row blocks and applies one scale per 128-row group
+static bool stream_takes(int K, int group) { return K % BLOCK_K == 0 && group % 128 == 0; }
+static int gshift_of(int group) {  // log2(group / 128) when that is a power of two, else -1
+  const int d = group / 128;
+  if (d < 1 || (d & (d - 1)) != 0) return -1;
   int s = 0;
-  while ((128 << s) < group) ++s;
+  while ((1 << s) < d) ++s;
   return s;
 }
 
@@ -283,13 +287,13 @@ static void plan_wide(int M, int N, int K, int bits, const DeviceInfo& di, b200q
   pl->pdl = 0;
 }
 
-static int make_plan(int M, int N, int K, int var, b200q_plan_t* pl) {
+static int make_plan(int M, int N, int K, int var, int group, b200q_plan_t* pl) {
   const DeviceInfo di = device_info();
   std::memset(pl, 0, sizeof(*pl));
   const int bits = var_bits(var);
   // up to 16 rows: the mma.sync stream kernel (one weight decode per 16 x 128 tile feeds one or two
   // 8-row activation tiles); above, the tcgen05 kernels
-  if (M <= kStreamMaxRows) {
+  if (M <= kStreamMaxRows && stream_takes(K, group)) {
     if (plan_stream(M, N, K, bits, di, pl) == ST_OK) {
       pl->passes = 1;
       pl->workspace_bytes = stream_workspace_bytes(N);  // fp32 scratch [N][8 or 16]
@@ -346,8 +350,9 @@ static int run_umma(const void* a, int lda, const void* bq, const void* scales, 
   p.status = reinterpret_cast<int*>(workspace);
   p.counters = reinterpret_cast<int*>(reinterpret_cast<char*>(workspace) + WS_HEADER_BYTES);
   p.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + WS_HEADER_BYTES + ws_counter_bytes(N));
-  p.M = M; p.N = N; p.K = K; p.KB = K / BLOCK_K; p.ldc = ldc;
-  p.gshift = gshift_of(group, K);
+  p.M = M; p.N = N; p.K = K; p.G = K / 128; p.ldc = ldc;
+  p.group = group;
+  p.rpg = group < 128 ? 128 / group : 1;
   p.tm = tm; p.m_tiles = m_tiles; p.n_tiles = n_tiles;
   p.splits = pl.splits; p.kblocks_per_split = kblocks / pl.splits;
   p.a_stages = a_stages;
@@ -390,8 +395,9 @@ static int run_wide(const void* a, int lda, const void* bq, const void* scales, 
   p.status = reinterpret_cast<int*>(workspace);
   p.counters = reinterpret_cast<int*>(reinterpret_cast<char*>(workspace) + WS_HEADER_BYTES);
   p.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + WS_HEADER_BYTES + ws_counter_bytes(N));
-  p.M = M; p.N = N; p.K = K; p.KB = K / BLOCK_K; p.ldc = ldc;
-  p.gshift = gshift_of(group, K);
+  p.M = M; p.N = N; p.K = K; p.G = K / 128; p.ldc = ldc;
+  p.group = group;
+  p.rpg = group < 128 ? 128 / group : 1;
   p.m_tiles = m_tiles; p.n_tiles = n_tiles;
   p.splits = pl.splits; p.kblocks_per_split = 2 * G / pl.splits;
   p.a_rows = a_rows;
@@ -411,6 +417,7 @@ static int run_stream(const void* a, int lda, const void* bq, const void* scales
                       const b200q_plan_t& pl, const b200q_gather_t* gather = nullptr) {
   const int bits = var_bits(var);
   const int KB = K / BLOCK_K;
+  if (!stream_takes(K, group)) return ST_UNSUPPORTED;
   if (pl.splits < 1 || KB % pl.splits != 0 || pl.ctas_per_split < 1) return ST_INVALID_ARG;
   if (pl.stages < 1 || pl.stages > 8) return ST_INVALID_ARG;
   if (((uintptr_t)scales) & 15) return ST_INVALID_ARG;  // scale rows are fetched with 32-byte bulk copies
@@ -423,7 +430,8 @@ static int run_stream(const void* a, int lda, const void* bq, const void* scales
   p.counters = reinterpret_cast<int*>(reinterpret_cast<char*>(workspace) + WS_HEADER_BYTES);
   p.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + WS_HEADER_BYTES + ws_counter_bytes(N));
   p.N = N; p.K = K; p.lda = lda; p.ldc = ldc; p.KB = KB; p.NT = N / BLOCK_N;
-  p.gshift = gshift_of(group, K);
+  p.gshift = gshift_of(group);
+  p.gdiv = group / 128;
   p.S = pl.splits; p.KBc = KB / pl.splits; p.CPC = pl.ctas_per_split;
   if (p.S * p.CPC > 4 * device_info().sm_count) return ST_INVALID_ARG;
   p.pitch = stream_pitch(p.KBc * 512);
@@ -518,9 +526,9 @@ int b200q_last_cuda_error(void) { return g_last_cuda_error; }
 int b200q_plan(int M, int N, int K, int wtype, int zero_point, int group, b200q_plan_t* plan) {
   if (!plan) return ST_INVALID_ARG;
   int var;
-  int st = check_problem(M, N, K, wtype, zero_point, group, 128, &var);
+  int st = check_problem(M, N, K, wtype, zero_point, group, true, &var);
   if (st != ST_OK) return st;
-  return make_plan(M, N, K, var, plan);
+  return make_plan(M, N, K, var, group, plan);
 }
 
 size_t b200q_workspace_bytes(int M, int N, int K, int wtype, int zero_point, int group) {
@@ -535,7 +543,7 @@ int b200q_gemm_planned(const void* a, int lda, const void* bq, const void* scale
   if (!plan) return ST_INVALID_ARG;
   if (!act_ok(act_dtype)) return ST_UNSUPPORTED;
   int var;
-  int st = check_problem(M, N, K, wtype, zero_point, group, 128, &var);
+  int st = check_problem(M, N, K, wtype, zero_point, group, true, &var);
   if (st != ST_OK) return st;
   return run_gemm(a, lda, bq, scales, c, ldc, M, N, K, var, group, act_dtype, workspace, workspace_bytes,
                   reinterpret_cast<cudaStream_t>(stream), *plan);
@@ -552,10 +560,10 @@ int b200q_gemm_gather(const void* a, int lda, const void* bq, const void* scales
   if (((uintptr_t)bq) & 15) return ST_INVALID_ARG;
   if (lda < K || (lda % 8) != 0) return ST_INVALID_ARG;
   int var;
-  int st = check_problem(M, N, K, wtype, zero_point, group, 128, &var);
+  int st = check_problem(M, N, K, wtype, zero_point, group, true, &var);
   if (st != ST_OK) return st;
   b200q_plan_t pl;
-  st = make_plan(M, N, K, var, &pl);  // the fused gather lives in the stream kernel only
+  st = make_plan(M, N, K, var, group, &pl);  // the fused gather lives in the stream kernel only
   if (st != ST_OK) return st;
   if (pl.kernel != 2) return ST_UNSUPPORTED;
   return run_stream(a, lda, bq, scales, nullptr, gather->ldc, M, N, K, var, group, act_dtype, workspace,
@@ -604,10 +612,10 @@ int b200q_gemm(const void* a, int lda, const void* bq, const void* scales, void*
                void* stream) {
   if (!act_ok(act_dtype)) return ST_UNSUPPORTED;
   int var;
-  int st = check_problem(M, N, K, wtype, zero_point, group, 128, &var);
+  int st = check_problem(M, N, K, wtype, zero_point, group, true, &var);
   if (st != ST_OK) return st;
   b200q_plan_t pl;
-  st = make_plan(M, N, K, var, &pl);
+  st = make_plan(M, N, K, var, group, &pl);
   if (st != ST_OK) return st;
   return run_gemm(a, lda, bq, scales, c, ldc, M, N, K, var, group, act_dtype, workspace, workspace_bytes,
                   reinterpret_cast<cudaStream_t>(stream), pl);
@@ -692,10 +700,10 @@ int b200q_gemm_static_ws(const void* a, int lda, const void* bq, const void* sca
                          int K, int wtype, int zero_point, int group, int act_dtype, void* stream) {
   if (!act_ok(act_dtype)) return ST_UNSUPPORTED;
   int var;
-  int st = check_problem(M, N, K, wtype, zero_point, group, 128, &var);
+  int st = check_problem(M, N, K, wtype, zero_point, group, true, &var);
   if (st != ST_OK) return st;
   b200q_plan_t pl;
-  st = make_plan(M, N, K, var, &pl);
+  st = make_plan(M, N, K, var, group, &pl);
   if (st != ST_OK) return st;
   if (pl.workspace_bytes > (uint64_t)B200Q_STATIC_WS_BYTES) return ST_WORKSPACE;  // beyond the built-in scratch
   void* ws = nullptr;
@@ -709,7 +717,7 @@ int b200q_dequantize(const void* bq, const void* scales, void* w, int N, int K, 
                      int act_dtype, void* stream) {
   if (!act_ok(act_dtype)) return ST_UNSUPPORTED;
   int var;
-  int st = check_problem(1, N, K, wtype, zero_point, group, 32, &var);
+  int st = check_problem(1, N, K, wtype, zero_point, group, false, &var);
   if (st != ST_OK) return st;
   if (!bq || !scales || !w) return ST_INVALID_ARG;
   if (((uintptr_t)bq | (uintptr_t)w) & 15) return ST_INVALID_ARG;
@@ -717,7 +725,7 @@ int b200q_dequantize(const void* bq, const void* scales, void* w, int N, int K, 
   p.bq = reinterpret_cast<const uint4*>(bq);
   p.scales = reinterpret_cast<const __half*>(scales);
   p.w = reinterpret_cast<__half*>(w);
-  p.N = N; p.K = K; p.group = group; p.KB = K / BLOCK_K; p.NT = N / BLOCK_N;
+  p.N = N; p.K = K; p.group = group; p.G = K / 128; p.NT = N / BLOCK_N;
   p.act = act_dtype;
   cudaError_t e = dequant_launch(var, p, reinterpret_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) { g_last_cuda_error = (int)e; return ST_CUDA; }
@@ -733,7 +741,7 @@ int b200q_quantize(const void* weight, int weight_dtype, int ldw, void* bq, void
   const int kind = (wtype >> 16) & 0xff, nbits = (wtype >> 8) & 0xff, e = (wtype >> 4) & 0xf, m = wtype & 0xf;
   if (kind > 2 || nbits < 1 || nbits > 8) return ST_UNSUPPORTED;
   if (kind == 2 && (nbits != 1 + e + m || e < 1 || m < 1)) return ST_UNSUPPORTED;
-  if (K % BLOCK_K != 0 || N % BLOCK_N != 0 || group % 32 != 0 || K % group != 0) return ST_UNSUPPORTED;
+  if (K % 128 != 0 || N % BLOCK_N != 0 || group % 32 != 0 || K % group != 0) return ST_UNSUPPORTED;
   if (((uintptr_t)bq & 15) || ((uintptr_t)scales & 1) || ((uintptr_t)weight & 3)) return ST_INVALID_ARG;
   float minv, maxv;
   if (kind == 0) { minv = 0.f; maxv = (float)((1 << nbits) - 1); }

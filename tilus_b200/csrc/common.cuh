@@ -34,10 +34,16 @@ constexpr size_t WS_HEADER_BYTES = 256;
 inline size_t ws_counter_bytes(int N) { return (((size_t)(N / BLOCK_N) * 4) + 255) / 256 * 256; }
 
 // ---- stream kernel (up to 16 rows per launch; the default for M <= 8): item-balanced, ring-fed --
-#ifndef B200Q_STREAM_WARPS
-#define B200Q_STREAM_WARPS 16
+// warps per CTA: up to 8 rows (MT = 1) two CTAs share an SM; 9..16 rows (MT = 2) one CTA has the SM
+#ifndef B200Q_W1
+#define B200Q_W1 16
 #endif
-constexpr int STREAM_WARPS = B200Q_STREAM_WARPS;
+#ifndef B200Q_W2
+#define B200Q_W2 16
+#endif
+constexpr int stream_warps(int mt) { return mt == 1 ? B200Q_W1 : B200Q_W2; }
+// bytes of mbarriers in front of the rings: 8 slots of 8 bytes per warp, rounded up to 1 KB
+constexpr int stream_header_bytes(int mt) { return (stream_warps(mt) * 64 + 1023) / 1024 * 1024; }
 constexpr int STREAM_SC_GROUPS = 16;  // groups per warp in the shared-memory scale cache (32 bytes each)
 // 128-row groups per ring item: items of 1..2 KB for every bit width
 constexpr int stream_gi(int bits) { return bits <= 2 ? 4 : bits <= 5 ? 2 : 1; }
@@ -68,7 +74,7 @@ struct StreamParams {
   int M, N, K;
   int lda, ldc;
   int KB, NT;            // K/512, N/16
-  int gshift;            // log2(group / 128), or -1 when there is one group per column (group == K)
+  int gshift, gdiv;      // scale row of 128-row group i: i >> gshift when gdiv = group / 128 is a power of two, else i / gdiv
   int S, KBc, CPC;       // k chunks, k blocks per chunk, CTAs per chunk; grid = S * CPC
   int T_own;             // whole column tiles per CTA (<= NT / CPC); the rest is shared item-wise
   int pitch;             // shared-memory row pitch of the activation chunk, in halfs
@@ -87,9 +93,10 @@ struct UmmaParams {
   float* partial;        // [M, N] fp32 split-K scratch, zero on entry and on exit
   int* counters;         // [n_tiles * m_tiles], zero on entry and on exit
   int* status;           // workspace status header
-  int M, N, K, KB;       // KB = K / 512
+  int M, N, K, G;        // G = K / 128
   int ldc;
-  int gshift;            // log2(group / 128), or -1 when group == K
+  int group;             // rows per scale: 32, 64 or a multiple of 128
+  int rpg;               // scale rows per 128-row group: 128 / group for group < 128, else 1
   int tm;                // activation rows per CTA tile = N extent of the MMA (32, 64, 128 or 256)
   int m_tiles, n_tiles;  // ceil(M / tm), ceil(N / 128)
   int splits;            // split-K factor
@@ -108,9 +115,10 @@ struct WideParams {
   float* partial;        // [M, N] fp32 split-K scratch, zero on entry and on exit
   int* counters;         // [n_tiles * m_tiles], zero on entry and on exit
   int* status;           // workspace status header
-  int M, N, K, KB;       // KB = K / 512
+  int M, N, K, G;        // G = K / 128
   int ldc;
-  int gshift;            // log2(group / 128), or -1 when group == K
+  int group;             // rows per scale: 32, 64 or a multiple of 128
+  int rpg;               // scale rows per 128-row group: 128 / group for group < 128, else 1
   int m_tiles, n_tiles;  // ceil(M / 128), ceil(N / 256)
   int splits;            // split-K factor
   int kblocks_per_split; // 64-row k blocks per work item (even)
@@ -125,7 +133,7 @@ struct DequantParams {
   const uint4* bq;
   const __half* scales;
   __half* w;  // [K, N] row-major (16-bit elements of the activation dtype)
-  int N, K, group, KB, NT;
+  int N, K, group, G, NT;  // G = K / 128
   int act;    // 0 fp16, 1 bf16
 };
 

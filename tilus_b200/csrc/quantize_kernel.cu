@@ -14,7 +14,7 @@
 // Pass 1: one warp per (column, group) reduces the absmax.  Pass 2: one thread per unit (32 codes
 // of one column) quantizes its 32 weights, builds the unit's b plane words (layout described in
 // decode.cuh / tilus_b200/packing.py; signed integers in offset binary) and stores them at the
-// unit's place in the [column tile][k block][group][half][lane] order.
+// unit's place in the [column tile][128-row group][half][lane] order.
 #include "common.cuh"
 
 namespace b200q {
@@ -26,7 +26,7 @@ struct QuantParams {
   uint32_t* bq;    // packed output, K*N*nbits/8 bytes
   unsigned short* scales;  // [K/group, N], 16-bit patterns of the activation dtype
   int act;         // 0 fp16, 1 bf16
-  int N, K, KB, group;
+  int N, K, G, group;  // G = K / 128
   int kind, nbits, ebits, mbits;  // kind: 0 unsigned, 1 two's complement, 2 float
   float minv, maxv;
 };
@@ -85,16 +85,16 @@ __device__ __forceinline__ uint32_t encode_float_code(float x, int nbits, int e,
 }
 
 __global__ void __launch_bounds__(128) quant_pack_kernel(const QuantParams p) {
-  // unit index = (((nt * KB + kb) * 4 + c) * 2 + half) * 32 + lane,  lane = r * 4 + j
+  // unit index = ((nt * G + g) * 2 + half) * 32 + lane,  lane = r * 4 + j,  g = 128-row group of K
   const long long unit = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long units = (long long)p.N * p.K / 32;
   if (unit >= units) return;
-  const int lane = (int)(unit & 31), half = (int)((unit >> 5) & 1), c = (int)((unit >> 6) & 3);
-  const long long blk = unit >> 8;
-  const int kb = (int)(blk % p.KB), nt = (int)(blk / p.KB);
+  const int lane = (int)(unit & 31), half = (int)((unit >> 5) & 1);
+  const long long grp = unit >> 6;
+  const int g = (int)(grp % p.G), nt = (int)(grp / p.G);
   const int r = lane >> 2, j = lane & 3;
   const int n = nt * 16 + half * 8 + r;
-  const int k0 = kb * 512 + c * 128 + j * 32;
+  const int k0 = g * 128 + j * 32;
   const float s = load_scale(p, (size_t)(k0 / p.group) * p.N + n);
   const uint32_t mask = (1u << p.nbits) - 1u;
   const uint32_t flip = p.kind == 1 ? (1u << (p.nbits - 1)) : 0u;  // offset binary for signed integers
@@ -133,7 +133,7 @@ cudaError_t quantize_launch(const void* w, int w_dtype, int ldw, void* bq, void*
   p.bq = reinterpret_cast<uint32_t*>(bq);
   p.scales = reinterpret_cast<unsigned short*>(scales);
   p.act = act;
-  p.N = N; p.K = K; p.KB = K / BLOCK_K; p.group = group;
+  p.N = N; p.K = K; p.G = K / 128; p.group = group;
   p.kind = kind; p.nbits = nbits; p.ebits = ebits; p.mbits = mbits;
   p.minv = minv; p.maxv = maxv;
   const long long warps = (long long)N * (K / group);

@@ -126,16 +126,13 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
 }
 
 #ifndef B200Q_S_CLASS2
-#define B200Q_S_CLASS2 1
+#define B200Q_S_CLASS2 0
 #endif
 #ifndef B200Q_S_FENCE
 #define B200Q_S_FENCE 0
 #endif
 #ifndef B200Q_S_QUAD
-#define B200Q_S_QUAD 1
-#endif
-#ifndef B200Q_MT2_PER_SM
-#define B200Q_MT2_PER_SM 1
+#define B200Q_S_QUAD 0
 #endif
 
 // The 8 k16 steps of one 128-row group, four pairs of codes at a time: pairs 4*SP .. 4*SP+3 of the
@@ -167,8 +164,8 @@ struct GroupSteps {
 };
 
 // Shared-memory layout (byte offsets from the dynamic smem base):
-//   [0, 1024)    mbarriers [warp][stage]   (16 warps x up to 8 stages)
-//   [1024, ...)  rings [warp][stage][ITEM_BYTES] of packed weights
+//   [0, HDR)     mbarriers [warp][stage]   (up to 8 stages of 8 bytes per warp, HDR a multiple of 1 KB)
+//   [HDR, ...)   rings [warp][stage][ITEM_BYTES] of packed weights
 //   then         scale caches [warp][STREAM_SC_GROUPS][16] 16-bit scales: those of the warp's next groups
 //   then         tile sums of the CTA's own column tiles [T_own][16 columns][8*MT rows] floats
 //   then         activation chunk [M][pitch] halfs, then group sums [groups][8*MT] floats
@@ -178,7 +175,7 @@ struct GroupSteps {
 // and shared memory, which keeps the two 8-row accumulator sets in registers and a K chunk of the
 // 16 activation rows next to the rings.
 template <int VAR, int MT, bool GATHER, int ACT>
-__global__ void __launch_bounds__(STREAM_WARPS * 32, MT == 1 ? 2 : B200Q_MT2_PER_SM) stream_kernel(const StreamParams p) {
+__global__ void __launch_bounds__(stream_warps(MT) * 32, MT == 1 ? 2 : 1) stream_kernel(const StreamParams p) {
   constexpr int B = var_bits(VAR);
   constexpr int MP = 8 * MT;
   constexpr int BIAS = var_bias(VAR);
@@ -186,7 +183,8 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, MT == 1 ? 2 : B200Q_MT2_PER
   constexpr int NI = 4 / GI;  // items per block
   constexpr int ITEM_BYTES = GI * 256 * B;
   constexpr int SLOT_BYTES = ITEM_BYTES;
-  constexpr int NWARPS = STREAM_WARPS;
+  constexpr int NWARPS = stream_warps(MT);
+  constexpr int HDR = stream_header_bytes(MT);
   constexpr int SCG = STREAM_SC_GROUPS;
   constexpr float F = (float)(1u << lin_factor_log2(VAR));
   // Where the linear pattern of a pair sits in the fp16 mantissa (bit T, decode.cuh int_target) sets a
@@ -199,7 +197,7 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, MT == 1 ? 2 : B200Q_MT2_PER
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const int NST = p.stages;
   const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem_raw);
-  unsigned char* sScale = smem_raw + 1024 + (size_t)NWARPS * NST * SLOT_BYTES;
+  unsigned char* sScale = smem_raw + HDR + (size_t)NWARPS * NST * SLOT_BYTES;
   float* sAcc = reinterpret_cast<float*>(sScale + (size_t)NWARPS * SCG * 32);
   __half* sA = reinterpret_cast<__half*>(sAcc + (size_t)p.T_own * 16 * MP);
   // 64 zero bytes after the activation chunk: what the lanes of rows that do not exist read
@@ -237,7 +235,7 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, MT == 1 ? 2 : B200Q_MT2_PER
     }
   }
   const int n_left = l1 - l0, n_total = n_left + p.T_own * IPT;
-  // n_total < 2^26 (column tiles x k blocks x 4 of one CTA), NWARPS = 16: the products fit in 32 bits
+  // n_total < 2^26 (column tiles x k blocks x 4 of one CTA), NWARPS <= 32: the products fit in 32 bits
   const int v0 = (int)((unsigned)n_total * (unsigned)warp / NWARPS), v1 = (int)((unsigned)n_total * (unsigned)(warp + 1) / NWARPS);
   // this warp's two item runs: cA items of left-over tiles, then cB items of the CTA's own tiles
   const int cA = v0 < n_left ? min(v1, n_left) - v0 : 0;
@@ -251,7 +249,7 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, MT == 1 ? 2 : B200Q_MT2_PER
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   const uint32_t bar0 = smem_base + warp * 64;
-  const uint32_t ring_s = smem_base + 1024 + warp * NST * SLOT_BYTES;
+  const uint32_t ring_s = smem_base + HDR + warp * NST * SLOT_BYTES;
 
   // ---- producer: lane 0 requests the items of the warp, in order, into the warp's ring ----
   int pc_q, issued = 0;
@@ -288,7 +286,8 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, MT == 1 ? 2 : B200Q_MT2_PER
     } else {
       tile = own_tile0 + div_ipt(oB + itx - cA, q);
     }
-    const int row = p.gshift >= 0 ? ((kb_base * 4 + q * GI + gi) >> p.gshift) : 0;
+    const int gidx128 = kb_base * 4 + q * GI + gi;  // 128-row group of K
+    const int row = p.gshift >= 0 ? (gidx128 >> p.gshift) : gidx128 / p.gdiv;
     return reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(p.scales) + (size_t)row * p.N + tile * 16) + (lane & 1);
   };
   auto fill_scales = [&](int first) {
@@ -381,39 +380,58 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, MT == 1 ? 2 : B200Q_MT2_PER
       const int e = lin_prescale_shift(VAR, h0 + q);
       mult[q] = h2_from_bits(dup16((uint32_t)(15 - e) << 10));  // 2^-e
     }
+    // four loads in flight per thread: the staging pass costs one memory round trip per four
+    // 16-byte pieces instead of one per piece
+    constexpr int SB = 4;
     int m = 0, vv = tid;  // idx = m * vec_per_row + vv
-    for (int idx = tid; idx < total; idx += NWARPS * 32) {
-      while (vv >= vec_per_row) { vv -= vec_per_row; ++m; }
-      const int kk = vv * 8;
-      vv += NWARPS * 32;
-      const uint4* src = reinterpret_cast<const uint4*>(a_base + (size_t)m * p.lda + (size_t)kb_base * 512 + kk);
-      uint4 v = GATHER ? *src : __ldg(src);
-      if constexpr (ACT == 1) {
-        v.x = bf16x2_to_f16x2(v.x); v.y = bf16x2_to_f16x2(v.y);
-        v.z = bf16x2_to_f16x2(v.z); v.w = bf16x2_to_f16x2(v.w);
-      }
-      __half2 x0 = h2_from_bits(v.x), x1 = h2_from_bits(v.y), x2 = h2_from_bits(v.z), x3 = h2_from_bits(v.w);
-      if constexpr (BIAS != 0) {
-        const float2 f0 = __half22float2(x0), f1 = __half22float2(x1), f2 = __half22float2(x2),
-                     f3 = __half22float2(x3);
-        float sum = ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y));
-        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-        sum += __shfl_xor_sync(0xffffffffu, sum, 4);
-        sum += __shfl_xor_sync(0xffffffffu, sum, 8);
-        if ((lane & 15) == 0) {
-          const float nbv = -(float)BIAS * sum * (1.0f / F);
-          float* q4 = sNb + (((kk >> 7) * MT + (m >> 3)) * 4 + ((m & 7) >> 1)) * 4 + (m & 1);
-          q4[0] = nbv;
-          q4[2] = nbv;
+    for (int idx0 = tid; idx0 < total; idx0 += SB * NWARPS * 32) {
+      uint4 vq[SB];
+      int mq[SB], kq[SB];
+#pragma unroll
+      for (int u = 0; u < SB; ++u) {
+        const int idx = idx0 + u * NWARPS * 32;
+        while (vv >= vec_per_row) { vv -= vec_per_row; ++m; }
+        mq[u] = m; kq[u] = vv * 8;
+        vv += NWARPS * 32;
+        if (idx < total) {
+          const uint4* src = reinterpret_cast<const uint4*>(a_base + (size_t)mq[u] * p.lda + (size_t)kb_base * 512 + kq[u]);
+          vq[u] = GATHER ? *src : __ldg(src);
         }
       }
-      if constexpr (PRESCALE) {
-        x0 = __hmul2(x0, mult[0]); x1 = __hmul2(x1, mult[1]);
-        x2 = __hmul2(x2, mult[2]); x3 = __hmul2(x3, mult[3]);
+#pragma unroll
+      for (int u = 0; u < SB; ++u) {
+        const int idx = idx0 + u * NWARPS * 32;
+        if (idx >= total) continue;  // uniform over each half-warp: 16 consecutive pieces lie in one row
+        uint4 v = vq[u];
+        const int mm = mq[u], kk = kq[u];
+        if constexpr (ACT == 1) {
+          v.x = bf16x2_to_f16x2(v.x); v.y = bf16x2_to_f16x2(v.y);
+          v.z = bf16x2_to_f16x2(v.z); v.w = bf16x2_to_f16x2(v.w);
+        }
+        __half2 x0 = h2_from_bits(v.x), x1 = h2_from_bits(v.y), x2 = h2_from_bits(v.z), x3 = h2_from_bits(v.w);
+        if constexpr (BIAS != 0) {
+          const float2 f0 = __half22float2(x0), f1 = __half22float2(x1), f2 = __half22float2(x2),
+                       f3 = __half22float2(x3);
+          float sum = ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y));
+          const unsigned hm = 0xffffu << (lane & 16);  // the 16 lanes that share this 128-column group
+          sum += __shfl_xor_sync(hm, sum, 1);
+          sum += __shfl_xor_sync(hm, sum, 2);
+          sum += __shfl_xor_sync(hm, sum, 4);
+          sum += __shfl_xor_sync(hm, sum, 8);
+          if ((lane & 15) == 0) {
+            const float nbv = -(float)BIAS * sum * (1.0f / F);
+            float* q4 = sNb + (((kk >> 7) * MT + (mm >> 3)) * 4 + ((mm & 7) >> 1)) * 4 + (mm & 1);
+            q4[0] = nbv;
+            q4[2] = nbv;
+          }
+        }
+        if constexpr (PRESCALE) {
+          x0 = __hmul2(x0, mult[0]); x1 = __hmul2(x1, mult[1]);
+          x2 = __hmul2(x2, mult[2]); x3 = __hmul2(x3, mult[3]);
+        }
+        v.x = bits_from_h2(x0); v.y = bits_from_h2(x1); v.z = bits_from_h2(x2); v.w = bits_from_h2(x3);
+        *reinterpret_cast<uint4*>(sA + (size_t)mm * p.pitch + kk + (kk >> 5) * 8) = v;
       }
-      v.x = bits_from_h2(x0); v.y = bits_from_h2(x1); v.z = bits_from_h2(x2); v.w = bits_from_h2(x3);
-      *reinterpret_cast<uint4*>(sA + (size_t)m * p.pitch + kk + (kk >> 5) * 8) = v;
     }
   }
   if (sc_first_valid) *reinterpret_cast<uint4*>(sc_warp + ((lane >> 1) % SCG) * 32 + (lane & 1) * 16) = sc_first;
@@ -696,7 +714,7 @@ static cudaError_t launch_one(const StreamParams& p, int smem_bytes, cudaStream_
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(p.S * p.CPC), 1, 1);
-  cfg.blockDim = dim3(STREAM_WARPS * 32, 1, 1);
+  cfg.blockDim = dim3(stream_warps(MT) * 32, 1, 1);
   cfg.dynamicSmemBytes = (size_t)smem_bytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];

@@ -68,7 +68,8 @@ struct UmmaBarriers {
   int last_flag;
 };
 
-__host__ __device__ constexpr int umma_wstage_bytes(int bits) { return 2048 * bits + 256; }
+// a ring stage: the packed weights of 128 columns x 128 rows, then up to four rows of 128 scales
+__host__ __device__ constexpr int umma_wstage_bytes(int bits) { return 2048 * bits + 1024; }
 
 template <int VAR, int ACT>
 __global__ void __launch_bounds__(UMMA_THREADS, 1)
@@ -158,17 +159,19 @@ umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
         uint32_t w[2 * B];
         const uint32_t st = wring_s + (uint32_t)gs * WSTAGE;
         lds_two_units<B>(st + lane_off, w);
-        unsigned short sbits;
-        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sbits) : "r"(st + 2048u * B + (uint32_t)nl * 2u));
+        // the scales of this thread's two 32-row units: scale row (unit * rpg) / 4 of the stage
+        unsigned short sb0, sb1;
+        const uint32_t sc_s = st + 2048u * B + (uint32_t)nl * 2u;
+        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sb0) : "r"(sc_s + (uint32_t)(((2 * grp) * p.rpg) >> 2) * 256u));
+        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sb1) : "r"(sc_s + (uint32_t)(((2 * grp + 1) * p.rpg) >> 2) * 256u));
         if (!nvalid) {
 #pragma unroll
           for (int q = 0; q < 2 * B; ++q) w[q] = 0u;
-          sbits = 0;
+          sb0 = 0; sb1 = 0;
         }
         uint32_t out[32];
-        const uint32_t s2 = (uint32_t)sbits * 0x00010001u;  // the 16-bit scale in both halves
-        unit_decode_scaled<VAR, ACT>(w, s2, out);
-        unit_decode_scaled<VAR, ACT>(w + B, s2, out + 16);
+        unit_decode_scaled<VAR, ACT>(w, (uint32_t)sb0 * 0x00010001u, out);  // the 16-bit scale in both halves
+        unit_decode_scaled<VAR, ACT>(w + B, (uint32_t)sb1 * 0x00010001u, out + 16);
         // the ring stage has been read (its values fed the arithmetic above)
         __syncwarp();
         if (lane == 0) mbar_arrive(BAR_ADDR(g_empty, gs));
@@ -411,24 +414,24 @@ umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
         const uint32_t dst = wring_s + (uint32_t)gs * WSTAGE;
         if (lane == 0)
           asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar),
-                       "r"((uint32_t)pieces * (256u * B + 32u))
+                       "r"((uint32_t)pieces * (256u * B + 32u * (uint32_t)p.rpg))
                        : "memory");
         __syncwarp();
         const int G = (kk0 >> 1) + g;  // 128-row group of K
         if (lane < pieces) {
-          const unsigned char* src = bq + ((size_t)(nt0 + lane) * p.KB + (G >> 2)) * (size_t)(1024 * B) +
-                                     (size_t)(G & 3) * (256 * B);
+          const unsigned char* src = bq + ((size_t)(nt0 + lane) * p.G + G) * (size_t)(256 * B);
           asm volatile(
               "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
                   dst + (uint32_t)lane * (256u * B)),
               "l"(src), "r"(256u * B), "r"(bar)
               : "memory");
-        } else if (lane == 8) {
-          const int row = p.gshift >= 0 ? (G >> p.gshift) : 0;
+        } else if (lane >= 8 && lane < 8 + p.rpg) {
+          // scale row(s) of the group: one per 128 / rpg rows
+          const int row = p.rpg == 1 ? (G * 128) / p.group : G * p.rpg + (lane - 8);
           const __half* src = p.scales + (size_t)row * p.N + n_tile * 128;
           asm volatile(
               "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                  dst + 2048u * B),
+                  dst + 2048u * B + (uint32_t)(lane - 8) * 256u),
               "l"(src), "r"((uint32_t)pieces * 32u), "r"(bar)
               : "memory");
         }

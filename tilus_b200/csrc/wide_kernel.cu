@@ -62,7 +62,8 @@ struct WideBarriers {
   int last_flag;
 };
 
-__host__ __device__ constexpr int wide_wstage_bytes(int bits) { return 4096 * bits + 512; }
+// a ring stage: the packed weights of 256 columns x 128 rows, then up to four rows of 256 scales
+__host__ __device__ constexpr int wide_wstage_bytes(int bits) { return 4096 * bits + 2048; }
 
 template <int VAR, int ACT>
 __global__ void __launch_bounds__(WIDE_THREADS, 1)
@@ -154,10 +155,16 @@ wide_kernel(const WideParams p, const __grid_constant__ CUtensorMap tmap_a) {
         const int gs = g_run % WG;
         if (!mbar_wait_abortable(BAR_ADDR(g_full, gs), (uint32_t)(g_run / WG) & 1u, abort_flag)) { good = false; break; }
         const uint32_t st = w_s + (uint32_t)gs * WSTAGE;
-        unsigned short sbits;
-        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sbits) : "r"(st + 4096u * B + (uint32_t)nl * 2u));
-        if (!nvalid) sbits = 0;
-        const uint32_t s2 = (uint32_t)sbits * 0x00010001u;  // the 16-bit scale in both halves
+        // the scales of this column's four 32-row units: scale row (unit * rpg) / 4 of the stage
+        uint32_t s2u[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          unsigned short sbits;
+          asm volatile("ld.shared.u16 %0, [%1];"
+                       : "=h"(sbits)
+                       : "r"(st + 4096u * B + (uint32_t)((u * p.rpg) >> 2) * 512u + (uint32_t)nl * 2u));
+          s2u[u] = nvalid ? (uint32_t)sbits * 0x00010001u : 0u;  // the 16-bit scale in both halves
+        }
         // all of this column's codes of the group go to registers first, so that the ring stage is
         // free for the next copy while the decode and the stores below run
         // Adjacent columns lie 16 * B bytes apart in the ring stage, so lanes reading the same unit of
@@ -192,8 +199,9 @@ wide_kernel(const WideParams p, const __grid_constant__ CUtensorMap tmap_a) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {  // the two 64-row blocks of the group
           uint32_t out[32];
-          unit_decode_scaled<VAR, ACT>(wq[h][0], s2, out);
-          unit_decode_scaled<VAR, ACT>(wq[h][1], s2, out + 16);
+          // wq[h][0] is unit usw of block h, wq[h][1] unit usw ^ 1
+          unit_decode_scaled<VAR, ACT>(wq[h][0], usw ? s2u[2 * h + 1] : s2u[2 * h], out);
+          unit_decode_scaled<VAR, ACT>(wq[h][1], usw ? s2u[2 * h] : s2u[2 * h + 1], out + 16);
           const int bi = 2 * g_run + h;  // running 64-block index
           const int sb = bi % WIDE_SB;
           if (!mbar_wait_abortable(BAR_ADDR(b_empty, sb), ((uint32_t)(bi / WIDE_SB) & 1u) ^ 1u, abort_flag)) { good = false; break; }
@@ -363,25 +371,25 @@ wide_kernel(const WideParams p, const __grid_constant__ CUtensorMap tmap_a) {
         const uint32_t dst = w_s + (uint32_t)gs * WSTAGE;
         if (lane == 0)
           asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar),
-                       "r"((uint32_t)pieces * (256u * B + 32u))
+                       "r"((uint32_t)pieces * (256u * B + 32u * (uint32_t)p.rpg))
                        : "memory");
         __syncwarp();
         const int G = (kk0 >> 1) + g;  // 128-row group of K
         if (lane < pieces) {
-          const unsigned char* src = bq + ((size_t)(nt0 + lane) * p.KB + (G >> 2)) * (size_t)(1024 * B) +
-                                     (size_t)(G & 3) * (256 * B);
+          const unsigned char* src = bq + ((size_t)(nt0 + lane) * p.G + G) * (size_t)(256 * B);
           asm volatile(
               "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
                   dst + (uint32_t)lane * (256u * B)),
               "l"(src), "r"(256u * B), "r"(bar)
               : "memory");
         }
-        if (lane == 16) {
-          const int row = p.gshift >= 0 ? (G >> p.gshift) : 0;
+        if (lane >= 16 && lane < 16 + p.rpg) {
+          // scale row(s) of the group: one per 128 / rpg rows
+          const int row = p.rpg == 1 ? (G * 128) / p.group : G * p.rpg + (lane - 16);
           const __half* src = p.scales + (size_t)row * p.N + n_tile * 256;
           asm volatile(
               "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                  dst + 4096u * B),
+                  dst + 4096u * B + (uint32_t)(lane - 16) * 512u),
               "l"(src), "r"((uint32_t)pieces * 32u), "r"(bar)
               : "memory");
         }

@@ -25,17 +25,19 @@ pair as the two 16-bit halves of a register, ready for the fp16 magic-number
 conversion.  Signed integer codes are stored with the sign bit flipped (offset
 binary) so that signed and unsigned types decode with one subtraction.
 
-*Block*: 16 columns x 512 rows = 4 row groups of 128 x 16 columns x 4 units of 32.
-Stored group by group; inside group c the units are ordered [half = 0..1][lane = 0..31]
-with lane = r*4 + j holding column n = nt*16 + half*8 + r, rows kb*512 + c*128 + j*32 +
-[0, 32), each unit as its b words: word offset ((c*2 + half)*32 + lane)*b + v.  So a
-128-row group of the block (one scale per column when group_size is a multiple of 128)
-is 256*b contiguous bytes, a whole block 1024*b contiguous bytes, the four lanes that
-share a column split a group in 32-row units, and the 128 rows of one column of a
-group are 16*b contiguous bytes.
+*Group*: 16 columns x 128 rows = 16 columns x 4 units of 32.  Inside group g of column tile nt
+the units are ordered [half = 0..1][lane = 0..31] with lane = r*4 + j holding column
+n = nt*16 + half*8 + r, rows g*128 + j*32 + [0, 32), each unit as its b words: word offset
+(half*32 + lane)*b + v.  So a 128-row group (one scale per column when group_size is a
+multiple of 128) is 256*b contiguous bytes, the four lanes that share a column split a group
+in 32-row units, and the 128 rows of one column of a group are 16*b contiguous bytes.  Four
+consecutive groups form a 512-row *block* of 1024*b contiguous bytes, the unit of work of the
+decode kernel.
 
-*Matrix*: blocks in [nt][kb] order (column-tile major), so a contiguous range of
-column tiles - an N shard - is a contiguous byte range.
+*Matrix*: groups in [nt][g] order (column-tile major, g = 0 .. K/128 - 1), so a contiguous
+range of column tiles - an N shard - is a contiguous byte range.  K must be a multiple of
+128 (the decode kernel for up to 16 rows wants whole blocks, K a multiple of 512; other K
+run on the tensor-core kernels).
 """
 from __future__ import annotations
 
@@ -46,6 +48,7 @@ from .dtypes import KIND_INT, WeightDType, weight_dtype
 LAYOUT_VERSION = 1
 BLOCK_N = 16
 BLOCK_K = 512
+GROUP_K = 128
 UNIT_K = 32
 
 PLANES = {1: (1,), 2: (2,), 3: (2, 1), 4: (4,), 5: (4, 1), 6: (4, 2), 7: (4, 2, 1), 8: (8,)}
@@ -125,9 +128,9 @@ def pack_ref_tiled(codes: torch.Tensor, nbits: int) -> torch.Tensor:
 # codes <-> b200 interleave
 # ---------------------------------------------------------------------------
 def check_shape(K: int, N: int) -> None:
-    if K % BLOCK_K != 0 or N % BLOCK_N != 0:
+    if K % GROUP_K != 0 or N % BLOCK_N != 0:
         raise ValueError(
-            f"b200 weight layout needs in_features % {BLOCK_K} == 0 and out_features % {BLOCK_N} == 0, "
+            f"b200 weight layout needs in_features % {GROUP_K} == 0 and out_features % {BLOCK_N} == 0, "
             f"got K={K}, N={N}"
         )
 
@@ -187,15 +190,15 @@ def interleave(codes: torch.Tensor, dt, chunk_tiles: int = 64) -> torch.Tensor:
     b = dt.nbits
     K, N = codes.shape
     check_shape(K, N)
-    KB, NT = K // BLOCK_K, N // BLOCK_N
-    out = torch.empty(NT, KB, 4, 2, 32, b, dtype=torch.int32, device=codes.device)
+    G, NT = K // GROUP_K, N // BLOCK_N
+    out = torch.empty(NT, G, 2, 32, b, dtype=torch.int32, device=codes.device)
     sc = stored_codes(codes.to(torch.uint8), dt)
     for t0 in range(0, NT, chunk_tiles):
         t1 = min(NT, t0 + chunk_tiles)
-        blk = sc[:, t0 * 16 : t1 * 16].reshape(KB, 4, 4, 32, t1 - t0, 2, 8)  # kb c j i nt half r
-        blk = blk.permute(4, 0, 1, 5, 6, 2, 3)  # nt kb c half r j i
-        words = _unit_words(blk.to(torch.int32), b)  # nt kb c half r j v
-        out[t0:t1] = words.reshape(t1 - t0, KB, 4, 2, 32, b)
+        blk = sc[:, t0 * 16 : t1 * 16].reshape(G, 4, 32, t1 - t0, 2, 8)  # g j i nt half r
+        blk = blk.permute(3, 0, 4, 5, 1, 2)  # nt g half r j i
+        words = _unit_words(blk.to(torch.int32), b)  # nt g half r j v
+        out[t0:t1] = words.reshape(t1 - t0, G, 2, 32, b)
     return out.reshape(-1).view(torch.uint8)
 
 
@@ -204,12 +207,12 @@ def deinterleave(storage: torch.Tensor, dt, K: int, N: int) -> torch.Tensor:
     dt = weight_dtype(dt)
     b = dt.nbits
     check_shape(K, N)
-    KB, NT = K // BLOCK_K, N // BLOCK_N
+    G, NT = K // GROUP_K, N // BLOCK_N
     st = storage.reshape(-1).contiguous()
     assert st.dtype == torch.uint8 and st.numel() * 8 == K * N * b
-    words = st.view(torch.int32).reshape(NT, KB, 4, 2, 8, 4, b)  # nt kb c half r j v
-    codes = _words_to_codes(words, b)  # nt kb c half r j i
-    codes = codes.permute(1, 2, 5, 6, 0, 3, 4).reshape(K, N)  # kb c j i nt half r
+    words = st.view(torch.int32).reshape(NT, G, 2, 8, 4, b)  # nt g half r j v
+    codes = _words_to_codes(words, b)  # nt g half r j i
+    codes = codes.permute(1, 4, 5, 0, 2, 3).reshape(K, N)  # g j i nt half r
     return stored_codes(codes.contiguous(), dt)
 
 
