@@ -301,10 +301,25 @@ static int make_plan(int M, int N, int K, int var, int group, b200q_plan_t* pl) 
     }
   }
   // a few dozen rows: weights on the wide side of the MMA; beyond, the transposed prefill kernel
-  if (M <= kWideMaxRows) plan_wide(M, N, K, bits, di, pl);
-  else plan_umma(M, N, K, bits, di, pl);
+  if (M <= kWideMaxRows) {
+    plan_wide(M, N, K, bits, di, pl);
+  } else {
+    // A last row tile of at most 16 rows (M = 4097: one row) would cost a whole 256-row tile per
+    // column tile; those rows go to the decode kernel in a second launch instead (passes = 2).
+    const int tail = M % 256;
+    b200q_plan_t tail_plan;
+    if (M > 256 && tail >= 1 && tail <= kStreamMaxRows && stream_takes(K, group) &&
+        plan_stream(tail, N, K, bits, di, &tail_plan) == ST_OK) {
+      plan_umma(M - tail, N, K, bits, di, pl);
+      pl->passes = 2;
+    } else {
+      plan_umma(M, N, K, bits, di, pl);
+    }
+  }
   const size_t part = pl->splits > 1 ? (size_t)M * N * sizeof(float) : 0;
-  pl->workspace_bytes = WS_HEADER_BYTES + ws_counter_bytes(N) + part;
+  size_t need = WS_HEADER_BYTES + ws_counter_bytes(N) + part;
+  if (pl->passes == 2 && need < stream_workspace_bytes(N)) need = stream_workspace_bytes(N);
+  pl->workspace_bytes = need;
   return ST_OK;
 }
 
@@ -489,6 +504,22 @@ static int run_gemm(const void* a, int lda, const void* bq, const void* scales, 
   if (((uintptr_t)a | (uintptr_t)bq | (uintptr_t)c) & 15) return ST_INVALID_ARG;
   if (((uintptr_t)scales) & 1) return ST_INVALID_ARG;
   if (lda < K || ldc < N || (lda % 8) != 0) return ST_INVALID_ARG;
+  if (pl.kernel == 1 && pl.passes == 2) {
+    // the full 256-row tiles on the tcgen05 kernel, the short last tile on the decode kernel
+    const int tail = M % 256;
+    if (M <= 256 || tail < 1 || tail > kStreamMaxRows) return ST_INVALID_ARG;
+    b200q_plan_t tail_plan;
+    std::memset(&tail_plan, 0, sizeof(tail_plan));
+    if (plan_stream(tail, N, K, var_bits(var), device_info(), &tail_plan) != ST_OK) return ST_UNSUPPORTED;
+    b200q_plan_t head = pl;
+    head.passes = 1;
+    const int st = run_umma(a, lda, bq, scales, c, ldc, M - tail, N, K, var, group, act, workspace, ws_bytes, stream, head);
+    if (st != ST_OK) return st;
+    const size_t row0 = (size_t)(M - tail);
+    return run_stream(reinterpret_cast<const unsigned short*>(a) + row0 * lda, lda, bq, scales,
+                      reinterpret_cast<unsigned short*>(c) + row0 * ldc, ldc, tail, N, K, var, group, act, workspace,
+                      ws_bytes, stream, tail_plan);
+  }
   if (pl.kernel == 1)
     return run_umma(a, lda, bq, scales, c, ldc, M, N, K, var, group, act, workspace, ws_bytes, stream, pl);
   if (pl.kernel == 2)

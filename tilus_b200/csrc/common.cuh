@@ -34,14 +34,10 @@ constexpr size_t WS_HEADER_BYTES = 256;
 inline size_t ws_counter_bytes(int N) { return (((size_t)(N / BLOCK_N) * 4) + 255) / 256 * 256; }
 
 // ---- stream kernel (up to 16 rows per launch; the default for M <= 8): item-balanced, ring-fed --
-// warps per CTA: up to 8 rows (MT = 1) two CTAs share an SM; 9..16 rows (MT = 2) one CTA has the SM
-#ifndef B200Q_W1
-#define B200Q_W1 16
-#endif
-#ifndef B200Q_W2
-#define B200Q_W2 16
-#endif
-constexpr int stream_warps(int mt) { return mt == 1 ? B200Q_W1 : B200Q_W2; }
+// warps per CTA.  Up to 8 rows (MT = 1) two CTAs share an SM: 12 warps each leave 85 registers per
+// thread, which the loop needs to stay out of local memory (16 warps at 64 registers spilled and
+// measured 5-10 % slower; 10 and 14 warps were no better).  9..16 rows (MT = 2): one CTA has the SM.
+constexpr int stream_warps(int mt) { return mt == 1 ? 12 : 16; }
 // bytes of mbarriers in front of the rings: 8 slots of 8 bytes per warp, rounded up to 1 KB
 constexpr int stream_header_bytes(int mt) { return (stream_warps(mt) * 64 + 1023) / 1024 * 1024; }
 constexpr int STREAM_SC_GROUPS = 16;  // groups per warp in the shared-memory scale cache (32 bytes each)

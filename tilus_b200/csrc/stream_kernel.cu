@@ -125,44 +125,6 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-#ifndef B200Q_S_CLASS2
-#define B200Q_S_CLASS2 0
-#endif
-#ifndef B200Q_S_FENCE
-#define B200Q_S_FENCE 0
-#endif
-#ifndef B200Q_S_QUAD
-#define B200Q_S_QUAD 0
-#endif
-
-// The 8 k16 steps of one 128-row group, four pairs of codes at a time: pairs 4*SP .. 4*SP+3 of the
-// lane's two units (columns r and r+8) are turned into operands right before the two MMAs that take
-// them, so that only eight operand registers are live at a time.  d[mt][0] and d[mt][1] are the two
-// accumulation chains of 8-row tile mt.
-template <int VAR, int MT, bool CLASS2, int SP>
-struct GroupSteps {
-  static __device__ __forceinline__ void run(const uint32_t* w0, const uint32_t* w1,
-                                             const unsigned char* const (&a_ptr)[MT], const uint32_t (&kmask)[MT],
-                                             uint32_t koff, float (&d)[MT][2][4]) {
-    constexpr int H = 4 * SP;
-    constexpr int P01 = CLASS2 ? 2 : 1;  // second pair of chain 0's MMA
-    constexpr int P10 = CLASS2 ? 1 : 2;  // first pair of chain 1's MMA
-    const uint32_t x00 = pair_lin<VAR, H>(w0), y00 = pair_lin<VAR, H>(w1);
-    const uint32_t x01 = pair_lin<VAR, H + P01>(w0), y01 = pair_lin<VAR, H + P01>(w1);
-    const uint32_t x10 = pair_lin<VAR, H + P10>(w0), y10 = pair_lin<VAR, H + P10>(w1);
-    const uint32_t x11 = pair_lin<VAR, H + 3>(w0), y11 = pair_lin<VAR, H + 3>(w1);
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
-      const uint4 av = *reinterpret_cast<const uint4*>(a_ptr[mt] + (koff & kmask[mt]) + SP * 16);
-      const uint32_t b00 = av.x, b01 = CLASS2 ? av.z : av.y, b10 = CLASS2 ? av.y : av.z, b11 = av.w;
-      mma_m16n8k16(d[mt][0], x00, y00, x01, y01, b00, b01);
-      if constexpr (SP == 0) mma_m16n8k16_init(d[mt][1], x10, y10, x11, y11, b10, b11);
-      else mma_m16n8k16(d[mt][1], x10, y10, x11, y11, b10, b11);
-    }
-    if constexpr (SP < 3) GroupSteps<VAR, MT, CLASS2, SP + 1>::run(w0, w1, a_ptr, kmask, koff, d);
-  }
-};
-
 // Shared-memory layout (byte offsets from the dynamic smem base):
 //   [0, HDR)     mbarriers [warp][stage]   (up to 8 stages of 8 bytes per warp, HDR a multiple of 1 KB)
 //   [HDR, ...)   rings [warp][stage][ITEM_BYTES] of packed weights
@@ -188,12 +150,9 @@ __global__ void __launch_bounds__(stream_warps(MT) * 32, MT == 1 ? 2 : 1) stream
   constexpr int SCG = STREAM_SC_GROUPS;
   constexpr float F = (float)(1u << lin_factor_log2(VAR));
   // Where the linear pattern of a pair sits in the fp16 mantissa (bit T, decode.cuh int_target) sets a
-  // factor 2^T on its products.  8-bit integers and the float types have one T for all pairs.  4-bit
-  // integers have two (T = 0 for even pairs, 4 for odd ones): even and odd pairs go to separate
-  // accumulation chains and the odd chain is scaled by 2^-4 once per group.  Every other width has
-  // more than two, and its activations are pre-multiplied by 2^-T when they are staged.
-  constexpr bool CLASS2 = B200Q_S_CLASS2 && !var_is_float(VAR) && B == 4;
-  constexpr bool PRESCALE = !var_is_float(VAR) && !CLASS2 && B != 8;
+  // factor 2^T on its products; the activations are pre-multiplied by 2^-T when they are staged.
+  // 8-bit integers and the float types have T = 0 for every pair and need no such pass.
+  constexpr bool PRESCALE = !var_is_float(VAR) && B != 8;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const int NST = p.stages;
   const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem_raw);
@@ -496,24 +455,14 @@ __global__ void __launch_bounds__(stream_warps(MT) * 32, MT == 1 ? 2 : 1) stream
           uint32_t w0[B], w1[B];
           ld_unit_words<B>(slot + w_lane + gi * (256 * B), w0);
           ld_unit_words<B>(slot + w_lane + gi * (256 * B) + 128 * B, w1);
-#if !B200Q_S_QUAD
           uint32_t W0[16], W1[16];
           unit_decode_linear<VAR>(w0, W0);
           unit_decode_linear<VAR>(w1, W1);
-#endif
           if (gi == GI - 1) {
-            // every lane holds its copy of the item's last group in registers (the loads have
-            // returned: a shuffle of their values orders them before the copy that lane 0 issues
-            // into the slot)
-            uint32_t dep = w0[0] ^ w1[B - 1];
-            asm volatile("" : "+r"(dep));
+            // every lane has turned its copy of the item's last group into operands (the loads have
+            // returned: their values were used), so lane 0 may ask for the next item into this slot
             __syncwarp();
-            if (lane == 0 && issued < n_items) {
-#if B200Q_S_FENCE
-              asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-#endif
-              issue_next(bar, ring_s + slot_off);
-            }
+            if (lane == 0 && issued < n_items) issue_next(bar, ring_s + slot_off);
           }
           const uint32_t koff = (uint32_t)((g0 + gi) * 320);  // bytes: 128 columns + 4 x 8 of padding per group
           // two accumulation chains per 8-row tile; the first starts from the zero-point term of the group
@@ -524,34 +473,25 @@ __global__ void __launch_bounds__(stream_warps(MT) * 32, MT == 1 ? 2 : 1) stream
             if constexpr (BIAS != 0) nb = nb4[((g0 + gi) * MT + mt) * 4];
             d[mt][0][0] = nb.x; d[mt][0][1] = nb.y; d[mt][0][2] = nb.z; d[mt][0][3] = nb.w;
           }
-#if B200Q_S_QUAD
-          GroupSteps<VAR, MT, CLASS2, 0>::run(w0, w1, a_ptr, kmask, koff, d);
-#else
-          // pairs h = 4*sp .. 4*sp+3 of both units against the same four pairs of activations; with two
-          // mantissa positions (CLASS2) the even pairs feed chain 0 and the odd pairs chain 1
-          constexpr int P01 = CLASS2 ? 2 : 1;  // second pair of chain 0's MMA
-          constexpr int P10 = CLASS2 ? 1 : 2;  // first pair of chain 1's MMA
+          // pairs h = 4*sp .. 4*sp+3 of both units against the same four pairs of activations
 #pragma unroll
           for (int sp = 0; sp < 4; ++sp) {
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
               const uint4 av = *reinterpret_cast<const uint4*>(a_ptr[mt] + (koff & kmask[mt]) + sp * 16);
-              const uint32_t b00 = av.x, b01 = CLASS2 ? av.z : av.y, b10 = CLASS2 ? av.y : av.z, b11 = av.w;
-              mma_m16n8k16(d[mt][0], W0[4 * sp], W1[4 * sp], W0[4 * sp + P01], W1[4 * sp + P01], b00, b01);
+              mma_m16n8k16(d[mt][0], W0[4 * sp], W1[4 * sp], W0[4 * sp + 1], W1[4 * sp + 1], av.x, av.y);
               if (sp == 0)
-                mma_m16n8k16_init(d[mt][1], W0[P10], W1[P10], W0[3], W1[3], b10, b11);
+                mma_m16n8k16_init(d[mt][1], W0[2], W1[2], W0[3], W1[3], av.z, av.w);
               else
-                mma_m16n8k16(d[mt][1], W0[4 * sp + P10], W1[4 * sp + P10], W0[4 * sp + 3], W1[4 * sp + 3], b10, b11);
+                mma_m16n8k16(d[mt][1], W0[4 * sp + 2], W1[4 * sp + 2], W0[4 * sp + 3], W1[4 * sp + 3], av.z, av.w);
             }
           }
-#endif
-          constexpr float C1 = CLASS2 ? 0.0625f : 1.0f;  // chain 1 of a 4-bit type holds 2^4 x its products
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt) {
-            acc[mt][0] = fmaf(sf0[gi], fmaf(d[mt][1][0], C1, d[mt][0][0]), acc[mt][0]);
-            acc[mt][1] = fmaf(sf0[gi], fmaf(d[mt][1][1], C1, d[mt][0][1]), acc[mt][1]);
-            acc[mt][2] = fmaf(sf1[gi], fmaf(d[mt][1][2], C1, d[mt][0][2]), acc[mt][2]);
-            acc[mt][3] = fmaf(sf1[gi], fmaf(d[mt][1][3], C1, d[mt][0][3]), acc[mt][3]);
+            acc[mt][0] = fmaf(sf0[gi], d[mt][0][0] + d[mt][1][0], acc[mt][0]);
+            acc[mt][1] = fmaf(sf0[gi], d[mt][0][1] + d[mt][1][1], acc[mt][1]);
+            acc[mt][2] = fmaf(sf1[gi], d[mt][0][2] + d[mt][1][2], acc[mt][2]);
+            acc[mt][3] = fmaf(sf1[gi], d[mt][0][3] + d[mt][1][3], acc[mt][3]);
           }
         }
         slot_off += SLOT_BYTES; bar += 8;

@@ -47,10 +47,6 @@
 
 namespace b200q {
 
-#ifndef B200Q_EPI_EARLY
-#define B200Q_EPI_EARLY 1
-#endif
-
 constexpr int UMMA_THREADS = 608;   // 8 dequant warps, 8 epilogue warps, 2 producers, MMA warp
 constexpr int UMMA_SA_MAX = 6;      // activation stages (most)
 constexpr int UMMA_SW = 8;          // weight stages in tensor memory (32 columns each)
@@ -205,13 +201,16 @@ umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
     const uint32_t daddr = tmem + ((uint32_t)(ew * 32) << 16);
     int tile_it = 0;
     bool good = true;
+    // with several tiles per CTA the accumulator is handed back before the stores (the next tile's
+    // MMAs run under them); a CTA with a single tile has nothing to overlap and takes the shorter path
+    const bool early_handback = p.splits == 1 && total_tiles > (int)gridDim.x;
     for (int t = blockIdx.x; t < total_tiles && good; t += gridDim.x, ++tile_it) {
       TILE_COORDS(t)
       const int n = n_tile * 128 + nl;
       const bool nvalid = n < p.N;
       if (!mbar_wait_abortable(BAR_ADDR(d_full, 0), (uint32_t)tile_it & 1u, abort_flag)) { good = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      if (p.splits == 1 && B200Q_EPI_EARLY) {
+      if (early_handback) {
         // Lane l holds column n of the tile, one accumulator row per tensor-memory column.  All of this
         // warp's 32-row chunks are read and rounded to the output dtype first (two rows per register)
         // and D is handed back at once, so that the next tile's MMAs run under the transposition and
