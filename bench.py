@@ -318,12 +318,15 @@ def measure_stack(world, rank, dev, steps, warmup, batches=(1, 8, 32, 64)) -> di
     n_layers = 32
     protos, probs = {}, {}
     for name, k_in, n_out in shapes:  # one synthetic weight per shape, one device copy per layer
-        # scales around 1 / (sqrt(K) * std(q - 8)): every linear keeps the activations' magnitude, so
-        # the values stay finite through all 128 of them and the comparisons below mean something
-        # (uniform codes with the benchmark's U(0.005, 0.02) scales grow ~4x per layer and overflow
-        # fp16 within a few blocks; the timing does not depend on the values)
-        s_mean = 1.0 / (k_in ** 0.5 * 4.61)
+        # Values chosen so that the activations keep their magnitude through all 128 linears and the
+        # comparisons below mean something: codes uniform in 1..15 (zero mean after the zero point 8;
+        # uniform 0..15 has mean -0.5, a common mode that grows ~7x per layer) and scales around
+        # 1 / (sqrt(K) * std(q - 8)).  The benchmark's own U(0.005, 0.02) scales overflow fp16 within a
+        # few blocks; the timing does not depend on the values.
+        s_mean = 1.0 / (k_in ** 0.5 * 4.32)
         prob = synth.make_problem(1, n_out, k_in, dt, GROUP, seed=7, scale_range=(0.75 * s_mean, 1.25 * s_mean))
+        prob["codes"] = torch.randint(1, 16, (k_in, n_out), generator=torch.Generator().manual_seed(11),
+                                      dtype=torch.int32).to(torch.uint8)
         probs[name] = prob
         n0, n1 = sharded.shard_range(n_out, world, rank)
         protos[name] = (packing.interleave(prob["codes"][:, n0:n1].contiguous().to(dev), dt),
