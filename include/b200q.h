@@ -145,21 +145,19 @@ size_t b200q_static_workspace_limit(void);
  * b200q_gemm_gather computes this rank's columns like b200q_gemm (M <= 16; workspace of
  * b200q_workspace_bytes for the same problem) and stores them straight
  * into the full output row [M, ldc] of every rank (peer-mapped device pointers; stores only, no
- * loads from peers).  Every rank owns two row buffers used alternately (`out[g]` = buffer 0 of
- * rank g, buffer 1 is `buffer_elems` elements further), `world` 32-bit arrival counters
- * (`flags_local`; slot g counts the CTAs of rank g's fused launches that have delivered their
- * columns here) and a call counter `epoch_local`, all zero at the start.  A launch is fused call
- * number E + 1 of its rank, with E read from `epoch_local` on the device.  It waits - bounded,
- * 0.25 s, else B200Q_ERR_DEVICE_TIMEOUT in the status word - until every slot of `flags_local`
- * has reached this rank's own slot (all ranks launch the same grids, so that is the count of all
- * CTAs of calls 1..E: the activations are complete and nobody still reads the buffer about to be
- * overwritten), writes buffer (E + 1) % 2 of every rank; each CTA then adds one to
- * `flag_slot[g]` (= this rank's slot in rank g's counters) for every g, and the launch's last CTA
- * stores E + 1 to `epoch_local`.  With `a_prev_offset >= 0` the activations are this rank's
- * previous gathered output (buffer E % 2, from that element on, row stride lda) and `a` is
- * ignored.  No per-call state is passed from the host, so the same call sequence can be captured
- * once and replayed from a CUDA graph.  All ranks must make the same sequence of calls with the
- * same shapes.  Word 8 of the workspace header counts the CTAs of the launch. */
+ * loads from peers), then raises this rank's flag on every rank.  Every rank owns two row
+ * buffers used alternately (`out[g]` = buffer 0 of rank g, buffer 1 is `buffer_elems` elements
+ * further), `world` 32-bit flags and a call counter `epoch_local`, all zero at the start.  A
+ * launch is fused call number E + 1 of its rank, with E read from `epoch_local` on the device:
+ * it waits - bounded, 0.25 s, else B200Q_ERR_DEVICE_TIMEOUT in the status word - until all
+ * `world` slots of `flags_local` have reached E (every rank has finished call E, so the
+ * activations are complete and nobody still reads the buffer about to be overwritten), writes
+ * buffer (E + 1) % 2 of every rank, sets `flag_slot[g]` (= this rank's slot in rank g's flags) to
+ * E + 1 and stores E + 1 to `epoch_local`.  With `a_prev_offset >= 0` the activations are this
+ * rank's previous gathered output (buffer E % 2, from that element on, row stride lda) and `a`
+ * is ignored.  No per-call state is passed from the host, so the same call sequence can be
+ * captured once and replayed from a CUDA graph.  All ranks must make the same sequence of calls.
+ * Word 8 of the workspace header counts the CTAs of the launch. */
 typedef struct b200q_gather {
   int32_t world, rank;
   int32_t ldc;            /* elements per full output row */

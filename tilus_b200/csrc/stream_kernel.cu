@@ -281,30 +281,27 @@ __global__ void __launch_bounds__(stream_warps(MT) * 32, MT == 1 ? 2 : 1) stream
   size_t gather_buf = 0;  // element offset of the row buffer this call writes, inside every rank's region
   unsigned epoch = 0;
   if (GATHER) {
-    // Flag slot g of a rank counts the CTAs of rank g's fused launches that have delivered their
-    // columns here (every CTA of every rank adds one to its slot on every rank when its stores are
-    // out).  All ranks launch the same grids, so this rank's own slot - complete once its previous
-    // kernel is, which the wait above has established - is the count every slot must have reached
-    // before this call may read the gathered activations or overwrite the other row buffer.
-    __shared__ unsigned s_expected;
+    // The rank's own flag slot holds the number of its completed fused calls (its last CTA raises it
+    // with the others), so one round of loads brings both the epoch and the peers' progress.
+    __shared__ unsigned s_epoch_word;
+    unsigned* s_epoch = &s_epoch_word;
     unsigned mine = 0;
     if (tid < p.ga.G) {
-      asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(mine) : "l"(p.ga.flags + tid) : "memory");
-      if (tid == p.ga.rank) s_expected = mine;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(mine) : "l"(p.ga.flags + tid) : "memory");
+      if (tid == p.ga.rank) *s_epoch = mine;
     }
     __syncthreads();
-    const unsigned expected = s_expected;
-    epoch = *reinterpret_cast<volatile const unsigned*>(p.ga.epoch);  // fused calls completed (moved on by the last CTA of each)
+    epoch = *s_epoch;
     gather_buf = ((epoch + 1) & 1u) ? p.ga.buf_elems : 0;
     if (p.ga.a_prev_off >= 0)
       a_base = reinterpret_cast<const unsigned short*>(p.ga.out[p.ga.rank]) + ((epoch & 1u) ? p.ga.buf_elems : 0) + p.ga.a_prev_off;
-    if (tid < p.ga.G) {
-      if ((int)(mine - expected) < 0) {  // a peer's CTAs are still out: bounded wait
+    if (epoch != 0) {
+      if (tid < p.ga.G && (int)(mine - epoch) < 0) {  // a peer has not finished call `epoch` yet: bounded wait
         uint64_t t0 = 0;
         for (int spin = 0;; ++spin) {
           unsigned v;
-          asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.ga.flags + tid) : "memory");
-          if ((int)(v - expected) >= 0) break;
+          asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.ga.flags + tid) : "memory");
+          if ((int)(v - epoch) >= 0) break;
           uint64_t now;
           asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
           if (spin == 0) t0 = now;
@@ -317,10 +314,8 @@ __global__ void __launch_bounds__(stream_warps(MT) * 32, MT == 1 ? 2 : 1) stream
           }
         }
       }
-      // acquire at system scope what the counted CTAs released before they added themselves
-      asm volatile("fence.acq_rel.sys;" ::: "memory");
+      __syncthreads();
     }
-    __syncthreads();
   }
 
   // ---- stage the activation chunk A[0:M, kb_base*512 : +KBc*512] as fp16 (pre-scaled where the
@@ -624,21 +619,23 @@ __global__ void __launch_bounds__(stream_warps(MT) * 32, MT == 1 ? 2 : 1) stream
     }
   }
 
-  // ---- fused all-gather: every CTA tells every rank that its share of this rank's columns of the
-  // output row is in place (no CTA waits for another one of its launch) ----
+  // ---- fused all-gather: the last CTA of the launch tells every rank that this rank's columns
+  // of the output row are in place.  Every CTA orders its stores before its arrival at GPU scope;
+  // the last arriver, which has observed all arrivals, releases at system scope: by cumulativity
+  // every CTA's stores are visible to whoever acquires the flag. ----
   if (GATHER) {
     __syncthreads();
     if (tid == 0) {
-      // release at system scope what this CTA's threads stored to the peers (ordered before by the
-      // barrier), then count this CTA in on every rank
-      asm volatile("fence.acq_rel.sys;" ::: "memory");
-      for (int g = 0; g < p.ga.G; ++g)
-        asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(p.ga.flag_slot[g]) : "memory");
-      // the call counter (row buffer parity; read by this rank's next fused launch once this one has
-      // completed, and by the host) moves on when the last CTA of the launch has read it
-      if (atomicAdd(p.ga.done, 1u) == gridDim.x - 1) {
+      // release at GPU scope what this CTA's threads stored (ordered before by the barrier), acquire
+      // what the CTAs that arrived earlier released
+      unsigned arrived;
+      asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(arrived) : "l"(p.ga.done) : "memory");
+      if (arrived == gridDim.x - 1) {
         atomicExch(p.ga.done, 0u);
-        *p.ga.epoch = epoch + 1;
+        asm volatile("fence.acq_rel.sys;" ::: "memory");  // one system-scope fence, then plain flag stores
+        for (int g = 0; g < p.ga.G; ++g)
+          asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p.ga.flag_slot[g]), "r"(epoch + 1) : "memory");
+        *p.ga.epoch = epoch + 1;  // for the host (PeerGather.calls_completed)
       }
     }
   }

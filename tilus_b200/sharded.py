@@ -114,13 +114,13 @@ class PeerGather:
     """Peer-mapped output rows and arrival flags for the fused all-gather of a column-sharded
     decode stack (include/b200q.h, b200q_gemm_gather).
 
-    Every rank owns one region: `world` 32-bit arrival counters ("flags"), a call counter, and two
-    16-bit row buffers [max_rows, max_cols] used alternately.  `ptrs[g]` is rank g's region as seen
-    from this process.  A fused call waits (on the device) until every rank's CTAs of the previous
-    call have delivered their columns, writes its own columns into the other row buffer of every
-    rank, and each of its CTAs counts itself in on every rank; the counters live on the device, so
-    the calls carry no per-call state and a sequence of them can be captured in a CUDA graph and
-    replayed.  All ranks must make the same sequence of calls (same shapes, hence same grids).
+    Every rank owns one region: `world` 32-bit flags, a call counter, and two fp16 row buffers
+    [max_rows, max_cols] used alternately.  `ptrs[g]` is rank g's region as seen from this
+    process.  A fused call waits (on the device) until every rank has finished the previous
+    call, writes its columns into the other row buffer of every rank and raises its flag on
+    every rank; the call counter lives on the device, so the calls carry no per-call state and
+    a sequence of them can be captured in a CUDA graph and replayed.  All ranks must make the
+    same sequence of calls.
     """
 
     FLAGS_OFF, EPOCH_OFF, ROWS_OFF = 0, 64, 256
@@ -230,9 +230,8 @@ class PeerGather:
 
     def wait_all_ranks(self, timeout_s: float = 2.0) -> int:
         """Waits until every rank's columns of this rank's latest call have landed here: this rank's
-        own stream is synchronised, then its flag words are polled (bounded).  Slot g counts the CTAs
-        of rank g's fused launches that have delivered their columns; all ranks launch the same grids,
-        so every slot must reach this rank's own count.  Returns the number of completed calls."""
+        own stream is synchronised, then its flag words - one per source rank, raised over NVLink by
+        that rank's kernel - are polled until all have reached the call counter (bounded)."""
         import time
 
         epoch = self.calls_completed()
@@ -240,11 +239,10 @@ class PeerGather:
         t0 = time.perf_counter()
         while True:
             seen = flags.cpu()
-            if bool(((seen - seen[self.rank]) >= 0).all()):
+            if bool(((seen - epoch) >= 0).all()):
                 return epoch
             if time.perf_counter() - t0 > timeout_s:
-                raise _lib.B200QError(_lib.ST_DEVICE_TIMEOUT,
-                                      f"fused gather: flags {seen.tolist()} never reached this rank's own count")
+                raise _lib.B200QError(_lib.ST_DEVICE_TIMEOUT, f"fused gather: flags {seen.tolist()} never reached call {epoch}")
             time.sleep(0.0005)
 
     def fetch(self, row: GatheredRow) -> torch.Tensor:
