@@ -152,6 +152,29 @@ def test_umma_kernel_forced_split_k_and_clean_workspace(M, N, K, splits):
                                       ctas_per_split=m_tiles * n_tiles), seed=13)
 
 
+@pytest.mark.parametrize("small_ws", [False, True])
+def test_umma_kernel_last_round_split_along_k(small_ws):
+    """160 tiles on 148 persistent CTAs: the 12 tiles of the last round are cut into K ranges whose
+    partial sums meet in the fp32 scratch (left zeroed).  With a workspace too small for that scratch
+    the kernel takes whole tiles instead; both must agree with the oracle."""
+    dev = _dev()
+    M, N, K, dt = 512, 10240, 2048, D.int4b
+    prob = synth.make_problem(M, N, K, dt, 128, seed=9)
+    assert ops.plan(M, N, K, dt, 0, 128)["kernel"] == 1
+    need = ops.workspace_bytes(M, N, K, dt, 0, 128)
+    assert need > (1 << 20)  # room for 12 tile slabs of 256 x 128 fp32
+    ws = torch.zeros(4096 if small_ws else need, dtype=torch.uint8, device=dev)
+    bq = packing.interleave(prob["codes"], dt).to(dev)
+    c = ops.quantized_matmul(prob["a"].to(dev), bq, prob["scales"].to(dev), dt, 128, 0, workspace=ws)
+    torch.cuda.synchronize()
+    assert int(ws.count_nonzero()) == 0, "workspace not restored to zero"
+    ref = qo.quantized_matmul(prob["a"].numpy(), prob["codes"].numpy(), prob["scales"].numpy(), dt, 128, 0)
+    got = c.cpu().numpy()
+    assert _rel_err(got, ref) <= REL_TOL
+    for n0 in range(0, N, 1024):  # the cut tiles are the last ones in raster order: look at every column range
+        assert _rel_err(got[:, n0:n0 + 1024], ref[:, n0:n0 + 1024]) <= REL_TOL, n0
+
+
 @pytest.mark.parametrize("M", [512, 4096, 4097])
 def test_umma_kernel_many_row_tiles(M):
     """The persistent tile walk of the prefill kernel with more than one row tile, more tiles than

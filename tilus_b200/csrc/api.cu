@@ -33,11 +33,11 @@ B200Q_DECL_UPART(4) B200Q_DECL_UPART(5) B200Q_DECL_UPART(6) B200Q_DECL_UPART(7)
   cudaError_t wide_launch_part##i(int, const WideParams&, const void*, int, cudaStream_t);
 B200Q_DECL_WPART(0) B200Q_DECL_WPART(1) B200Q_DECL_WPART(2) B200Q_DECL_WPART(3)
 B200Q_DECL_WPART(4) B200Q_DECL_WPART(5) B200Q_DECL_WPART(6) B200Q_DECL_WPART(7)
-int wide_smem_bytes(int bits, int wg_stages, int a_rows);
-int wide_wg_stages(int bits, int max_smem, int a_rows);
+int wide_smem_bytes(int bits, int wg_stages, int a_rows, int rpg);
+int wide_wg_stages(int bits, int max_smem, int a_rows, int rpg);
 int wide_a_rows(int M);
-int umma_smem_bytes(int tm, int bits, int a_stages);
-int umma_a_stages(int tm, int bits, int max_smem);
+int umma_smem_bytes(int tm, int bits, int a_stages, int rpg);
+int umma_a_stages(int tm, int bits, int max_smem, int rpg);
 
 static thread_local int g_last_cuda_error = 0;
 
@@ -254,7 +254,9 @@ static int gshift_of(int group) {  // log2(group / 128) when that is a power of 
 }
 
 // tcgen05 kernel: tile rows, tiles and split-K so that the grid fills the SMs
-static void plan_umma(int M, int N, int K, int bits, const DeviceInfo& di, b200q_plan_t* pl) {
+static int rpg_of(int group) { return group < 128 ? 128 / group : 1; }
+
+static void plan_umma(int M, int N, int K, int bits, int group, const DeviceInfo& di, b200q_plan_t* pl) {
   const int tm = M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
   const int m_tiles = (M + tm - 1) / tm, n_tiles = (N + 127) / 128;
   const int ctas = m_tiles * n_tiles;
@@ -269,8 +271,8 @@ static void plan_umma(int M, int N, int K, int bits, const DeviceInfo& di, b200q
   pl->splits = splits;
   pl->cluster = 1;
   pl->ctas_per_split = ctas;
-  pl->stages = umma_a_stages(tm, bits, di.max_smem);
-  pl->smem_bytes = umma_smem_bytes(tm, bits, pl->stages);
+  pl->stages = umma_a_stages(tm, bits, di.max_smem, rpg_of(group));
+  pl->smem_bytes = umma_smem_bytes(tm, bits, pl->stages, rpg_of(group));
   pl->tile_m = tm;
   pl->warps = 19;
   pl->passes = 1;
@@ -279,7 +281,7 @@ static void plan_umma(int M, int N, int K, int bits, const DeviceInfo& di, b200q
 
 // wide tcgen05 kernel (kernel 3): 128-row x 256-column tiles, split-K while the tiles do not fill the SMs
 static const int kWideMaxRows = 128;
-static void plan_wide(int M, int N, int K, int bits, const DeviceInfo& di, b200q_plan_t* pl) {
+static void plan_wide(int M, int N, int K, int bits, int group, const DeviceInfo& di, b200q_plan_t* pl) {
   const int m_tiles = (M + 127) / 128, n_tiles = (N + 255) / 256;
   const int tiles = m_tiles * n_tiles, G = K / 128;
   int splits = 1;
@@ -290,13 +292,32 @@ static void plan_wide(int M, int N, int K, int bits, const DeviceInfo& di, b200q
   pl->splits = splits;
   pl->cluster = 1;
   pl->ctas_per_split = tiles;
-  pl->stages = wide_wg_stages(bits, di.max_smem, wide_a_rows(M));
-  pl->smem_bytes = wide_smem_bytes(bits, pl->stages, wide_a_rows(M));
+  pl->stages = wide_wg_stages(bits, di.max_smem, wide_a_rows(M), rpg_of(group));
+  pl->smem_bytes = wide_smem_bytes(bits, pl->stages, wide_a_rows(M), rpg_of(group));
   pl->tile_m = 128;
   pl->warps = 23;
   pl->passes = 1;
   pl->pdl = 0;
 }
+
+// The persistent CTAs of the transposed tcgen05 kernel take tiles round by round.  When the last round
+// would be less than half full, its tiles are cut into `splits` K ranges (whole 128-row groups, at
+// least 8 64-row blocks each) so that the round costs a fraction of a tile's time.  Returns the number
+// of such tail tiles (0: none).
+static int umma_tail(int tiles, int grid, int kblocks, int uniform_splits, int N, int* splits) {
+  *splits = 1;
+  if (uniform_splits != 1 || tiles <= grid) return 0;
+  const int rem = tiles % grid;
+  if (rem == 0 || rem * 2 > grid || rem > N / BLOCK_N) return 0;
+  int best = 1;
+  for (int s = 2; s <= 16; s *= 2)
+    if (s * rem <= grid && kblocks % (2 * s) == 0 && kblocks / s >= 8) best = s;
+  if (best == 1) return 0;
+  *splits = best;
+  return rem;
+}
+// fp32 scratch of the transposed tcgen05 kernel: one [tm][128] slab per tile slot
+static size_t umma_partial_bytes(int slots, int tm) { return (size_t)slots * tm * 128 * sizeof(float); }
 
 static int make_plan(int M, int N, int K, int var, int group, b200q_plan_t* pl) {
   const DeviceInfo di = device_info();
@@ -313,7 +334,7 @@ static int make_plan(int M, int N, int K, int var, int group, b200q_plan_t* pl) 
   }
   // a few dozen rows: weights on the wide side of the MMA; beyond, the transposed prefill kernel
   if (M <= kWideMaxRows) {
-    plan_wide(M, N, K, bits, di, pl);
+    plan_wide(M, N, K, bits, group, di, pl);
   } else {
     // A last row tile of at most 16 rows (M = 4097: one row) would cost a whole 256-row tile per
     // column tile; those rows go to the decode kernel in a second launch instead (passes = 2).
@@ -321,13 +342,21 @@ static int make_plan(int M, int N, int K, int var, int group, b200q_plan_t* pl) 
     b200q_plan_t tail_plan;
     if (M > 256 && tail >= 1 && tail <= kStreamMaxRows && stream_takes(K, group) &&
         plan_stream(tail, N, K, bits, di, &tail_plan) == ST_OK) {
-      plan_umma(M - tail, N, K, bits, di, pl);
+      plan_umma(M - tail, N, K, bits, group, di, pl);
       pl->passes = 2;
     } else {
-      plan_umma(M, N, K, bits, di, pl);
+      plan_umma(M, N, K, bits, group, di, pl);
     }
   }
-  const size_t part = pl->splits > 1 ? (size_t)M * N * sizeof(float) : 0;
+  size_t part = pl->splits > 1 ? (size_t)M * N * sizeof(float) : 0;
+  if (pl->kernel == 1) {  // fp32 slabs per tile slot: every tile of a split-K launch, or the cut tiles of the last round
+    const int Mu = pl->passes == 2 ? M - M % 256 : M;
+    const int tiles = ((Mu + pl->tile_m - 1) / pl->tile_m) * ((N + 127) / 128);
+    const int grid = tiles * pl->splits < di.sm_count ? tiles * pl->splits : di.sm_count;
+    int tail_splits;
+    const int tail = umma_tail(tiles, grid, K / 64, pl->splits, N, &tail_splits);
+    part = umma_partial_bytes(pl->splits > 1 ? tiles : tail, pl->tile_m);
+  }
   size_t need = WS_HEADER_BYTES + ws_counter_bytes(N) + part;
   if (pl->passes == 2 && need < stream_workspace_bytes(N)) need = stream_workspace_bytes(N);
   pl->workspace_bytes = need;
@@ -355,8 +384,17 @@ static int run_umma(const void* a, int lda, const void* bq, const void* scales, 
   if (pl.splits > 1 && m_tiles * n_tiles > N / BLOCK_N) return ST_INVALID_ARG;  // counters region
   if ((ldc % 8) != 0 || (((uintptr_t)scales) & 15)) return ST_INVALID_ARG;  // 16-byte stores, bulk-copied scale rows
   const int bits = var_bits(var);
-  const int a_stages = umma_a_stages(tm, bits, device_info().max_smem);
-  const size_t need = WS_HEADER_BYTES + ws_counter_bytes(N) + (pl.splits > 1 ? (size_t)M * N * sizeof(float) : 0);
+  const int a_stages = umma_a_stages(tm, bits, device_info().max_smem, rpg_of(group));
+  const int all_tiles = m_tiles * n_tiles;
+  const int grid = pl.splits * all_tiles < device_info().sm_count ? pl.splits * all_tiles : device_info().sm_count;
+  int tail_splits = 1;
+  int tail_tiles = umma_tail(all_tiles, grid, kblocks, pl.splits, N, &tail_splits);
+  size_t need = WS_HEADER_BYTES + ws_counter_bytes(N) + umma_partial_bytes(pl.splits > 1 ? all_tiles : tail_tiles, tm);
+  if (tail_tiles > 0 && workspace && ws_bytes < need) {  // a caller with a smaller workspace: whole tiles only
+    tail_tiles = 0;
+    tail_splits = 1;
+    need = WS_HEADER_BYTES + ws_counter_bytes(N);
+  }
   if (!workspace || ws_bytes < need || ((uintptr_t)workspace & 255)) return ST_WORKSPACE;
   EncodeTiledFn enc = encode_tiled_fn();
   if (!enc) return ST_CUDA;
@@ -378,15 +416,16 @@ static int run_umma(const void* a, int lda, const void* bq, const void* scales, 
   p.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + WS_HEADER_BYTES + ws_counter_bytes(N));
   p.M = M; p.N = N; p.K = K; p.G = K / 128; p.ldc = ldc;
   p.group = group;
-  p.rpg = group < 128 ? 128 / group : 1;
+  p.rpg = rpg_of(group);
   p.tm = tm; p.m_tiles = m_tiles; p.n_tiles = n_tiles;
   p.splits = pl.splits; p.kblocks_per_split = kblocks / pl.splits;
+  p.tail_tiles = tail_tiles; p.tail_splits = tail_tiles > 0 ? tail_splits : 0;
+  p.tail_kblocks = tail_tiles > 0 ? kblocks / tail_splits : 0;
   p.a_stages = a_stages;
   p.m_group = umma_m_group(tm, K, m_tiles);
   p.act = act;
-  const int tiles = pl.splits * m_tiles * n_tiles;
-  p.grid = tiles < device_info().sm_count ? tiles : device_info().sm_count;
-  const int smem = umma_smem_bytes(tm, bits, a_stages);
+  p.grid = grid;
+  const int smem = umma_smem_bytes(tm, bits, a_stages, rpg_of(group));
   if (smem > device_info().max_smem) return ST_UNSUPPORTED;
   cudaError_t e = umma_launch(var, p, &tmap, smem, stream);
   if (e != cudaSuccess) { g_last_cuda_error = (int)e; return ST_CUDA; }
@@ -423,15 +462,15 @@ static int run_wide(const void* a, int lda, const void* bq, const void* scales, 
   p.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + WS_HEADER_BYTES + ws_counter_bytes(N));
   p.M = M; p.N = N; p.K = K; p.G = K / 128; p.ldc = ldc;
   p.group = group;
-  p.rpg = group < 128 ? 128 / group : 1;
+  p.rpg = rpg_of(group);
   p.m_tiles = m_tiles; p.n_tiles = n_tiles;
   p.splits = pl.splits; p.kblocks_per_split = 2 * G / pl.splits;
   p.a_rows = a_rows;
   p.act = act;
-  p.wg_stages = wide_wg_stages(bits, device_info().max_smem, a_rows);
+  p.wg_stages = wide_wg_stages(bits, device_info().max_smem, a_rows, rpg_of(group));
   const int items = pl.splits * m_tiles * n_tiles;
   p.grid = items < device_info().sm_count ? items : device_info().sm_count;
-  const int smem = wide_smem_bytes(bits, p.wg_stages, a_rows);
+  const int smem = wide_smem_bytes(bits, p.wg_stages, a_rows, rpg_of(group));
   if (smem > device_info().max_smem) return ST_UNSUPPORTED;
   cudaError_t e = wide_launch(var, p, &tmap, smem, stream);
   if (e != cudaSuccess) { g_last_cuda_error = (int)e; return ST_CUDA; }
@@ -747,7 +786,12 @@ int b200q_gemm_static_ws(const void* a, int lda, const void* bq, const void* sca
   b200q_plan_t pl;
   st = make_plan(M, N, K, var, group, &pl);
   if (st != ST_OK) return st;
-  if (pl.workspace_bytes > (uint64_t)B200Q_STATIC_WS_BYTES) return ST_WORKSPACE;  // beyond the built-in scratch
+  if (pl.workspace_bytes > (uint64_t)B200Q_STATIC_WS_BYTES) {
+    // beyond the built-in scratch - unless all that asks for the room is the optional K split of the
+    // prefill kernel's last round, which the kernel does without when the scratch is too small
+    const uint64_t without_tail = pl.passes == 2 ? stream_workspace_bytes(N) : WS_HEADER_BYTES + ws_counter_bytes(N);
+    if (!(pl.kernel == 1 && pl.splits == 1 && without_tail <= (uint64_t)B200Q_STATIC_WS_BYTES)) return ST_WORKSPACE;
+  }
   void* ws = nullptr;
   st = static_ws_pointer(&ws);
   if (st != ST_OK) return st;

@@ -86,8 +86,8 @@ struct UmmaParams {
   const uint4* bq;       // b200 layout
   const __half* scales;  // [K/group, N]
   __half* c;             // [M, N], leading dimension ldc
-  float* partial;        // [M, N] fp32 split-K scratch, zero on entry and on exit
-  int* counters;         // [n_tiles * m_tiles], zero on entry and on exit
+  float* partial;        // fp32 split-K scratch [tile slot][tm rows][128 columns], zero on entry and on exit
+  int* counters;         // one per tile slot, zero on entry and on exit
   int* status;           // workspace status header
   int M, N, K, G;        // G = K / 128
   int ldc;
@@ -97,6 +97,9 @@ struct UmmaParams {
   int m_tiles, n_tiles;  // ceil(M / tm), ceil(N / 128)
   int splits;            // split-K factor
   int kblocks_per_split; // 64-row k blocks per tile (even)
+  int tail_tiles;        // the last tail_tiles tiles (raster order) are cut into tail_splits K ranges of
+  int tail_splits;       // tail_kblocks 64-row blocks each (0 / 1 / all of K: no tail)
+  int tail_kblocks;
   int a_stages;          // activation stages in shared memory
   int grid;              // persistent CTAs: min(tiles, SMs)
   int m_group;           // row tiles per raster group: tiles of m_group row tiles x all column tiles run together

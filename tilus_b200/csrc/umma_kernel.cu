@@ -64,14 +64,14 @@ struct UmmaBarriers {
   int last_flag;
 };
 
-// a ring stage: the packed weights of 128 columns x 128 rows, then up to four rows of 128 scales
-__host__ __device__ constexpr int umma_wstage_bytes(int bits) { return 2048 * bits + 1024; }
+// a ring stage: the packed weights of 128 columns x 128 rows, then rpg (1, 2 or 4) rows of 128 scales
+__host__ __device__ constexpr int umma_wstage_bytes(int bits, int rpg) { return 2048 * bits + 256 * rpg; }
 
 template <int VAR, int ACT>
 __global__ void __launch_bounds__(UMMA_THREADS, 1)
 umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
   constexpr int B = var_bits(VAR);
-  constexpr uint32_t WSTAGE = (uint32_t)umma_wstage_bytes(B);
+  const uint32_t WSTAGE = (uint32_t)umma_wstage_bytes(B, p.rpg);
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // [0, SA * TM * 128): activation stages (1024-byte aligned for the 128-byte swizzle: aligned
   // by hand), then the weight ring, then the barriers
@@ -88,9 +88,13 @@ umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
 #define BAR_ADDR(field, i) (bars_s + (uint32_t)offsetof(UmmaBarriers, field) + (uint32_t)(i) * 8u)
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int total_tiles = p.splits * p.n_tiles * p.m_tiles;
-  const int nkk = p.kblocks_per_split;  // 64-blocks per tile (even)
-  const int ngrp = nkk >> 1;            // 128-row groups per tile
+  // Work items.  The first splits * main_tiles items are the tiles 0 .. main_tiles-1 (raster order),
+  // each over 1/splits of K.  The last tail_tiles tiles - what would be a thinly filled last round of
+  // the persistent CTAs - are cut into tail_splits K ranges each, so that the round takes a fraction
+  // of a tile's time; their partial sums meet in the fp32 scratch like any split-K tile.
+  const int main_tiles = p.m_tiles * p.n_tiles - p.tail_tiles;
+  const int main_items = p.splits * main_tiles;
+  const int total_tiles = main_items + p.tail_splits * p.tail_tiles;  // work items of the launch
   volatile int* abort_flag = &bars->abort_flag;
 
   if (tid == 0) {
@@ -121,11 +125,16 @@ umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
   // together share weight columns and the activation rows of one group stay in L2 while the weights
   // stream past them.  The last group holds the m_tiles % MG left-over row tiles.
   const int MG = p.m_group;
-  const int tiles_per_split = p.m_tiles * p.n_tiles;
   const int full_group_tiles = (p.m_tiles / MG) * MG * p.n_tiles;
 #define TILE_COORDS(t)                                                        \
-  const int split = (t) / tiles_per_split;                                    \
-  const int t_in = (t) - split * tiles_per_split;                             \
+  const bool in_tail = (t) >= main_items;                                     \
+  const int t_rel = in_tail ? (t) - main_items : (t);                         \
+  const int per = in_tail ? p.tail_tiles : main_tiles;                        \
+  const int split = t_rel / per;                                              \
+  const int t_in = t_rel - split * per + (in_tail ? main_tiles : 0);          \
+  const int nkk = in_tail ? p.tail_kblocks : p.kblocks_per_split;             \
+  const int ngrp = nkk >> 1;                                                  \
+  const bool splitk = in_tail || p.splits > 1;                                \
   const bool in_full = t_in < full_group_tiles;                               \
   const int gsz = in_full ? MG : p.m_tiles % MG;                              \
   const int t_g = in_full ? t_in : t_in - full_group_tiles;                   \
@@ -133,9 +142,10 @@ umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
   const int t_w = in_full ? t_g - grp_i * (MG * p.n_tiles) : t_g;             \
   const int n_tile = t_w / gsz;                                               \
   const int m_tile = grp_i * MG + (t_w - n_tile * gsz);                       \
+  const int slot = in_tail ? t_in - main_tiles : n_tile * p.m_tiles + m_tile; \
   const int kk0 = split * nkk;                                                \
   const int m0 = m_tile * TM;                                                 \
-  (void)m_tile; (void)n_tile; (void)split; (void)kk0; (void)m0;
+  (void)m_tile; (void)n_tile; (void)split; (void)kk0; (void)m0; (void)ngrp; (void)splitk; (void)slot;
 
   if (warp < 8) {
     // ================= dequantize: shared-memory ring -> registers -> tensor memory =================
@@ -203,14 +213,14 @@ umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
     bool good = true;
     // with several tiles per CTA the accumulator is handed back before the stores (the next tile's
     // MMAs run under them); a CTA with a single tile has nothing to overlap and takes the shorter path
-    const bool early_handback = p.splits == 1 && total_tiles > (int)gridDim.x;
+    const bool many_items = total_tiles > (int)gridDim.x;
     for (int t = blockIdx.x; t < total_tiles && good; t += gridDim.x, ++tile_it) {
       TILE_COORDS(t)
       const int n = n_tile * 128 + nl;
       const bool nvalid = n < p.N;
       if (!mbar_wait_abortable(BAR_ADDR(d_full, 0), (uint32_t)tile_it & 1u, abort_flag)) { good = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      if (early_handback) {
+      if (!splitk && many_items) {
         // Lane l holds column n of the tile, one accumulator row per tensor-memory column.  All of this
         // warp's 32-row chunks are read and rounded to the output dtype first (two rows per register)
         // and D is handed back at once, so that the next tile's MMAs run under the transposition and
@@ -286,7 +296,7 @@ umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
             __syncwarp();
             if (lane == 0) mbar_arrive(BAR_ADDR(d_empty, 0));
           }
-          if (m0 + c0 < p.M && p.splits == 1) {
+          if (m0 + c0 < p.M && !splitk) {
             const bool b0 = lane & 1, b1 = lane & 2, b2 = lane & 4;
             uint32_t h[16];
 #pragma unroll
@@ -327,27 +337,31 @@ umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
               const uint32_t give = odd ? v[q] : v[q + 1];      // row q + !odd, own column
               const uint32_t got = __shfl_xor_sync(0xffffffffu, give, 1);  // row q + odd, the other column
               const float lo = __uint_as_float(odd ? got : mine), hi = __uint_as_float(odd ? mine : got);
-              const int m = m0 + c0 + q + (odd ? 1 : 0);
+              const int mr = c0 + q + (odd ? 1 : 0);  // row inside the tile
               const int ne = n & ~1;
-              if (m < p.M && ne < p.N) red_add_v2(p.partial + (size_t)m * p.N + ne, lo, hi);
+              if (m0 + mr < p.M && ne < p.N)
+                red_add_v2(p.partial + ((size_t)slot * TM + mr) * 128 + (nl & ~1), lo, hi);
             }
           }
         }
       }
       (void)nvalid;
-      if (p.splits > 1) {
-        // the last split to arrive converts the fp32 sums and restores the zeros
+      if (splitk) {
+        // the last K range to arrive converts the tile's fp32 sums (kept per tile slot: [slot][row][128
+        // columns]) and restores the zeros
+        const int nsplit = in_tail ? p.tail_splits : p.splits;
         asm volatile("bar.sync 1, 256;" ::: "memory");
         if (warp == 8 && lane == 0) {
           __threadfence();
-          const int old = atomicAdd(p.counters + n_tile * p.m_tiles + m_tile, 1);
-          const int last = (old + 1 == p.splits) ? 1 : 0;
+          const int old = atomicAdd(p.counters + slot, 1);
+          const int last = (old + 1 == nsplit) ? 1 : 0;
           if (last) __threadfence();
           bars->last_flag = last;
         }
         asm volatile("bar.sync 1, 256;" ::: "memory");
         if (bars->last_flag) {
           // eight independent loads per thread in flight: one L2 round trip per batch, not per load
+          float* tile_sums = p.partial + (size_t)slot * TM * 128;
           for (int base = tid - 256; base < 64 * TM; base += 8 * 256) {
             float2 x[8];
 #pragma unroll
@@ -355,22 +369,21 @@ umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
               const int idx = base + u * 256;
               const int nn = n_tile * 128 + (idx & 63) * 2, m = m0 + (idx >> 6);
               if (idx < 64 * TM && nn < p.N && m < p.M)
-                x[u] = __ldcg(reinterpret_cast<const float2*>(p.partial + (size_t)m * p.N + nn));
+                x[u] = __ldcg(reinterpret_cast<const float2*>(tile_sums + (size_t)idx * 2));
             }
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
               const int idx = base + u * 256;
               const int nn = n_tile * 128 + (idx & 63) * 2, m = m0 + (idx >> 6);
               if (idx < 64 * TM && nn < p.N && m < p.M) {
-                float2* src = reinterpret_cast<float2*>(p.partial + (size_t)m * p.N + nn);
                 *reinterpret_cast<uint32_t*>(p.c + (size_t)m * p.ldc + nn) = pack2<ACT>(x[u].x, x[u].y);
-                __stcg(src, make_float2(0.f, 0.f));
+                __stcg(reinterpret_cast<float2*>(tile_sums + (size_t)idx * 2), make_float2(0.f, 0.f));
               }
             }
           }
-          if (warp == 8 && lane == 0) p.counters[n_tile * p.m_tiles + m_tile] = 0;
+          if (warp == 8 && lane == 0) p.counters[slot] = 0;
         }
-        asm volatile("bar.sync 1, 256;" ::: "memory");  // last_flag may be rewritten by the next tile
+        asm volatile("bar.sync 1, 256;" ::: "memory");  // last_flag may be rewritten by the next item
       }
     }
   } else if (warp == 16) {
@@ -443,6 +456,7 @@ umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
       bool good = true;
       int ai = 0, tile_it = 0;
       for (int t = blockIdx.x; t < total_tiles && good; t += gridDim.x, ++tile_it) {
+        TILE_COORDS(t)
         // D must have been read out by the epilogue of the previous tile
         if (!mbar_wait_abortable(BAR_ADDR(d_empty, 0), ((uint32_t)tile_it & 1u) ^ 1u, abort_flag)) { good = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -538,13 +552,13 @@ cudaError_t B200Q_CAT(umma_launch_part, B200Q_PART)(int var, const UmmaParams& p
 
 #if B200Q_PART == 0
 // dynamic shared memory: alignment slack + activation stages + weight ring + barriers
-int umma_smem_bytes(int tm, int bits, int a_stages) {
-  return 1024 + a_stages * tm * 128 + UMMA_WG * umma_wstage_bytes(bits) + (int)sizeof(UmmaBarriers) + 64;
+int umma_smem_bytes(int tm, int bits, int a_stages, int rpg) {
+  return 1024 + a_stages * tm * 128 + UMMA_WG * umma_wstage_bytes(bits, rpg) + (int)sizeof(UmmaBarriers) + 64;
 }
 // most activation stages (<= UMMA_SA_MAX) that fit next to the weight ring
-int umma_a_stages(int tm, int bits, int max_smem) {
+int umma_a_stages(int tm, int bits, int max_smem, int rpg) {
   int sa = UMMA_SA_MAX;
-  while (sa > 2 && umma_smem_bytes(tm, bits, sa) > max_smem) --sa;
+  while (sa > 2 && umma_smem_bytes(tm, bits, sa, rpg) > max_smem) --sa;
   return sa;
 }
 #endif

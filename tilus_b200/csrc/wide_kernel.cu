@@ -62,14 +62,14 @@ struct WideBarriers {
   int last_flag;
 };
 
-// a ring stage: the packed weights of 256 columns x 128 rows, then up to four rows of 256 scales
-__host__ __device__ constexpr int wide_wstage_bytes(int bits) { return 4096 * bits + 2048; }
+// a ring stage: the packed weights of 256 columns x 128 rows, then rpg (1, 2 or 4) rows of 256 scales
+__host__ __device__ constexpr int wide_wstage_bytes(int bits, int rpg) { return 4096 * bits + 512 * rpg; }
 
 template <int VAR, int ACT>
 __global__ void __launch_bounds__(WIDE_THREADS, 1)
 wide_kernel(const WideParams p, const __grid_constant__ CUtensorMap tmap_a) {
   constexpr int B = var_bits(VAR);
-  constexpr uint32_t WSTAGE = (uint32_t)wide_wstage_bytes(B);
+  const uint32_t WSTAGE = (uint32_t)wide_wstage_bytes(B, p.rpg);
   constexpr uint32_t BSTAGE = 256u * 128u;
   // Activation stages: the copy fills a_rows rows (32, 64 or 128: the batch rounded up); the MMA
   // always reads 128 rows, i.e. 16 KB, from the stage's base.  Rows beyond the batch only feed
@@ -507,16 +507,16 @@ cudaError_t B200Q_CAT(wide_launch_part, B200Q_PART)(int var, const WideParams& p
 
 #if B200Q_PART == 0
 // dynamic shared memory: alignment slack + activation stages + B operand stages + packed ring + barriers
-int wide_smem_bytes(int bits, int wg_stages, int a_rows) {
-  return 1024 + (WIDE_SA - 1) * a_rows * 128 + 128 * 128 + WIDE_SB * 256 * 128 + wg_stages * wide_wstage_bytes(bits) +
+int wide_smem_bytes(int bits, int wg_stages, int a_rows, int rpg) {
+  return 1024 + (WIDE_SA - 1) * a_rows * 128 + 128 * 128 + WIDE_SB * 256 * 128 + wg_stages * wide_wstage_bytes(bits, rpg) +
          (int)sizeof(WideBarriers) + 64;
 }
 // rows one activation copy fills: the batch rounded up to 32, 64 or 128
 int wide_a_rows(int M) { return M <= 32 ? 32 : (M <= 64 ? 64 : 128); }
 // most packed weight groups in the ring (<= WIDE_WG_MAX) that fit
-int wide_wg_stages(int bits, int max_smem, int a_rows) {
+int wide_wg_stages(int bits, int max_smem, int a_rows, int rpg) {
   int wg = WIDE_WG_MAX;
-  while (wg > 1 && wide_smem_bytes(bits, wg, a_rows) > max_smem) --wg;
+  while (wg > 1 && wide_smem_bytes(bits, wg, a_rows, rpg) > max_smem) --wg;
   return wg;
 }
 #endif
