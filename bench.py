@@ -19,7 +19,8 @@ copied out every step), `cpu_baseline` (the CPU oracle - the reference's PyTorch
 dequantize + matmul semantics - timed on this host), `clocks`, `gpu_launches`,
 `headline_shapes` (the metric's three shapes M = 1 / 16 / 4096 against their rooflines),
 `stack` (the Llama-3-8B-shaped decode linear stack, N-sharded over the ranks of this run
-with an all-gather per layer: NCCL and fused into the GEMV kernel, strong scaling) and an
+with an all-gather per layer: NCCL and over peer memory - fused into the GEMV kernel for
+M <= 16, a push / collect kernel pair above -, strong scaling) and an
 `extra` sweep: the other bit widths at M=1, M=16, the M=16 K=N=4096 configuration, the
 per-channel float6 / int3 batch sweep, the Llama-3-8B layer shapes at M in {1, 8, 32, 64},
 the reference example's own table (K=4096, N=12288, eight weight types, M in {1, 16, 4096,
@@ -351,15 +352,15 @@ def measure_stack(world, rank, dev, steps, warmup, batches=(1, 8, 32, 64)) -> di
             x = down(h[:, :14336])
         return x
 
-    ctx = sharded.PeerGather.create(16, 28672, dev)
+    ctx = sharded.PeerGather.create(64, 28672, dev)
 
     def step_fused(x, blocks=layers):
         row = x
         for qkv, o, gate_up, down in blocks:
             row = ctx.gemm(row, qkv)
-            row = ctx.gemm(row.cols(0, 4096), o)
+            row = ctx.gemm(ctx.cols(row, 0, 4096), o)
             row = ctx.gemm(row, gate_up)
-            row = ctx.gemm(row.cols(0, 14336), down)
+            row = ctx.gemm(ctx.cols(row, 0, 14336), down)
         return row
 
     w_ref = {}
@@ -387,7 +388,7 @@ def measure_stack(world, rank, dev, steps, warmup, batches=(1, 8, 32, 64)) -> di
     results, graphs = {}, []
     for m in batches:
         x = (torch.randn(m, 4096, generator=torch.Generator().manual_seed(m)) * 0.05).to(torch.float16).to(dev)
-        modes = ["nccl" if world > 1 else "single"] + (["fused"] if m <= 16 else [])
+        modes = ["nccl" if world > 1 else "single"] + ["fused"]
         entry = {}
         # ---- correctness of what is timed (all device work first: a rank that computed the oracle
         # in between would keep its peers' fused kernels waiting beyond their bounded wait) ----
@@ -444,7 +445,9 @@ def measure_stack(world, rank, dev, steps, warmup, batches=(1, 8, 32, 64)) -> di
     return {"workload": "llama3_8b_linear_stack_u4_g128", "layers": n_layers, "linears_per_step": 4 * n_layers,
             "scaling": "strong", "unit": "ms per 128-linear step", "per_gpu_weight_bytes": weight_bytes,
             "gather": {"nccl": "ncclAllGather per layer (M > 1: + one permute copy)",
-                       "fused": "peer stores from the GEMV kernel + per-rank flags (b200q_gemm_gather), M <= 16"},
+                       "fused": "M <= 16: peer stores from the GEMV kernel + per-rank flags (b200q_gemm_gather); "
+                                "M > 16: GEMM, then a push kernel (peer stores + flags) and a collect kernel "
+                                "(b200q_gather_push)"},
             "results": results}
 
 

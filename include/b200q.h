@@ -174,6 +174,19 @@ int b200q_gemm_gather(const void* a, int lda, const void* bq, const void* scales
                       int zero_point, int group, int act_dtype, void* workspace, size_t workspace_bytes, void* stream,
                       const b200q_gather_t* gather);
 
+/* The same all-gather for an output that some other kernel produced (batches of more than 16 rows run
+ * b200q_gemm on the local shard first), as two calls made one after the other on one stream:
+ * b200q_gather_push copies shard[M, N_loc] (row stride lds) into this rank's column range of row
+ * buffer (E + 1) % 2 of every rank and raises the flags like a fused call; b200q_gather_collect waits
+ * (bounded) until all ranks' shards of that call have landed here and copies the complete rows to
+ * full_local [M, ldc] (row stride ld_local; NULL: wait only).  Same regions, counters and rules as
+ * b200q_gemm_gather, with which they can be mixed; `workspace` holds the status header (256 bytes are
+ * enough).  status[1] = 7 / 8 names a wait of push / collect that gave up. */
+int b200q_gather_push(const void* shard, int lds, int M, int N_loc, void* workspace, size_t workspace_bytes,
+                      void* stream, const b200q_gather_t* gather);
+int b200q_gather_collect(void* full_local, int ld_local, int M, void* workspace, size_t workspace_bytes, void* stream,
+                         const b200q_gather_t* gather);
+
 /* Device memory that other processes of the node can map (cudaMalloc + CUDA IPC): allocate,
  * export a 64-byte handle, open a peer's handle (enables peer access), close, free.  These five
  * are the only functions of the library that allocate or free device memory. */

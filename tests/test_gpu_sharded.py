@@ -159,3 +159,39 @@ def test_fused_gather_wait_runs_out_and_reports():
     ref = qo.quantized_matmul(prob["a"].numpy(), prob["codes"][:, :256].numpy(), prob["scales"][:, :256].numpy(), dt, g, 0)
     err = np.abs(c.float().cpu().numpy() - ref.astype(np.float32)).max() / np.abs(ref.astype(np.float32)).max()
     assert err <= 1e-2
+
+
+@pytest.mark.parametrize("M", [20, 64])
+def test_push_collect_gather_above_16_rows(M):
+    """More than 16 rows: local GEMM, then push (shard to every rank's row buffer + flags) and collect
+    (wait for all shards, copy the rows out).  Two ranks played on one stream: both push, then both
+    collect - a collect waits for the pushes of the same call, so they must all have been queued."""
+    dev = torch.device("cuda:0")
+    dt, g, world = D.int4b, 128, 2
+    dims = [(512, 1024), (1024, 512)]
+    probs = [synth.make_problem(M, n, k, dt, g, seed=30 + i) for i, (k, n) in enumerate(dims)]
+    regions, ctxs = _virtual_group(world, 64, 1024, dev)
+    x = [(probs[0]["a"] * 0.25).to(torch.float16).to(dev)] * world
+    ref = x[0].cpu().numpy()
+    for (k, n), prob in zip(dims, probs):
+        lins = []
+        for r in range(world):
+            lin = sharded.ShardedQuantizedLinear(float16, dt, g, k, n, shard=(world, r)).to(dev)
+            lin.load_codes(prob["codes"], prob["scales"])
+            lins.append(lin)
+        shards = [lins[r].local(x[r]) for r in range(world)]
+        for r in range(world):
+            ctxs[r].push(shards[r], lins[r])
+        full = [torch.empty(M, n, dtype=torch.float16, device=dev) for _ in range(world)]
+        for r in range(world):
+            ctxs[r].collect(full[r], M, n)
+        x = full
+        ref = qo.quantized_matmul(ref, prob["codes"].numpy(), prob["scales"].numpy(), dt, g, 0)
+    torch.cuda.synchronize()
+    ws = ops.get_workspace(dev, 1 << 20)
+    assert ops.device_status(ws) == [0, 0, 0, 0]
+    for r in range(world):
+        got = x[r].float().cpu().numpy()
+        err = np.abs(got - ref.astype(np.float32)).max() / np.abs(ref.astype(np.float32)).max()
+        assert err <= 2e-2, (r, err)
+        assert ctxs[r].calls_completed() == len(dims)

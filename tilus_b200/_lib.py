@@ -76,6 +76,8 @@ SYMBOLS = {
     "b200q_static_ws_init": (_i, []),
     "b200q_dequantize": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "b200q_gemm_gather": (_i, [_vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp, ctypes.POINTER(Gather)]),
+    "b200q_gather_push": (_i, [_vp, _i, _i, _i, _vp, _sz, _vp, ctypes.POINTER(Gather)]),
+    "b200q_gather_collect": (_i, [_vp, _i, _i, _vp, _sz, _vp, ctypes.POINTER(Gather)]),
     "b200q_peer_alloc": (_i, [_sz, ctypes.POINTER(ctypes.c_void_p)]),
     "b200q_peer_export": (_i, [_vp, ctypes.c_char_p]),
     "b200q_peer_open": (_i, [ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p)]),

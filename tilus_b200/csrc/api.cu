@@ -22,6 +22,10 @@ B200Q_DECL_SPART(0) B200Q_DECL_SPART(1) B200Q_DECL_SPART(2) B200Q_DECL_SPART(3)
 B200Q_DECL_SPART(4) B200Q_DECL_SPART(5) B200Q_DECL_SPART(6) B200Q_DECL_SPART(7)
 cudaError_t dequant_launch(int var, const DequantParams& p, cudaStream_t stream);
 cudaError_t cast_launch(const CastParams& p, int act, bool swiglu, cudaStream_t stream);
+cudaError_t gather_push_launch(const void* src, int lds, int M, int N_loc, int ldc, int* status, const GatherArgs& ga,
+                               cudaStream_t stream);
+cudaError_t gather_collect_launch(void* dst_local, int ld_local, int M, int ldc, int* status, const GatherArgs& ga,
+                                  cudaStream_t stream);
 cudaError_t quantize_launch(const void* w, int w_dtype, int ldw, void* bq, void* scales, int N, int K, int group,
                             int kind, int nbits, int ebits, int mbits, float minv, float maxv, int act,
                             cudaStream_t stream);
@@ -477,6 +481,29 @@ static int run_wide(const void* a, int lda, const void* bq, const void* scales, 
   return ST_OK;
 }
 
+// b200q_gather_t of the C ABI -> the kernels' GatherArgs (checked)
+static int fill_gather_args(const b200q_gather_t* gather, int M, int N, void* workspace, GatherArgs* ga) {
+  std::memset(ga, 0, sizeof(*ga));
+  if (gather->world < 1 || gather->world > 8 || gather->rank < 0 || gather->rank >= gather->world) return ST_INVALID_ARG;
+  if (gather->ldc < gather->col_offset + N || gather->col_offset < 0 || !gather->flags_local ||
+      !gather->epoch_local || gather->buffer_elems < (int64_t)M * gather->ldc)
+    return ST_INVALID_ARG;
+  ga->G = gather->world;
+  ga->rank = gather->rank;
+  ga->col_off = gather->col_offset;
+  for (int g = 0; g < gather->world; ++g) {
+    if (!gather->out[g] || !gather->flag_slot[g]) return ST_INVALID_ARG;
+    ga->out[g] = reinterpret_cast<__half*>(gather->out[g]);
+    ga->flag_slot[g] = reinterpret_cast<unsigned*>(gather->flag_slot[g]);
+  }
+  ga->flags = reinterpret_cast<const unsigned*>(gather->flags_local);
+  ga->epoch = reinterpret_cast<unsigned*>(gather->epoch_local);
+  ga->buf_elems = gather->buffer_elems;
+  ga->a_prev_off = gather->a_prev_offset;
+  ga->done = reinterpret_cast<unsigned*>(workspace) + 8;  // word 8 of the status header
+  return ST_OK;
+}
+
 static int run_stream(const void* a, int lda, const void* bq, const void* scales, void* c, int ldc, int M, int N,
                       int K, int var, int group, int act, void* workspace, size_t ws_bytes, cudaStream_t stream,
                       const b200q_plan_t& pl, const b200q_gather_t* gather = nullptr) {
@@ -512,24 +539,9 @@ static int run_stream(const void* a, int lda, const void* bq, const void* scales
   }
   std::memset(&p.ga, 0, sizeof(p.ga));
   if (gather) {
-    if (M > 16 || gather->world < 1 || gather->world > 8 || gather->rank < 0 || gather->rank >= gather->world)
-      return ST_INVALID_ARG;
-    if (gather->ldc < gather->col_offset + N || gather->col_offset < 0 || !gather->flags_local ||
-        !gather->epoch_local || gather->buffer_elems < (int64_t)M * gather->ldc)
-      return ST_INVALID_ARG;
-    p.ga.G = gather->world;
-    p.ga.rank = gather->rank;
-    p.ga.col_off = gather->col_offset;
-    for (int g = 0; g < gather->world; ++g) {
-      if (!gather->out[g] || !gather->flag_slot[g]) return ST_INVALID_ARG;
-      p.ga.out[g] = reinterpret_cast<__half*>(gather->out[g]);
-      p.ga.flag_slot[g] = reinterpret_cast<unsigned*>(gather->flag_slot[g]);
-    }
-    p.ga.flags = reinterpret_cast<const unsigned*>(gather->flags_local);
-    p.ga.epoch = reinterpret_cast<unsigned*>(gather->epoch_local);
-    p.ga.buf_elems = gather->buffer_elems;
-    p.ga.a_prev_off = gather->a_prev_offset;
-    p.ga.done = reinterpret_cast<unsigned*>(workspace) + 8;  // word 8 of the status header
+    if (M > 16) return ST_INVALID_ARG;
+    const int gst = fill_gather_args(gather, M, N, workspace, &p.ga);
+    if (gst != ST_OK) return gst;
     p.ldc = gather->ldc;
   }
   const int rows = stream_rows_per_pass(M);
@@ -649,6 +661,36 @@ int b200q_gemm_gather(const void* a, int lda, const void* bq, const void* scales
   if (pl.kernel != 2) return ST_UNSUPPORTED;
   return run_stream(a, lda, bq, scales, nullptr, gather->ldc, M, N, K, var, group, act_dtype, workspace,
                     workspace_bytes, reinterpret_cast<cudaStream_t>(stream), pl, gather);
+}
+
+int b200q_gather_push(const void* shard, int lds, int M, int N_loc, void* workspace, size_t workspace_bytes,
+                      void* stream, const b200q_gather_t* gather) {
+  if (!shard || !gather || M < 1 || N_loc < 8) return ST_INVALID_ARG;
+  if ((N_loc % 8) != 0 || (lds % 8) != 0 || lds < N_loc || (((uintptr_t)shard) & 15)) return ST_INVALID_ARG;
+  if ((gather->ldc % 8) != 0 || (gather->col_offset % 8) != 0) return ST_INVALID_ARG;
+  if (!workspace || workspace_bytes < WS_HEADER_BYTES || ((uintptr_t)workspace & 255)) return ST_WORKSPACE;
+  GatherArgs ga;
+  const int st = fill_gather_args(gather, M, N_loc, workspace, &ga);
+  if (st != ST_OK) return st;
+  cudaError_t e = gather_push_launch(shard, lds, M, N_loc, gather->ldc, reinterpret_cast<int*>(workspace), ga,
+                                     reinterpret_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) { g_last_cuda_error = (int)e; return ST_CUDA; }
+  return ST_OK;
+}
+
+int b200q_gather_collect(void* full_local, int ld_local, int M, void* workspace, size_t workspace_bytes, void* stream,
+                         const b200q_gather_t* gather) {
+  if (!gather || M < 1) return ST_INVALID_ARG;
+  if ((gather->ldc % 8) != 0) return ST_INVALID_ARG;
+  if (full_local && ((ld_local % 8) != 0 || ld_local < gather->ldc || (((uintptr_t)full_local) & 15))) return ST_INVALID_ARG;
+  if (!workspace || workspace_bytes < WS_HEADER_BYTES || ((uintptr_t)workspace & 255)) return ST_WORKSPACE;
+  GatherArgs ga;
+  const int st = fill_gather_args(gather, M, 0, workspace, &ga);
+  if (st != ST_OK) return st;
+  cudaError_t e = gather_collect_launch(full_local, ld_local, M, gather->ldc, reinterpret_cast<int*>(workspace), ga,
+                                        reinterpret_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) { g_last_cuda_error = (int)e; return ST_CUDA; }
+  return ST_OK;
 }
 
 int b200q_peer_alloc(size_t bytes, void** ptr) {

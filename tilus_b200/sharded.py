@@ -131,6 +131,7 @@ class PeerGather:
         self.max_rows, self.max_cols = max_rows, max_cols
         self.device = torch.device(device)
         self._owned = None     # this rank's region, if allocated by create()
+        self._full = {}        # gathered outputs of calls with more than 16 rows, per shape
         self._opened = []      # peers' regions mapped by create()
         self.dtype = torch.float16  # dtype of the latest call's output rows
 
@@ -186,33 +187,61 @@ class PeerGather:
     def _view(self, byte_off: int, nbytes: int) -> torch.Tensor:
         return torch.as_tensor(_RawCudaBuffer(self.ptrs[self.rank] + byte_off, nbytes), device=self.device)
 
-    def gemm(self, x, layer: "ShardedQuantizedLinear") -> GatheredRow:
-        """One fused call: this rank's columns of layer(x), gathered into every rank's row buffer.
-        x is a tensor [M, K] or the GatheredRow (or a column range of it) of the previous call."""
-        lib = _lib.load()
-        local = layer.local
-        N_full, N_loc, K = layer.out_features, local.out_features, layer.in_features
+    def _desc(self, N_full: int, col_offset: int) -> "_lib.Gather":
         g = _lib.Gather()
-        if isinstance(x, GatheredRow):
-            M, lda, a_ptr = x.rows, x.row_stride, None
-            if x.width != K:
-                raise ValueError(f"expected {K} input features, got {x.width}")
-            g.a_prev_offset = x.col_start
-        else:
-            if x.dtype != local.scales.dtype or x.stride(1) != 1 or x.shape[1] != K:
-                raise TypeError(f"activations must be {local.scales.dtype} [M, {K}] with unit inner stride")
-            M, lda, a_ptr = x.shape[0], x.stride(0), x.data_ptr()
-            g.a_prev_offset = -1
-        if M > self.max_rows or N_full > self.max_cols or M > 16:
-            raise ValueError("fused gather covers M <= 16 rows within the context's buffer size")
-        g.world, g.rank, g.ldc, g.col_offset = self.world, self.rank, N_full, layer.n0
+        g.world, g.rank, g.ldc, g.col_offset = self.world, self.rank, N_full, col_offset
         for r in range(self.world):
             g.out[r] = self.ptrs[r] + self.ROWS_OFF
             g.flag_slot[r] = self.ptrs[r] + self.FLAGS_OFF + 4 * self.rank
         g.flags_local = self.ptrs[self.rank] + self.FLAGS_OFF
         g.epoch_local = self.ptrs[self.rank] + self.EPOCH_OFF
         g.buffer_elems = self.max_rows * self.max_cols
+        g.a_prev_offset = -1
+        return g
+
+    def gemm(self, x, layer: "ShardedQuantizedLinear"):
+        """One call: this rank's columns of layer(x), gathered into every rank's row buffer.  x is a
+        tensor [M, K] or what the previous call returned (or a column range of it, `cols`).
+
+        Up to 16 rows the GEMV kernel itself stores into every rank's buffer (b200q_gemm_gather) and the
+        result is a GatheredRow - a handle whose buffer only the device knows; the next call takes it
+        as its activations, `fetch` brings it to a tensor.  Above 16 rows the local GEMM runs as usual
+        and two small kernels push its shard to every rank and collect the complete rows
+        (b200q_gather_push); the result is an ordinary tensor [M, N] owned by this context (valid
+        until the next call with the same shape)."""
+        lib = _lib.load()
+        local = layer.local
+        N_full, N_loc, K = layer.out_features, local.out_features, layer.in_features
         dt, zp, grp = local.w_dtype, local.zero_point, local.group_size
+        if isinstance(x, GatheredRow):
+            M = x.rows
+        else:
+            if x.dtype != local.scales.dtype or x.stride(1) != 1 or x.shape[1] != K:
+                raise TypeError(f"activations must be {local.scales.dtype} [M, {K}] with unit inner stride")
+            M = x.shape[0]
+        if M > self.max_rows or N_full > self.max_cols:
+            raise ValueError("batch or layer width beyond the context's buffer size")
+        g = self._desc(N_full, layer.n0)
+        self.dtype = local.scales.dtype
+        if M > 16:
+            if isinstance(x, GatheredRow):
+                raise ValueError("a GatheredRow feeds fused calls (M <= 16) only")
+            with torch.cuda.device(self.device):
+                shard = local(x)
+                full = self._full.get((M, N_full, self.dtype))
+                if full is None:
+                    full = torch.empty(M, N_full, dtype=self.dtype, device=self.device)
+                    self._full[(M, N_full, self.dtype)] = full
+                self.push(shard, layer)
+                self.collect(full, M, N_full)
+            return full
+        if isinstance(x, GatheredRow):
+            lda, a_ptr = x.row_stride, None
+            if x.width != K:
+                raise ValueError(f"expected {K} input features, got {x.width}")
+            g.a_prev_offset = x.col_start
+        else:
+            lda, a_ptr = x.stride(0), x.data_ptr()
         with torch.cuda.device(self.device):
             ws = ops.get_workspace(self.device, ops.workspace_bytes(M, N_loc, K, dt, zp, grp))
             st = lib.b200q_gemm_gather(a_ptr, lda, local.quantized_weight.data_ptr(), local.scales.data_ptr(), M,
@@ -220,8 +249,30 @@ class PeerGather:
                                        ws.numel(),
                                        torch.cuda.current_stream(self.device).cuda_stream, ctypes.byref(g))
         _lib.check(st)
-        self.dtype = local.scales.dtype
         return GatheredRow(M, N_full, 0, N_full)
+
+    def push(self, shard: torch.Tensor, layer: "ShardedQuantizedLinear"):
+        """First half of a gathered call with more than 16 rows: this rank's shard [M, N/G] to every rank."""
+        g = self._desc(layer.out_features, layer.n0)
+        with torch.cuda.device(self.device):
+            ws = ops.get_workspace(self.device, 1 << 20)
+            _lib.check(_lib.load().b200q_gather_push(
+                shard.data_ptr(), shard.stride(0), shard.shape[0], shard.shape[1], ws.data_ptr(), ws.numel(),
+                torch.cuda.current_stream(self.device).cuda_stream, ctypes.byref(g)))
+
+    def collect(self, full: torch.Tensor, M: int, N_full: int):
+        """Second half: wait for every rank's shard of the call just pushed, copy the rows to `full`."""
+        g = self._desc(N_full, 0)
+        with torch.cuda.device(self.device):
+            ws = ops.get_workspace(self.device, 1 << 20)
+            _lib.check(_lib.load().b200q_gather_collect(
+                full.data_ptr(), full.stride(0), M, ws.data_ptr(), ws.numel(),
+                torch.cuda.current_stream(self.device).cuda_stream, ctypes.byref(g)))
+
+    @staticmethod
+    def cols(row, start: int, stop: int):
+        """Columns [start, stop) of what `gemm` returned, as the activations of the next call."""
+        return row.cols(start, stop) if isinstance(row, GatheredRow) else row[:, start:stop]
 
     def calls_completed(self) -> int:
         """The device-side call counter (synchronises the current stream)."""
@@ -245,9 +296,12 @@ class PeerGather:
                 raise _lib.B200QError(_lib.ST_DEVICE_TIMEOUT, f"fused gather: flags {seen.tolist()} never reached call {epoch}")
             time.sleep(0.0005)
 
-    def fetch(self, row: GatheredRow) -> torch.Tensor:
+    def fetch(self, row) -> torch.Tensor:
         """The latest call's gathered output (or the column range `row` of it) as a new tensor, once
         every rank's columns are in place."""
+        if not isinstance(row, GatheredRow):  # more than 16 rows: already collected on the device
+            torch.cuda.current_stream(self.device).synchronize()
+            return row.clone()
         parity = self.wait_all_ranks() & 1
         nbytes = self.max_rows * self.max_cols * 2
         buf = self._view(self.ROWS_OFF + parity * nbytes, nbytes).view(self.dtype)
