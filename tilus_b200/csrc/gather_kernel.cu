@@ -54,6 +54,10 @@ __device__ __forceinline__ bool wait_flags(const PushParams& p, unsigned target,
 }
 
 __global__ void __launch_bounds__(256) gather_push_kernel(const PushParams p) {
+  // launched with programmatic stream serialization: resident early, waits here for the GEMM whose
+  // output it copies
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const unsigned epoch = *reinterpret_cast<volatile const unsigned*>(p.ga.epoch);
   // nobody may still be reading the buffer about to be overwritten: every rank has finished call E
   if (epoch != 0) wait_flags(p, epoch, 7);
@@ -81,6 +85,8 @@ __global__ void __launch_bounds__(256) gather_push_kernel(const PushParams p) {
 }
 
 __global__ void __launch_bounds__(256) gather_collect_kernel(const PushParams p) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // this rank's push has completed: the call counter is final
   const unsigned epoch = *reinterpret_cast<volatile const unsigned*>(p.ga.epoch);  // includes this call's push
   wait_flags(p, epoch, 8);
   if (!p.dst_local) return;
@@ -94,6 +100,20 @@ __global__ void __launch_bounds__(256) gather_collect_kernel(const PushParams p)
     const uint4 x = __ldcg(reinterpret_cast<const uint4*>(row + (size_t)m * p.ldc + v * 8));
     *reinterpret_cast<uint4*>(p.dst_local + (size_t)m * p.ld_local + v * 8) = x;
   }
+}
+
+static cudaError_t launch_pdl(void (*kern)(const PushParams), int grid, const PushParams& p, cudaStream_t stream) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid, 1, 1);
+  cfg.blockDim = dim3(256, 1, 1);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, p);
 }
 
 static PushParams make_params(const void* src, int lds, void* dst_local, int ld_local, int M, int N_loc, int ldc,
@@ -114,8 +134,7 @@ cudaError_t gather_push_launch(const void* src, int lds, int M, int N_loc, int l
   int grid = (M * (N_loc / 8) + 255) / 256;
   if (grid > 64) grid = 64;
   if (grid < 1) grid = 1;
-  gather_push_kernel<<<grid, 256, 0, stream>>>(p);
-  return cudaGetLastError();
+  return launch_pdl(gather_push_kernel, grid, p, stream);
 }
 
 cudaError_t gather_collect_launch(void* dst_local, int ld_local, int M, int ldc, int* status, const GatherArgs& ga,
@@ -124,8 +143,7 @@ cudaError_t gather_collect_launch(void* dst_local, int ld_local, int M, int ldc,
   int grid = (M * (ldc / 8) + 255) / 256;
   if (grid > 296) grid = 296;
   if (grid < 1) grid = 1;
-  gather_collect_kernel<<<grid, 256, 0, stream>>>(p);
-  return cudaGetLastError();
+  return launch_pdl(gather_collect_kernel, grid, p, stream);
 }
 
 }  // namespace b200q
