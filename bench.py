@@ -300,7 +300,7 @@ def run_profile_case(args) -> None:
                       "us_per_launch_plain_stream": us}))
 
 
-def measure_stack(world, rank, dev, steps, warmup, batches=(1, 8, 32, 64)) -> dict:
+def measure_stack(world, rank, dev, steps, warmup, batches=(1, 8, 32, 64), tagged_rows=16) -> dict:
     """Llama-3-8B-shaped decode linear stack, N-sharded over the ranks, all-gather of every layer's
     output: 32 x {qkv 4096->6144, o 4096->4096, gate_up 4096->28672, down 14336->4096}, uint4 g128
     weights, batch M in {1, 8, 32, 64}.  Strong scaling: the model is fixed, the shards shrink with the
@@ -352,7 +352,7 @@ def measure_stack(world, rank, dev, steps, warmup, batches=(1, 8, 32, 64)) -> di
             x = down(h[:, :14336])
         return x
 
-    ctx = sharded.PeerGather.create(64, 28672, dev)
+    ctx = sharded.PeerGather.create(64, 28672, dev, tagged_rows=tagged_rows)
 
     def step_fused(x, blocks=layers):
         row = x
@@ -445,7 +445,9 @@ def measure_stack(world, rank, dev, steps, warmup, batches=(1, 8, 32, 64)) -> di
     return {"workload": "llama3_8b_linear_stack_u4_g128", "layers": n_layers, "linears_per_step": 4 * n_layers,
             "scaling": "strong", "unit": "ms per 128-linear step", "per_gpu_weight_bytes": weight_bytes,
             "gather": {"nccl": "ncclAllGather per layer (M > 1: + one permute copy)",
-                       "fused": "M <= 16: peer stores from the GEMV kernel + per-rank flags (b200q_gemm_gather); "
+                       "fused": f"M <= {min(tagged_rows, 16)} on 2+ GPUs: peer stores of tagged words from the GEMV "
+                                "kernel, polled by the next one (b200q_gemm_gather, B200Q_GATHER_TAGGED); "
+                                "else M <= 16: peer stores from the GEMV kernel + per-rank flags; "
                                 "M > 16: GEMM, then a push kernel (peer stores + flags) and a collect kernel "
                                 "(b200q_gather_push)"},
             "results": results}
@@ -471,7 +473,8 @@ def run_stack(args) -> None:
     torch.cuda.set_device(dev)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    res = measure_stack(world, rank, dev, args.steps, args.warmup)
+    res = measure_stack(world, rank, dev, args.steps, args.warmup, tagged_rows=args.tagged_rows,
+                        batches=tuple(int(b) for b in args.stack_batches.split(",")))
     if rank == 0:
         print(json.dumps({"metric": "Llama-3-8B-shaped decode linear stack, N-sharded, all-gather per layer",
                           "n_gpus": world, "steps": args.steps, "dtype": "f16", "data": "synthetic", **res}),
@@ -609,7 +612,8 @@ def run_b200(args) -> None:
         watchdog.daemon = True
         watchdog.start()
         try:
-            stack = measure_stack(world, rank, dev, max(3, min(args.steps, 10)), args.warmup)
+            stack = measure_stack(world, rank, dev, max(3, min(args.steps, 10)), args.warmup,
+                                  tagged_rows=args.tagged_rows)
         except Exception as exc:  # the headline line must still be printed
             stack = {"error": f"{type(exc).__name__}: {exc}"}
         finally:
@@ -707,6 +711,9 @@ def main():
     ap.add_argument("--stack", action="store_true",
                     help="time the N-sharded Llama-3-8B-shaped decode linear stack (all-gather per layer) instead")
     ap.add_argument("--no-stack", action="store_true", help="skip the N-sharded decode stack")
+    ap.add_argument("--stack-batches", default="1,8,32,64", help="--stack: batch sizes to run")
+    ap.add_argument("--tagged-rows", type=int, default=16,
+                    help="stack: batches of up to this many rows hand their rows over as tagged words (0: flags only)")
     ap.add_argument("--profile-case", default=None, choices=["decode", "batch16", "batch32", "prefill"],
                     help="run a few plain launches of one kernel (for ncu) instead of the benchmark")
     args = ap.parse_args()

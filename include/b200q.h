@@ -157,7 +157,26 @@ size_t b200q_static_workspace_limit(void);
  * rank's previous gathered output (buffer E % 2, from that element on, row stride lda) and `a`
  * is ignored.  No per-call state is passed from the host, so the same call sequence can be
  * captured once and replayed from a CUDA graph.  All ranks must make the same sequence of calls.
- * Word 8 of the workspace header counts the CTAs of the launch. */
+ * Word 8 of the workspace header counts the CTAs of the launch.
+ *
+ * mode = B200Q_GATHER_TAGGED replaces flags by tags inside the data: for these batches the hand-over
+ * between GPUs is most of a layer's time.  The row buffers then hold 64-bit words
+ * {two 16-bit outputs, 32-bit call number}: `out[g]` = word buffer 0 of rank g ([M, ldc / 2] words),
+ * THREE buffers per rank used in turn, `buffer_elems` = words between consecutive buffers,
+ * `epoch_local` = 16 consecutive 32-bit words of this mode's own (word 0 the call counter, word 8 an
+ * arrival counter, the rest spare; zero at the start), `flag_slot` / `flags_local` unused.  Fused call E + 1
+ * stores each pair of its outputs with the tag E + 1 in one 64-bit store into buffer (E + 1) % 3 of
+ * every rank; with `a_prev_offset >= 0` it reads buffer E % 3 word by word and repeats a load -
+ * bounded as above - until the word carries tag E.  No launch waits for a whole grid of another
+ * GPU and nothing is fenced; the previous call's data is safe because whoever overwrites a buffer
+ * has read words that were written after its last reader finished.  Two rules follow: a call with
+ * activations from outside (`a_prev_offset < 0`) must not follow another such call directly unless a
+ * b200q_gather_collect (wait only is enough) lies between them, and every rank issues its calls on
+ * one stream.  b200q_gather_collect turns the latest call's tagged rows into dense rows;
+ * b200q_gather_push takes the flag mode only.  Tagged and flag calls use separate buffers and
+ * counters and do not see each other. */
+#define B200Q_GATHER_FLAGS 0
+#define B200Q_GATHER_TAGGED 1
 typedef struct b200q_gather {
   int32_t world, rank;
   int32_t ldc;            /* elements per full output row */
@@ -168,6 +187,8 @@ typedef struct b200q_gather {
   void* epoch_local;      /* this rank's call counter, uint32 */
   int64_t buffer_elems;   /* elements between a rank's two row buffers */
   int64_t a_prev_offset;  /* >= 0: activations = this rank's previous gathered output from this element on */
+  int32_t mode;           /* B200Q_GATHER_FLAGS or B200Q_GATHER_TAGGED */
+  int32_t reserved;       /* 0 */
 } b200q_gather_t;
 
 int b200q_gemm_gather(const void* a, int lda, const void* bq, const void* scales, int M, int N, int K, int wtype,
@@ -181,7 +202,8 @@ int b200q_gemm_gather(const void* a, int lda, const void* bq, const void* scales
  * (bounded) until all ranks' shards of that call have landed here and copies the complete rows to
  * full_local [M, ldc] (row stride ld_local; NULL: wait only).  Same regions, counters and rules as
  * b200q_gemm_gather, with which they can be mixed; `workspace` holds the status header (256 bytes are
- * enough).  status[1] = 7 / 8 names a wait of push / collect that gave up. */
+ * enough).  status[1] = 7 / 8 names a wait of push / collect that gave up.  In tagged mode collect
+ * waits for the tags of the latest fused call and writes the values of its words as dense rows. */
 int b200q_gather_push(const void* shard, int lds, int M, int N_loc, void* workspace, size_t workspace_bytes,
                       void* stream, const b200q_gather_t* gather);
 int b200q_gather_collect(void* full_local, int ld_local, int M, void* workspace, size_t workspace_bytes, void* stream,

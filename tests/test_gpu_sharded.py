@@ -16,21 +16,23 @@ from tilus_b200 import dtypes as D
 pytestmark = pytest.mark.gpu
 
 
-def _virtual_group(world, max_rows, max_cols, dev):
-    regions = [torch.zeros(sharded.PeerGather.region_bytes(max_rows, max_cols), dtype=torch.uint8, device=dev)
-               for _ in range(world)]
+def _virtual_group(world, max_rows, max_cols, dev, tagged_rows=0):
+    """tagged_rows = 0: every fused call uses the flag protocol; n: batches of up to n rows use tagged words"""
+    regions = [torch.zeros(sharded.PeerGather.region_bytes(max_rows, max_cols, tagged_rows), dtype=torch.uint8,
+                           device=dev) for _ in range(world)]
     ptrs = [r.data_ptr() for r in regions]
-    return regions, [sharded.PeerGather(world, r, ptrs, max_rows, max_cols, dev) for r in range(world)]
+    return regions, [sharded.PeerGather(world, r, ptrs, max_rows, max_cols, dev, tagged_rows) for r in range(world)]
 
 
+@pytest.mark.parametrize("tagged", [False, True], ids=["flags", "tagged"])
 @pytest.mark.parametrize("M", [1, 5, 16])
 @pytest.mark.parametrize("world", [2, 4])
-def test_fused_gather_chain_matches_unsharded(M, world):
+def test_fused_gather_chain_matches_unsharded(M, world, tagged):
     dev = torch.device("cuda:0")
     dt, g = D.uint4b, 128
     dims = [(1024, 2048), (2048, 1024), (1024, 512)]  # a chain of three layers
     probs = [synth.make_problem(M, n, k, dt, g, seed=10 + i) for i, (k, n) in enumerate(dims)]
-    regions, ctxs = _virtual_group(world, 16, 2048, dev)
+    regions, ctxs = _virtual_group(world, 16, 2048, dev, 16 if tagged else 0)
     shards = []
     for (k, n), prob in zip(dims, probs):
         per_rank = []
@@ -57,16 +59,19 @@ def test_fused_gather_chain_matches_unsharded(M, world):
     # every rank saw every rank finish the last call, and counted its own calls
     for r in range(world):
         flags = regions[r][: 4 * world].view(torch.int32).cpu().numpy()
-        assert (flags == len(dims)).all()
-        assert ctxs[r].calls_completed() == len(dims)
+        assert (flags == (0 if tagged else len(dims))).all()
+        assert ctxs[r].calls_completed(tagged) == len(dims)
+        assert ctxs[r].calls_completed(not tagged) == 0
+    assert ops.device_status(ops.get_workspace(dev, 1 << 20)) == [0, 0, 0, 0]
 
 
-def test_fused_gather_replays_from_a_cuda_graph():
+@pytest.mark.parametrize("tagged", [False, True], ids=["flags", "tagged"])
+def test_fused_gather_replays_from_a_cuda_graph(tagged):
     """The calls carry no per-call state: a captured chain can be replayed and keeps counting."""
     dev = torch.device("cuda:0")
     dt, g, M, world = D.int4b, 128, 2, 2
     prob = synth.make_problem(M, 1024, 1024, dt, g, seed=3)
-    regions, ctxs = _virtual_group(world, 16, 1024, dev)
+    regions, ctxs = _virtual_group(world, 16, 1024, dev, 2 if tagged else 0)
     lins = []
     for r in range(world):
         lin = sharded.ShardedQuantizedLinear(float16, dt, g, 1024, 1024, shard=(world, r)).to(dev)
@@ -90,7 +95,7 @@ def test_fused_gather_replays_from_a_cuda_graph():
         want1 = qo.quantized_matmul(x.cpu().numpy(), prob["codes"].numpy(), prob["scales"].numpy(), dt, g, 0)
         want2 = qo.quantized_matmul(want1, prob["codes"].numpy(), prob["scales"].numpy(), dt, g, 0)
         for r in range(world):
-            assert ctxs[r].calls_completed() == 2 + 3 * 2
+            assert ctxs[r].calls_completed(tagged) == 2 + 3 * 2
             got = ctxs[r].fetch(rows[r]).float().cpu().numpy()
             err = np.abs(got - want2.astype(np.float32)).max() / np.abs(want2.astype(np.float32)).max()
             assert err <= 2e-2
@@ -159,6 +164,53 @@ def test_fused_gather_wait_runs_out_and_reports():
     ref = qo.quantized_matmul(prob["a"].numpy(), prob["codes"][:, :256].numpy(), prob["scales"][:, :256].numpy(), dt, g, 0)
     err = np.abs(c.float().cpu().numpy() - ref.astype(np.float32)).max() / np.abs(ref.astype(np.float32)).max()
     assert err <= 1e-2
+
+
+def test_tagged_gather_wait_runs_out_and_reports():
+    """The same with tagged words: rank 0's second call reads the previous call's rows, of which rank 1's
+    half never arrived; the loads of those words give up after a quarter of a second."""
+    dev = torch.device("cuda:0")
+    dt, g, M = D.int4b, 128, 2
+    prob = synth.make_problem(M, 512, 512, dt, g, seed=4)
+    regions, ctxs = _virtual_group(2, 16, 512, dev, 2)
+    lin = sharded.ShardedQuantizedLinear(float16, dt, g, 512, 512, shard=(2, 0)).to(dev)
+    lin.load_codes(prob["codes"], prob["scales"])
+    ws = ops.get_workspace(dev, ops.workspace_bytes(M, 256, 512, dt, 0, g))
+    assert ops.device_status(ws) == [0, 0, 0, 0]
+    row = ctxs[0].gemm(prob["a"].to(dev), lin)  # call 1: activations from outside, nothing to wait for
+    torch.cuda.synchronize()
+    assert ops.device_status(ws) == [0, 0, 0, 0]
+    ctxs[0].gemm(row, lin)                      # call 2: columns 256.. of call 1's row never arrive
+    torch.cuda.synchronize()
+    st = ops.device_status(ws)
+    assert st[0] == _lib.ST_DEVICE_TIMEOUT and st[1] == 5, st
+    assert ops.device_status(ws) == [0, 0, 0, 0]
+    assert ctxs[0].calls_completed(True) == 2
+    assert int(ws.count_nonzero()) == 0
+
+
+def test_tagged_gather_two_outside_calls_in_a_row():
+    """Two tagged calls in a row that take their activations from outside: the context puts a wait for
+    the first one's rows between them (the rule of the tagged mode), and results stay right."""
+    dev = torch.device("cuda:0")
+    dt, g, M, world = D.uint4b, 128, 1, 2
+    prob = synth.make_problem(M, 1024, 512, dt, g, seed=8)
+    regions, ctxs = _virtual_group(world, 16, 1024, dev, 2)
+    lins = []
+    for r in range(world):
+        lin = sharded.ShardedQuantizedLinear(float16, dt, g, 512, 1024, zero_point=prob["zero_point"], shard=(world, r)).to(dev)
+        lin.load_codes(prob["codes"], prob["scales"])
+        lins.append(lin)
+    x = prob["a"].to(dev)
+    ref = qo.quantized_matmul(prob["a"].numpy(), prob["codes"].numpy(), prob["scales"].numpy(), dt, g,
+                              prob["zero_point"]).astype(np.float32)
+    for _ in range(4):
+        rows = [ctxs[r].gemm(x, lins[r]) for r in range(world)]
+    for r in range(world):
+        got = ctxs[r].fetch(rows[r]).float().cpu().numpy()
+        assert np.abs(got - ref).max() / np.abs(ref).max() <= 1e-2
+        assert ctxs[r].calls_completed(True) == 4
+    assert ops.device_status(ops.get_workspace(dev, 1 << 20)) == [0, 0, 0, 0]
 
 
 @pytest.mark.parametrize("M", [20, 64])

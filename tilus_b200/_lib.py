@@ -21,6 +21,9 @@ class B200QError(RuntimeError):
         self.status = status
 
 
+GATHER_FLAGS, GATHER_TAGGED = 0, 1  # b200q_gather_t.mode
+
+
 class Gather(ctypes.Structure):
     """b200q_gather_t of include/b200q.h."""
     _fields_ = [
@@ -34,6 +37,8 @@ class Gather(ctypes.Structure):
         ("epoch_local", ctypes.c_void_p),
         ("buffer_elems", ctypes.c_int64),
         ("a_prev_offset", ctypes.c_int64),
+        ("mode", ctypes.c_int32),
+        ("reserved", ctypes.c_int32),
     ]
 
 

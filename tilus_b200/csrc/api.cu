@@ -485,14 +485,20 @@ static int run_wide(const void* a, int lda, const void* bq, const void* scales, 
 static int fill_gather_args(const b200q_gather_t* gather, int M, int N, void* workspace, GatherArgs* ga) {
   std::memset(ga, 0, sizeof(*ga));
   if (gather->world < 1 || gather->world > 8 || gather->rank < 0 || gather->rank >= gather->world) return ST_INVALID_ARG;
-  if (gather->ldc < gather->col_offset + N || gather->col_offset < 0 || !gather->flags_local ||
-      !gather->epoch_local || gather->buffer_elems < (int64_t)M * gather->ldc)
-    return ST_INVALID_ARG;
+  if (gather->mode != B200Q_GATHER_FLAGS && gather->mode != B200Q_GATHER_TAGGED) return ST_INVALID_ARG;
+  const bool tagged = gather->mode == B200Q_GATHER_TAGGED;
+  if (gather->ldc < gather->col_offset + N || gather->col_offset < 0 || !gather->epoch_local) return ST_INVALID_ARG;
+  if ((gather->ldc & 1) || (gather->col_offset & 1)) return ST_INVALID_ARG;  // outputs leave in column pairs
+  // dense rows: buffer_elems 16-bit elements between the two buffers; tagged: 64-bit words between the three
+  if (gather->buffer_elems < (int64_t)M * gather->ldc / (tagged ? 2 : 1)) return ST_INVALID_ARG;
+  if (!tagged && !gather->flags_local) return ST_INVALID_ARG;
+  if (gather->a_prev_offset >= 0 && (gather->a_prev_offset & 7)) return ST_INVALID_ARG;
   ga->G = gather->world;
   ga->rank = gather->rank;
   ga->col_off = gather->col_offset;
+  ga->mode = gather->mode;
   for (int g = 0; g < gather->world; ++g) {
-    if (!gather->out[g] || !gather->flag_slot[g]) return ST_INVALID_ARG;
+    if (!gather->out[g] || (!tagged && !gather->flag_slot[g])) return ST_INVALID_ARG;
     ga->out[g] = reinterpret_cast<__half*>(gather->out[g]);
     ga->flag_slot[g] = reinterpret_cast<unsigned*>(gather->flag_slot[g]);
   }
@@ -523,6 +529,10 @@ static int run_stream(const void* a, int lda, const void* bq, const void* scales
   p.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + WS_HEADER_BYTES + ws_counter_bytes(N));
   p.N = N; p.K = K; p.lda = lda; p.ldc = ldc; p.KB = KB; p.NT = N / BLOCK_N;
   p.gshift = gshift_of(group);
+  // Launches that hand rows over between GPUs release the launch of their successor late: measured on two
+  // GPUs, a successor that becomes resident while this launch still waits for its peers costs 0.3 - 0.5 ms
+  // per 128-layer step; launches that wait for nobody lose nothing either way.
+  p.trig = gather ? 1 : 0;
   p.gdiv = group / 128;
   p.S = pl.splits; p.KBc = KB / pl.splits; p.CPC = pl.ctas_per_split;
   if (p.S * p.CPC > 4 * device_info().sm_count) return ST_INVALID_ARG;
@@ -565,7 +575,7 @@ static int run_gemm(const void* a, int lda, const void* bq, const void* scales, 
   if (!a || !bq || !scales || !c) return ST_INVALID_ARG;
   if (((uintptr_t)a | (uintptr_t)bq | (uintptr_t)c) & 15) return ST_INVALID_ARG;
   if (((uintptr_t)scales) & 1) return ST_INVALID_ARG;
-  if (lda < K || ldc < N || (lda % 8) != 0) return ST_INVALID_ARG;
+  if (lda < K || ldc < N || (lda % 8) != 0 || (ldc & 1)) return ST_INVALID_ARG;  // outputs leave in column pairs
   if (pl.kernel == 1 && pl.passes == 2) {
     // the full 256-row tiles on the tcgen05 kernel, the short last tile on the decode kernel
     const int tail = M % 256;
@@ -668,6 +678,7 @@ int b200q_gather_push(const void* shard, int lds, int M, int N_loc, void* worksp
   if (!shard || !gather || M < 1 || N_loc < 8) return ST_INVALID_ARG;
   if ((N_loc % 8) != 0 || (lds % 8) != 0 || lds < N_loc || (((uintptr_t)shard) & 15)) return ST_INVALID_ARG;
   if ((gather->ldc % 8) != 0 || (gather->col_offset % 8) != 0) return ST_INVALID_ARG;
+  if (gather->mode != B200Q_GATHER_FLAGS) return ST_UNSUPPORTED;  // the push kernel writes dense rows
   if (!workspace || workspace_bytes < WS_HEADER_BYTES || ((uintptr_t)workspace & 255)) return ST_WORKSPACE;
   GatherArgs ga;
   const int st = fill_gather_args(gather, M, N_loc, workspace, &ga);

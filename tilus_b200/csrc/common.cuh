@@ -47,9 +47,18 @@ constexpr int stream_gi(int bits) { return bits <= 2 ? 4 : bits <= 5 ? 2 : 1; }
 // columns into the full output row of every rank and then raises its flag on every rank; the
 // next launch waits for all flags before it reads its activations.  The call counter lives on
 // the device (`epoch`), so a launch carries no per-call state and can be replayed from a graph.
+//
+// mode 1, tagged words: no flags.  The row buffers hold 8-byte words {two 16-bit outputs, call
+// number}, three buffers per rank used in turn; a launch stores its columns as such words (one
+// 64-bit store each: value and tag arrive together) into buffer (E + 1) % 3 of every rank, and the
+// next launch polls the words it stages until each carries tag E + 1.  Nothing waits for a whole
+// grid: the hand-over costs one store's flight time.  `out[g]` then points at 64-bit words and
+// `buf_elems` counts words.
+constexpr int GATHER_TAG_BUFFERS = 3;
 struct GatherArgs {
   int G, rank;             // ranks, this rank
   int col_off;             // first column of this rank's shard in the full row
+  int mode;                // 0: dense rows + flags; 1: tagged words (see above)
   __half* out[8];          // row buffer 0 of every rank (peer-mapped); buffer 1 is buf_elems further
   unsigned* flag_slot[8];  // this rank's slot in every rank's flag array (peer-mapped)
   const unsigned* flags;   // this rank's own flag array [G]
@@ -78,6 +87,7 @@ struct StreamParams {
   int pdl;               // launch with programmatic stream serialization
   int ipt_shift;         // log2 of the items per column tile inside a k chunk when that is a power of two, else -1
   int act;               // activation / scale / output dtype: 0 fp16, 1 bf16
+  int trig;              // 1: CTA 0 lets the next kernel of the stream launch only after its own griddepcontrol.wait
   GatherArgs ga;
 };
 

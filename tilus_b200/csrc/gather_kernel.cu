@@ -84,10 +84,48 @@ __global__ void __launch_bounds__(256) gather_push_kernel(const PushParams p) {
   }
 }
 
+// Tagged rows (GatherArgs mode 1) -> dense rows: every 8-byte word {two values, call number} of the latest
+// call's row buffer is read until it carries that call's number (bounded), then its values are written
+// to the local copy.  dst_local == nullptr: wait only.
+__device__ __forceinline__ void collect_tagged(const PushParams& p, unsigned epoch) {
+  const unsigned long long* row = reinterpret_cast<const unsigned long long*>(p.ga.out[p.ga.rank]) +
+                                  (size_t)(epoch % GATHER_TAG_BUFFERS) * (size_t)p.ga.buf_elems;
+  const int vec_per_row = p.ldc / 4;  // two words = four values per step
+  const int total = p.M * vec_per_row;
+  bool waiting = true;  // cleared once a wait has run out
+  for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
+    const int m = idx / vec_per_row, v = idx - m * vec_per_row;
+    const unsigned long long* src = row + (((size_t)m * p.ldc) >> 1) + v * 2;
+    ulonglong2 w;
+    uint64_t t0 = 0;
+    for (int spin = 0;; ++spin) {
+      asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(w.x), "=l"(w.y) : "l"(src) : "memory");
+      if (!waiting || ((unsigned)(w.x >> 32) == epoch && (unsigned)(w.y >> 32) == epoch)) break;
+      uint64_t now;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+      if (spin == 0) t0 = now;
+      else if (now - t0 > 250000000ull) {  // give up for good: report, carry on with what is there
+        atomicExch(p.status, ST_DEVICE_TIMEOUT);
+        p.status[1] = 8;
+        p.status[2] = blockIdx.x;
+        p.status[3] = threadIdx.x;
+        waiting = false;
+        break;
+      }
+    }
+    if (p.dst_local)
+      *reinterpret_cast<uint2*>(p.dst_local + (size_t)m * p.ld_local + v * 4) = make_uint2((uint32_t)w.x, (uint32_t)w.y);
+  }
+}
+
 __global__ void __launch_bounds__(256) gather_collect_kernel(const PushParams p) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");  // this rank's push has completed: the call counter is final
   const unsigned epoch = *reinterpret_cast<volatile const unsigned*>(p.ga.epoch);  // includes this call's push
+  if (p.ga.mode == 1) {
+    if (epoch != 0) collect_tagged(p, epoch);
+    return;
+  }
   wait_flags(p, epoch, 8);
   if (!p.dst_local) return;
   const unsigned short* row = reinterpret_cast<const unsigned short*>(p.ga.out[p.ga.rank]) +
@@ -140,7 +178,7 @@ cudaError_t gather_push_launch(const void* src, int lds, int M, int N_loc, int l
 cudaError_t gather_collect_launch(void* dst_local, int ld_local, int M, int ldc, int* status, const GatherArgs& ga,
                                   cudaStream_t stream) {
   const PushParams p = make_params(nullptr, 0, dst_local, ld_local, M, 0, ldc, status, ga);
-  int grid = (M * (ldc / 8) + 255) / 256;
+  int grid = (M * (ldc / (ga.mode == 1 ? 4 : 8)) + 255) / 256;
   if (grid > 296) grid = 296;
   if (grid < 1) grid = 1;
   return launch_pdl(gather_collect_kernel, grid, p, stream);

@@ -85,17 +85,34 @@ __device__ __forceinline__ unsigned short out_bits(float v) {
   if constexpr (ACT == 0) return __half_as_ushort(__float2half_rn(v));
   else return __bfloat16_as_ushort(__float2bfloat16_rn(v));
 }
-// One output value.  Plain launches write C; launches with a fused all-gather write the value
-// into the full output row of every rank (peer-mapped pointers, stores only).
-template <bool GATHER, int ACT>
-__device__ __forceinline__ void store_out(const StreamParams& p, size_t gather_buf, int m, int n, float v) {
-  const unsigned short h = out_bits<ACT>(v);
-  if constexpr (!GATHER) {
-    reinterpret_cast<unsigned short*>(p.c)[(size_t)m * p.ldc + n] = h;
-  } else {
+// Two adjacent output values (columns n and n + 1 of row m, n even).  Plain launches write C; launches
+// with a fused all-gather write into the full output row of every rank (peer-mapped pointers, stores
+// only): a 4-byte store into the dense row buffer, or - tagged mode - one 64-bit store of the two
+// values with the call number `tag` in the upper half.
+template <int GATHER, int ACT>
+__device__ __forceinline__ void store_pair(const StreamParams& p, size_t gather_buf, unsigned tag, int m, int n,
+                                           float v0, float v1) {
+  const uint32_t h2 = (uint32_t)out_bits<ACT>(v0) | ((uint32_t)out_bits<ACT>(v1) << 16);
+  if constexpr (GATHER == 0) {
+    *reinterpret_cast<uint32_t*>(reinterpret_cast<unsigned short*>(p.c) + (size_t)m * p.ldc + n) = h2;
+  } else if constexpr (GATHER == 1) {
     const size_t off = gather_buf + (size_t)m * p.ldc + p.ga.col_off + n;
-    for (int g = 0; g < p.ga.G; ++g) reinterpret_cast<unsigned short*>(p.ga.out[g])[off] = h;
+    for (int g = 0; g < p.ga.G; ++g)
+      *reinterpret_cast<uint32_t*>(reinterpret_cast<unsigned short*>(p.ga.out[g]) + off) = h2;
+  } else {
+    const size_t word = gather_buf + (((size_t)m * p.ldc + p.ga.col_off + n) >> 1);
+    const unsigned long long v = (unsigned long long)h2 | ((unsigned long long)tag << 32);
+    for (int g = 0; g < p.ga.G; ++g)
+      asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(reinterpret_cast<unsigned long long*>(p.ga.out[g]) + word),
+                   "l"(v)
+                   : "memory");
   }
+}
+// two tagged words (16 bytes) as they are now in memory; each 64-bit half is read atomically
+__device__ __forceinline__ ulonglong2 ld_tagged2(const unsigned long long* src) {
+  ulonglong2 v;
+  asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(v.x), "=l"(v.y) : "l"(src) : "memory");
+  return v;
 }
 // a scale of the activation dtype (raw 16 bits in the shared-memory cache) as fp32
 template <int ACT>
@@ -136,7 +153,7 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
 // one in the stream - share an SM.  MT = 2 (up to 16 rows): one CTA per SM with all of its registers
 // and shared memory, which keeps the two 8-row accumulator sets in registers and a K chunk of the
 // 16 activation rows next to the rings.
-template <int VAR, int MT, bool GATHER, int ACT>
+template <int VAR, int MT, int GATHER, int ACT>
 __global__ void __launch_bounds__(stream_warps(MT) * 32, MT == 1 ? 2 : 1) stream_kernel(const StreamParams p) {
   constexpr int B = var_bits(VAR);
   constexpr int MP = 8 * MT;
@@ -204,8 +221,11 @@ __global__ void __launch_bounds__(stream_warps(MT) * 32, MT == 1 ? 2 : 1) stream
   const int cB = max(v1 - max(v0, n_left), 0);
   const int tileB = own_tile0 + div_ipt(oB, qB);
   const int n_items = cA + cB;
-  // the next kernel of the stream may become resident as soon as there is room for it
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // The next kernel of the stream may become resident as soon as there is room for it - once every
+  // CTA of this launch has said so.  p.trig == 1: CTA 0 says so only after its own wait for the
+  // previous kernel, which keeps the next kernel's CTAs off the SMs until the previous one has gone.
+  const bool late_trigger = p.trig == 1 && blockIdx.x == 0;
+  if (!late_trigger) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   const uint32_t bar0 = smem_base + warp * 64;
   const uint32_t ring_s = smem_base + HDR + warp * NST * SLOT_BYTES;
@@ -271,6 +291,7 @@ __global__ void __launch_bounds__(stream_warps(MT) * 32, MT == 1 ? 2 : 1) stream
   for (int idx = tid; idx < p.T_own * 16 * MP; idx += NWARPS * 32) sAcc[idx] = 0.f;
   // everything below may read what the previous kernel of the stream wrote
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (late_trigger) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   // ---- fused all-gather: this launch is fused call number E + 1 of the rank (E is kept on the
   // device, so that the same launch can be replayed from a CUDA graph).  It may start once every
@@ -280,7 +301,17 @@ __global__ void __launch_bounds__(stream_warps(MT) * 32, MT == 1 ? 2 : 1) stream
   const unsigned short* a_base = reinterpret_cast<const unsigned short*>(p.a);
   size_t gather_buf = 0;  // element offset of the row buffer this call writes, inside every rank's region
   unsigned epoch = 0;
-  if (GATHER) {
+  const unsigned long long* a_tagged = nullptr;  // tagged mode: the activations as {two values, tag} words
+  if constexpr (GATHER == 2) {
+    // Tagged words: the call number was stored by the last CTA of this rank's previous fused launch,
+    // which has completed (stream order).  Nothing to wait for here: the staging loop polls the words
+    // it reads, and the buffer written below was last read two calls ago (see GatherArgs).
+    epoch = *reinterpret_cast<volatile const unsigned*>(p.ga.epoch);
+    gather_buf = (size_t)((epoch + 1) % GATHER_TAG_BUFFERS) * (size_t)p.ga.buf_elems;
+    if (p.ga.a_prev_off >= 0)
+      a_tagged = reinterpret_cast<const unsigned long long*>(p.ga.out[p.ga.rank]) +
+                 (size_t)(epoch % GATHER_TAG_BUFFERS) * (size_t)p.ga.buf_elems + (size_t)(p.ga.a_prev_off >> 1);
+  } else if constexpr (GATHER == 1) {
     // The rank's own flag slot holds the number of its completed fused calls (its last CTA raises it
     // with the others), so one round of loads brings both the epoch and the peers' progress.
     __shared__ unsigned s_epoch_word;
@@ -317,6 +348,7 @@ __global__ void __launch_bounds__(stream_warps(MT) * 32, MT == 1 ? 2 : 1) stream
       __syncthreads();
     }
   }
+  const unsigned out_tag = epoch + 1;  // tagged mode: what this call's output words carry
 
   // ---- stage the activation chunk A[0:M, kb_base*512 : +KBc*512] as fp16 (pre-scaled where the
   // weight type needs it), and the zero-point term of every 128-row group ----
@@ -342,10 +374,12 @@ __global__ void __launch_bounds__(stream_warps(MT) * 32, MT == 1 ? 2 : 1) stream
     // four loads in flight per thread: the staging pass costs one memory round trip per four
     // 16-byte pieces instead of one per piece
     constexpr int SB = 4;
+    bool tag_wait = true;  // tagged mode: cleared once a wait has run out
     int m = 0, vv = tid;  // idx = m * vec_per_row + vv
     for (int idx0 = tid; idx0 < total; idx0 += SB * NWARPS * 32) {
       uint4 vq[SB];
       int mq[SB], kq[SB];
+      ulonglong2 tlo[GATHER == 2 ? SB : 1], thi[GATHER == 2 ? SB : 1];  // tagged mode: the words as loaded
 #pragma unroll
       for (int u = 0; u < SB; ++u) {
         const int idx = idx0 + u * NWARPS * 32;
@@ -353,8 +387,41 @@ __global__ void __launch_bounds__(stream_warps(MT) * 32, MT == 1 ? 2 : 1) stream
         mq[u] = m; kq[u] = vv * 8;
         vv += NWARPS * 32;
         if (idx < total) {
-          const uint4* src = reinterpret_cast<const uint4*>(a_base + (size_t)mq[u] * p.lda + (size_t)kb_base * 512 + kq[u]);
-          vq[u] = GATHER ? __ldcg(src) : __ldg(src);  // gathered rows were written through L2 by other GPUs
+          if (GATHER == 2 && a_tagged != nullptr) {
+            // eight activations = four tagged words, checked once all loads of the batch are in flight
+            const unsigned long long* src = a_tagged + (((size_t)mq[u] * p.lda + (size_t)kb_base * 512 + kq[u]) >> 1);
+            tlo[GATHER == 2 ? u : 0] = ld_tagged2(src);
+            thi[GATHER == 2 ? u : 0] = ld_tagged2(src + 2);
+          } else {
+            const uint4* src = reinterpret_cast<const uint4*>(a_base + (size_t)mq[u] * p.lda + (size_t)kb_base * 512 + kq[u]);
+            vq[u] = GATHER ? __ldcg(src) : __ldg(src);  // gathered rows were written through L2 by other GPUs
+          }
+        }
+      }
+      if (GATHER == 2 && a_tagged != nullptr) {
+        // every word must carry the previous call's number; a word that does not yet is read again (bounded)
+#pragma unroll
+        for (int u = 0; u < SB; ++u) {
+          if (idx0 + u * NWARPS * 32 >= total) continue;
+          ulonglong2 lo = tlo[GATHER == 2 ? u : 0], hi = thi[GATHER == 2 ? u : 0];
+          const unsigned long long* src = a_tagged + (((size_t)mq[u] * p.lda + (size_t)kb_base * 512 + kq[u]) >> 1);
+          uint64_t t0 = 0;
+          for (int spin = 0; tag_wait && ((unsigned)(lo.x >> 32) != epoch || (unsigned)(lo.y >> 32) != epoch ||
+                                          (unsigned)(hi.x >> 32) != epoch || (unsigned)(hi.y >> 32) != epoch); ++spin) {
+            uint64_t now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            if (spin == 0) t0 = now;
+            else if (now - t0 > 250000000ull) {  // give up for good: report, carry on with what is there
+              atomicExch(p.status, ST_DEVICE_TIMEOUT);
+              p.status[1] = 5;  // where: wait for a peer's columns
+              p.status[2] = blockIdx.x;
+              p.status[3] = tid;
+              tag_wait = false;
+              break;
+            }
+            lo = ld_tagged2(src); hi = ld_tagged2(src + 2);
+          }
+          vq[u] = make_uint4((uint32_t)lo.x, (uint32_t)lo.y, (uint32_t)hi.x, (uint32_t)hi.y);
         }
       }
 #pragma unroll
@@ -537,15 +604,22 @@ __global__ void __launch_bounds__(stream_warps(MT) * 32, MT == 1 ? 2 : 1) stream
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt) {
             const int m0 = mt * 8 + 2 * j;
-            if (m0 < p.M) {
+            const bool rows = m0 < p.M;
 #pragma unroll
-              for (int h = 0; h < 2; ++h) {
-                float2* src = reinterpret_cast<float2*>(dst + (r + h * 8) * MP + m0);
-                const float2 v = __ldcg(src);
+            for (int h = 0; h < 2; ++h) {
+              float2* src = reinterpret_cast<float2*>(dst + (r + h * 8) * MP + m0);
+              float2 v = make_float2(0.f, 0.f);
+              if (rows) {
+                v = __ldcg(src);
                 __stcg(src, make_float2(0.f, 0.f));
-                const int n = cur_tile * 16 + r + h * 8;
-                store_out<GATHER, ACT>(p, gather_buf, m0, n, v.x);
-                if (m0 + 1 < p.M) store_out<GATHER, ACT>(p, gather_buf, m0 + 1, n, v.y);
+              }
+              // columns r and r ^ 1 sit four lanes apart (same rows): the even one writes row m0 of
+              // both columns, the odd one row m0 + 1
+              const float ox = __shfl_xor_sync(0xffffffffu, v.x, 4), oy = __shfl_xor_sync(0xffffffffu, v.y, 4);
+              const int nb = cur_tile * 16 + (r & ~1) + h * 8;
+              if (rows) {
+                if (!(r & 1)) store_pair<GATHER, ACT>(p, gather_buf, out_tag, m0, nb, v.x, ox);
+                else if (m0 + 1 < p.M) store_pair<GATHER, ACT>(p, gather_buf, out_tag, m0 + 1, nb, oy, v.y);
               }
             }
           }
@@ -579,7 +653,8 @@ __global__ void __launch_bounds__(stream_warps(MT) * 32, MT == 1 ? 2 : 1) stream
     const int n0 = own_tile0 * 16, ncols = p.T_own * 16;
     if (p.S == 1) {  // all of K was here: write C
       for (int m = 0; m < p.M; ++m)
-        for (int n = tid; n < ncols; n += NWARPS * 32) store_out<GATHER, ACT>(p, gather_buf, m, n0 + n, sAcc[n * MP + m]);
+        for (int n = 2 * tid; n < ncols; n += 2 * NWARPS * 32)
+          store_pair<GATHER, ACT>(p, gather_buf, out_tag, m, n0 + n, sAcc[n * MP + m], sAcc[(n + 1) * MP + m]);
     } else {
       // other k chunks hold the rest: meet in the global scratch; the last chunk to arrive converts
       for (int idx = tid * 4; idx < ncols * MP; idx += NWARPS * 32 * 4)
@@ -604,15 +679,28 @@ __global__ void __launch_bounds__(stream_warps(MT) * 32, MT == 1 ? 2 : 1) stream
         const int t = idx / (16 * MP);
         if (!s_last[t]) continue;
         if (!fenced) { __threadfence(); fenced = true; }
-        const int m = idx % MP, n = n0 + idx / MP;
+        const int m = idx % MP, col = idx / MP;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
         if (m < p.M) {
           float4* src = reinterpret_cast<float4*>(p.partial + (size_t)n0 * MP + idx);
-          const float4 v = __ldcg(src);
+          v = __ldcg(src);
           __stcg(src, make_float4(0.f, 0.f, 0.f, 0.f));
-          store_out<GATHER, ACT>(p, gather_buf, m, n, v.x);
-          if (m + 1 < p.M) store_out<GATHER, ACT>(p, gather_buf, m + 1, n, v.y);
-          if (m + 2 < p.M) store_out<GATHER, ACT>(p, gather_buf, m + 2, n, v.z);
-          if (m + 3 < p.M) store_out<GATHER, ACT>(p, gather_buf, m + 3, n, v.w);
+        }
+        // the same four rows of column col ^ 1 are held MP / 4 threads away (a warp lies inside one tile
+        // and takes this branch as a whole): the even column's thread writes rows m and m + 2 of both
+        // columns, the odd one's rows m + 1 and m + 3
+        float4 o;
+        o.x = __shfl_xor_sync(0xffffffffu, v.x, MP / 4); o.y = __shfl_xor_sync(0xffffffffu, v.y, MP / 4);
+        o.z = __shfl_xor_sync(0xffffffffu, v.z, MP / 4); o.w = __shfl_xor_sync(0xffffffffu, v.w, MP / 4);
+        if (m < p.M) {
+          const int nb = n0 + (col & ~1);
+          if (!(col & 1)) {
+            store_pair<GATHER, ACT>(p, gather_buf, out_tag, m, nb, v.x, o.x);
+            if (m + 2 < p.M) store_pair<GATHER, ACT>(p, gather_buf, out_tag, m + 2, nb, v.z, o.z);
+          } else {
+            if (m + 1 < p.M) store_pair<GATHER, ACT>(p, gather_buf, out_tag, m + 1, nb, o.y, v.y);
+            if (m + 3 < p.M) store_pair<GATHER, ACT>(p, gather_buf, out_tag, m + 3, nb, o.w, v.w);
+          }
         }
         if ((idx % (16 * MP)) == 0) p.counters[own_tile0 + t] = 0;
       }
@@ -625,7 +713,15 @@ __global__ void __launch_bounds__(stream_warps(MT) * 32, MT == 1 ? 2 : 1) stream
   // every CTA's stores are visible to whoever acquires the flag. ----
   if (GATHER) {
     __syncthreads();
-    if (tid == 0) {
+    if (tid == 0 && GATHER == 2) {
+      // tagged words need no release: every word announces itself.  The last CTA only moves the call
+      // counter on for this rank's next launch, which starts after this one has completed.
+      unsigned* done = p.ga.epoch + 8;  // arrival counter in the rank's region
+      if (atomicAdd(done, 1u) == gridDim.x - 1) {
+        atomicExch(done, 0u);
+        *p.ga.epoch = epoch + 1;
+      }
+    } else if (tid == 0) {
       // release at GPU scope what this CTA's threads stored (ordered before by the barrier), acquire
       // what the CTAs that arrived earlier released
       unsigned arrived;
@@ -641,7 +737,7 @@ __global__ void __launch_bounds__(stream_warps(MT) * 32, MT == 1 ? 2 : 1) stream
   }
 }
 
-template <int VAR, int MT, bool GATHER, int ACT>
+template <int VAR, int MT, int GATHER, int ACT>
 static cudaError_t launch_one(const StreamParams& p, int smem_bytes, cudaStream_t stream) {
   auto kern = stream_kernel<VAR, MT, GATHER, ACT>;
   static int configured_smem[16] = {0};
@@ -668,7 +764,7 @@ static cudaError_t launch_one(const StreamParams& p, int smem_bytes, cudaStream_
   return cudaLaunchKernelEx(&cfg, kern, p);
 }
 
-template <int VAR, int MT, bool GATHER>
+template <int VAR, int MT, int GATHER>
 static cudaError_t launch_act(const StreamParams& p, int smem_bytes, cudaStream_t stream) {
   return p.act == 0 ? launch_one<VAR, MT, GATHER, 0>(p, smem_bytes, stream)
                     : launch_one<VAR, MT, GATHER, 1>(p, smem_bytes, stream);
@@ -678,9 +774,11 @@ template <int VAR>
 static cudaError_t launch_var(int var, const StreamParams& p, int mt, int smem_bytes, cudaStream_t stream) {
   if constexpr (VAR % B200Q_NPARTS == B200Q_PART) {
     if (var == VAR) {
+      if (p.ga.G > 0 && p.ga.mode == 1)
+        return mt == 1 ? launch_act<VAR, 1, 2>(p, smem_bytes, stream) : launch_act<VAR, 2, 2>(p, smem_bytes, stream);
       if (p.ga.G > 0)
-        return mt == 1 ? launch_act<VAR, 1, true>(p, smem_bytes, stream) : launch_act<VAR, 2, true>(p, smem_bytes, stream);
-      return mt == 1 ? launch_act<VAR, 1, false>(p, smem_bytes, stream) : launch_act<VAR, 2, false>(p, smem_bytes, stream);
+        return mt == 1 ? launch_act<VAR, 1, 1>(p, smem_bytes, stream) : launch_act<VAR, 2, 1>(p, smem_bytes, stream);
+      return mt == 1 ? launch_act<VAR, 1, 0>(p, smem_bytes, stream) : launch_act<VAR, 2, 0>(p, smem_bytes, stream);
     }
   }
   if constexpr (VAR + 1 < VAR_COUNT) return launch_var<VAR + 1>(var, p, mt, smem_bytes, stream);

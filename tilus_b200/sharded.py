@@ -102,12 +102,13 @@ class GatheredRow:
     it, as the activations of the next call.  Which of the two row buffers holds it is only known
     on the device; PeerGather.fetch brings it to a tensor."""
 
-    def __init__(self, rows: int, row_stride: int, col_start: int, width: int):
+    def __init__(self, rows: int, row_stride: int, col_start: int, width: int, tagged: bool = False):
         self.rows, self.row_stride, self.col_start, self.width = rows, row_stride, col_start, width
+        self.tagged = tagged  # which of the context's two hand-over protocols produced it
 
     def cols(self, start: int, stop: int) -> "GatheredRow":
         assert 0 <= start < stop <= self.width and start % 8 == 0
-        return GatheredRow(self.rows, self.row_stride, self.col_start + start, stop - start)
+        return GatheredRow(self.rows, self.row_stride, self.col_start + start, stop - start, self.tagged)
 
 
 class PeerGather:
@@ -121,14 +122,23 @@ class PeerGather:
     every rank; the call counter lives on the device, so the calls carry no per-call state and
     a sequence of them can be captured in a CUDA graph and replayed.  All ranks must make the
     same sequence of calls.
+
+    Batches of at most `tagged_rows` rows (default: every fused call, M <= 16) use the tagged hand-over
+    instead (B200Q_GATHER_TAGGED): three more row buffers of 8-byte words {two outputs, call number} and
+    a call counter of their own; no flags, no grid-wide wait - the next call polls the words it reads.
+    Measured on two B200s over NVLink (128-linear decode stack): 1.71 -> 1.51 ms per step at M = 1,
+    1.80 -> 1.66 ms at M = 8.
     """
 
-    FLAGS_OFF, EPOCH_OFF, ROWS_OFF = 0, 64, 256
+    FLAGS_OFF, EPOCH_OFF, TAG_EPOCH_OFF, ROWS_OFF = 0, 64, 128, 256
+    TAG_BUFFERS = 3
 
-    def __init__(self, world: int, rank: int, ptrs, max_rows: int, max_cols: int, device):
+    def __init__(self, world: int, rank: int, ptrs, max_rows: int, max_cols: int, device, tagged_rows: int = 16):
         assert 1 <= world <= 8 and len(ptrs) == world
         self.world, self.rank, self.ptrs = world, rank, list(ptrs)
         self.max_rows, self.max_cols = max_rows, max_cols
+        self.tagged_rows = min(tagged_rows, 16, max_rows)
+        self._tag_prev = None  # (rows, row width, took its activations from outside) of the latest tagged call
         self.device = torch.device(device)
         self._owned = None     # this rank's region, if allocated by create()
         self._full = {}        # gathered outputs of calls with more than 16 rows, per shape
@@ -136,17 +146,22 @@ class PeerGather:
         self.dtype = torch.float16  # dtype of the latest call's output rows
 
     @staticmethod
-    def region_bytes(max_rows: int, max_cols: int) -> int:
-        return PeerGather.ROWS_OFF + 2 * max_rows * max_cols * 2
+    def _tag_off(max_rows: int, max_cols: int) -> int:
+        return (PeerGather.ROWS_OFF + 2 * max_rows * max_cols * 2 + 255) // 256 * 256
+
+    @staticmethod
+    def region_bytes(max_rows: int, max_cols: int, tagged_rows: int = 16) -> int:
+        tagged_rows = min(tagged_rows, 16, max_rows)
+        return PeerGather._tag_off(max_rows, max_cols) + PeerGather.TAG_BUFFERS * tagged_rows * (max_cols // 2) * 8
 
     @classmethod
-    def create(cls, max_rows: int, max_cols: int, device, group=None):
+    def create(cls, max_rows: int, max_cols: int, device, group=None, tagged_rows: int = 16):
         """Allocates this rank's region with the library's peer allocator (zeroed) and maps every
         other rank's region through CUDA IPC (one process per GPU, one node)."""
         lib = _lib.load()
         world = dist.get_world_size(group) if dist.is_initialized() else 1
         rank = dist.get_rank(group) if dist.is_initialized() else 0
-        nbytes = cls.region_bytes(max_rows, max_cols)
+        nbytes = cls.region_bytes(max_rows, max_cols, tagged_rows)
         with torch.cuda.device(device):
             mine = ctypes.c_void_p()
             _lib.check(lib.b200q_peer_alloc(nbytes, ctypes.byref(mine)))
@@ -163,7 +178,7 @@ class PeerGather:
                     peer = ctypes.c_void_p()
                     _lib.check(lib.b200q_peer_open(ctypes.create_string_buffer(handles[g], 64), ctypes.byref(peer)))
                     ptrs.append(peer.value)
-        ctx = cls(world, rank, ptrs, max_rows, max_cols, device)
+        ctx = cls(world, rank, ptrs, max_rows, max_cols, device, tagged_rows)
         ctx._owned = mine.value
         ctx._opened = [p for g, p in enumerate(ptrs) if g != rank]
         ctx._group = group
@@ -187,9 +202,18 @@ class PeerGather:
     def _view(self, byte_off: int, nbytes: int) -> torch.Tensor:
         return torch.as_tensor(_RawCudaBuffer(self.ptrs[self.rank] + byte_off, nbytes), device=self.device)
 
-    def _desc(self, N_full: int, col_offset: int) -> "_lib.Gather":
+    def _desc(self, N_full: int, col_offset: int, tagged: bool = False) -> "_lib.Gather":
         g = _lib.Gather()
         g.world, g.rank, g.ldc, g.col_offset = self.world, self.rank, N_full, col_offset
+        g.a_prev_offset = -1
+        if tagged:
+            off = self._tag_off(self.max_rows, self.max_cols)
+            g.mode = _lib.GATHER_TAGGED
+            for r in range(self.world):
+                g.out[r] = self.ptrs[r] + off
+            g.epoch_local = self.ptrs[self.rank] + self.TAG_EPOCH_OFF
+            g.buffer_elems = self.tagged_rows * (self.max_cols // 2)
+            return g
         for r in range(self.world):
             g.out[r] = self.ptrs[r] + self.ROWS_OFF
             g.flag_slot[r] = self.ptrs[r] + self.FLAGS_OFF + 4 * self.rank
@@ -221,7 +245,8 @@ class PeerGather:
             M = x.shape[0]
         if M > self.max_rows or N_full > self.max_cols:
             raise ValueError("batch or layer width beyond the context's buffer size")
-        g = self._desc(N_full, layer.n0)
+        tagged = M <= self.tagged_rows and self.world > 1  # a single rank has no hand-over to shorten
+        g = self._desc(N_full, layer.n0, tagged)
         self.dtype = local.scales.dtype
         if M > 16:
             if isinstance(x, GatheredRow):
@@ -239,9 +264,17 @@ class PeerGather:
             lda, a_ptr = x.row_stride, None
             if x.width != K:
                 raise ValueError(f"expected {K} input features, got {x.width}")
+            if x.tagged != tagged:
+                raise ValueError("the previous call's rows were handed over with the other protocol")
             g.a_prev_offset = x.col_start
         else:
             lda, a_ptr = x.stride(0), x.data_ptr()
+            if tagged and self._tag_prev is not None and self._tag_prev[2]:
+                # two tagged calls in a row that take their activations from outside: make sure every rank
+                # has written the first one's rows (so it has finished reading the buffer written next)
+                self.collect(None, self._tag_prev[0], self._tag_prev[1], tagged=True)
+        if tagged:
+            self._tag_prev = (M, N_full, not isinstance(x, GatheredRow))
         with torch.cuda.device(self.device):
             ws = ops.get_workspace(self.device, ops.workspace_bytes(M, N_loc, K, dt, zp, grp))
             st = lib.b200q_gemm_gather(a_ptr, lda, local.quantized_weight.data_ptr(), local.scales.data_ptr(), M,
@@ -249,7 +282,7 @@ class PeerGather:
                                        ws.numel(),
                                        torch.cuda.current_stream(self.device).cuda_stream, ctypes.byref(g))
         _lib.check(st)
-        return GatheredRow(M, N_full, 0, N_full)
+        return GatheredRow(M, N_full, 0, N_full, tagged)
 
     def push(self, shard: torch.Tensor, layer: "ShardedQuantizedLinear"):
         """First half of a gathered call with more than 16 rows: this rank's shard [M, N/G] to every rank."""
@@ -260,24 +293,26 @@ class PeerGather:
                 shard.data_ptr(), shard.stride(0), shard.shape[0], shard.shape[1], ws.data_ptr(), ws.numel(),
                 torch.cuda.current_stream(self.device).cuda_stream, ctypes.byref(g)))
 
-    def collect(self, full: torch.Tensor, M: int, N_full: int):
-        """Second half: wait for every rank's shard of the call just pushed, copy the rows to `full`."""
-        g = self._desc(N_full, 0)
+    def collect(self, full, M: int, N_full: int, tagged: bool = False):
+        """Second half: wait for every rank's shard of the call just pushed (or, tagged, of the latest
+        fused call), copy the rows to `full` (None: wait only)."""
+        g = self._desc(N_full, 0, tagged)
         with torch.cuda.device(self.device):
             ws = ops.get_workspace(self.device, 1 << 20)
             _lib.check(_lib.load().b200q_gather_collect(
-                full.data_ptr(), full.stride(0), M, ws.data_ptr(), ws.numel(),
-                torch.cuda.current_stream(self.device).cuda_stream, ctypes.byref(g)))
+                full.data_ptr() if full is not None else None, full.stride(0) if full is not None else 0, M,
+                ws.data_ptr(), ws.numel(), torch.cuda.current_stream(self.device).cuda_stream, ctypes.byref(g)))
 
     @staticmethod
     def cols(row, start: int, stop: int):
         """Columns [start, stop) of what `gemm` returned, as the activations of the next call."""
         return row.cols(start, stop) if isinstance(row, GatheredRow) else row[:, start:stop]
 
-    def calls_completed(self) -> int:
-        """The device-side call counter (synchronises the current stream)."""
+    def calls_completed(self, tagged: bool = False) -> int:
+        """The device-side call counter of the flag protocol (or of the tagged one); synchronises the
+        current stream."""
         torch.cuda.current_stream(self.device).synchronize()
-        return int(self._view(self.EPOCH_OFF, 4).view(torch.int32).item())
+        return int(self._view(self.TAG_EPOCH_OFF if tagged else self.EPOCH_OFF, 4).view(torch.int32).item())
 
     def wait_all_ranks(self, timeout_s: float = 2.0) -> int:
         """Waits until every rank's columns of this rank's latest call have landed here: this rank's
@@ -302,6 +337,14 @@ class PeerGather:
         if not isinstance(row, GatheredRow):  # more than 16 rows: already collected on the device
             torch.cuda.current_stream(self.device).synchronize()
             return row.clone()
+        if row.tagged:  # the collect kernel waits for every word's tag and writes dense rows
+            full = torch.empty(row.rows, row.row_stride, dtype=self.dtype, device=self.device)
+            self.collect(full, row.rows, row.row_stride, tagged=True)
+            torch.cuda.current_stream(self.device).synchronize()
+            st = ops.device_status(ops.get_workspace(self.device, 1 << 20))
+            if st[0] != 0:
+                raise _lib.B200QError(_lib.ST_DEVICE_TIMEOUT, f"tagged gather: rows never completed, status {st}")
+            return full[:, row.col_start : row.col_start + row.width].clone()
         parity = self.wait_all_ranks() & 1
         nbytes = self.max_rows * self.max_cols * 2
         buf = self._view(self.ROWS_OFF + parity * nbytes, nbytes).view(self.dtype)
