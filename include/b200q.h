@@ -97,12 +97,21 @@ int b200q_gemm(const void* a, int lda, const void* bq, const void* scales, void*
                void* stream);
 
 /* The same GEMM for a host that keeps activations and results in host memory (no counterpart in
- * the reference, whose operator takes device tensors): copies A[M, K] from `a_host` (row stride
- * lda, pinned memory if the copy is to be asynchronous) into `a_staging` (device, M*K 16-bit
- * elements) and runs b200q_gemm.  A result of at most 1 MiB whose `c_host` (row stride ldc) is
- * pinned memory the GPU can address is written there by the kernel itself; otherwise the GEMM
- * writes `c_staging` (device, M*N elements) and a copy to `c_host` follows.  All of it is queued
- * on `stream` by this one call; the caller synchronises before it reads c_host. */
+ * the reference, whose operator takes device tensors): brings A[M, K] from `a_host` (row stride
+ * lda) into `a_staging` (device, M*K 16-bit elements, 16-byte aligned) and runs b200q_gemm.  A result
+ * of at most 1 MiB whose `c_host` (row stride ldc) is pinned memory the GPU can address is written
+ * there by the kernel itself; otherwise the GEMM writes `c_staging` (device, M*N elements) and a
+ * copy to `c_host` follows.  All of it is queued on `stream` by this one call; the caller
+ * synchronises before it reads c_host.
+ *
+ * How A travels depends on where it lies.  Pageable memory, or more than 256 KB: a copy operation
+ * on the stream.  Pinned memory the GPU can address: a small kernel whose PCIe reads run under the
+ * previous kernel of the stream.  Pinned memory and a decode batch (M <= 16 on the stream kernel, result
+ * written straight to pinned c_host): no separate operation at all - the first CTAs of the GEMV kernel
+ * fetch the rows, the others wait for them (bounded, status[1] = 6), and consecutive such calls overlap on
+ * the GPU: a call does not wait for the kernel before it until it writes its outputs, which therefore
+ * still land in call order.  For that, `a_staging` and `workspace` must belong to the host calls of this
+ * stream alone: no other kernel may read `a_staging` while such calls are queued. */
 int b200q_gemm_host(const void* a_host, int lda, const void* bq, const void* scales, void* c_host, int ldc, int M,
                     int N, int K, int wtype, int zero_point, int group, int act_dtype, void* a_staging,
                     void* c_staging, void* workspace, size_t workspace_bytes, void* stream);

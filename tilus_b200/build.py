@@ -47,6 +47,7 @@ def _jobs():
     jobs.append(("quantize_kernel.cu", "quantize.o", []))
     jobs.append(("cast_kernel.cu", "cast.o", []))
     jobs.append(("gather_kernel.cu", "gather.o", []))
+    jobs.append(("fetch_kernel.cu", "fetch.o", []))
     jobs.append(("api.cu", "api.o", [f"-DB200Q_NPARTS={NPARTS}"]))
     return jobs
 

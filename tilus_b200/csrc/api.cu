@@ -22,6 +22,7 @@ B200Q_DECL_SPART(0) B200Q_DECL_SPART(1) B200Q_DECL_SPART(2) B200Q_DECL_SPART(3)
 B200Q_DECL_SPART(4) B200Q_DECL_SPART(5) B200Q_DECL_SPART(6) B200Q_DECL_SPART(7)
 cudaError_t dequant_launch(int var, const DequantParams& p, cudaStream_t stream);
 cudaError_t cast_launch(const CastParams& p, int act, bool swiglu, cudaStream_t stream);
+cudaError_t host_fetch_launch(const void* src, int lds, void* dst, int M, int K, cudaStream_t stream);
 cudaError_t gather_push_launch(const void* src, int lds, int M, int N_loc, int ldc, int* status, const GatherArgs& ga,
                                cudaStream_t stream);
 cudaError_t gather_collect_launch(void* dst_local, int ld_local, int M, int ldc, int* status, const GatherArgs& ga,
@@ -323,7 +324,7 @@ static int umma_tail(int tiles, int grid, int kblocks, int uniform_splits, int N
 // fp32 scratch of the transposed tcgen05 kernel: one [tm][128] slab per tile slot
 static size_t umma_partial_bytes(int slots, int tm) { return (size_t)slots * tm * 128 * sizeof(float); }
 
-static int make_plan(int M, int N, int K, int var, int group, b200q_plan_t* pl) {
+static int make_plan_uncached(int M, int N, int K, int var, int group, b200q_plan_t* pl) {
   const DeviceInfo di = device_info();
   std::memset(pl, 0, sizeof(*pl));
   const int bits = var_bits(var);
@@ -365,6 +366,30 @@ static int make_plan(int M, int N, int K, int var, int group, b200q_plan_t* pl) 
   if (pl->passes == 2 && need < stream_workspace_bytes(N)) need = stream_workspace_bytes(N);
   pl->workspace_bytes = need;
   return ST_OK;
+}
+
+// The table is a pure function of the shape (and of the device's SM count and shared memory, which
+// device_info caches for the current device), and a serving loop asks for the same few shapes over
+// and over: the latest results are kept per thread.
+static int make_plan(int M, int N, int K, int var, int group, b200q_plan_t* pl) {
+  struct Entry { int dev, M, N, K, var, group, status; b200q_plan_t plan; };
+  static thread_local Entry cache[16];
+  static thread_local int used = 0, next = 0;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  for (int i = 0; i < used; ++i) {
+    const Entry& e = cache[i];
+    if (e.M == M && e.N == N && e.K == K && e.var == var && e.group == group && e.dev == dev) {
+      *pl = e.plan;
+      return e.status;
+    }
+  }
+  const int status = make_plan_uncached(M, N, K, var, group, pl);
+  Entry& e = cache[next];
+  e.dev = dev; e.M = M; e.N = N; e.K = K; e.var = var; e.group = group; e.status = status; e.plan = *pl;
+  next = (next + 1) % 16;
+  if (used < 16) ++used;
+  return status;
 }
 
 // row tiles per raster group of the transposed tcgen05 kernel: as many as keep one group's
@@ -512,7 +537,10 @@ static int fill_gather_args(const b200q_gather_t* gather, int M, int N, void* wo
 
 static int run_stream(const void* a, int lda, const void* bq, const void* scales, void* c, int ldc, int M, int N,
                       int K, int var, int group, int act, void* workspace, size_t ws_bytes, cudaStream_t stream,
-                      const b200q_plan_t& pl, const b200q_gather_t* gather = nullptr) {
+                      const b200q_plan_t& pl, const b200q_gather_t* gather = nullptr, const void* a_host = nullptr,
+                      int lda_host = 0) {
+  // a_host: device-side address of activations in pinned host memory (row stride lda_host); `a` is then
+  // the dense [M, K] device staging the kernel's first CTAs fill (see StreamParams)
   const int bits = var_bits(var);
   const int KB = K / BLOCK_K;
   if (!stream_takes(K, group)) return ST_UNSUPPORTED;
@@ -548,6 +576,16 @@ static int run_stream(const void* a, int lda, const void* bq, const void* scales
         if ((1 << sh) == ipt) p.ipt_shift = sh;
   }
   std::memset(&p.ga, 0, sizeof(p.ga));
+  p.a_host = nullptr; p.fetch_flag = nullptr; p.fetch_ctas = 0; p.nowait = 0;
+  if (a_host) {
+    if (gather || M > stream_rows_per_pass(M)) return ST_INVALID_ARG;
+    const int per_cta = stream_warps(stream_mt(M)) * 32 * 4;  // 16-byte pieces one CTA fetches
+    p.a_host = reinterpret_cast<const __half*>(a_host);
+    p.lda = lda_host;
+    p.fetch_flag = reinterpret_cast<unsigned*>(workspace) + 16;  // words 16, 17 of the status header
+    p.fetch_ctas = (M * (K / 8) + per_cta - 1) / per_cta;
+    if (p.fetch_ctas > p.S * p.CPC) return ST_INVALID_ARG;
+  }
   if (gather) {
     if (M > 16) return ST_INVALID_ARG;
     const int gst = fill_gather_args(gather, M, N, workspace, &p.ga);
@@ -557,10 +595,11 @@ static int run_stream(const void* a, int lda, const void* bq, const void* scales
   const int rows = stream_rows_per_pass(M);
   for (int m0 = 0; m0 < M; m0 += rows) {
     const int mc = (M - m0) < rows ? (M - m0) : rows;
-    p.a = reinterpret_cast<const __half*>(a) + (size_t)m0 * lda;
+    p.a = reinterpret_cast<const __half*>(a) + (size_t)m0 * lda;  // (a_host: one pass, lda unused)
     p.c = reinterpret_cast<__half*>(c) + (size_t)m0 * ldc;
     p.M = mc;
     p.T_own = stream_tiles_owned(mc, p.NT, p.CPC);
+    p.nowait = (a_host && p.S == 1 && p.T_own * p.CPC == p.NT) ? 1 : 0;
     const int smem = stream_smem(mc, p.KBc * 512, bits, pl.stages, p.T_own);
     if (smem > device_info().max_smem) return ST_UNSUPPORTED;
     cudaError_t e = stream_launch(var, p, stream_mt(mc), smem, stream);
@@ -768,9 +807,43 @@ int b200q_gemm_host(const void* a_host, int lda, const void* bq, const void* sca
   if (!a_host || !c_host || !a_staging || !c_staging) return ST_INVALID_ARG;
   if (M < 1 || N < 1 || K < 1 || lda < K || ldc < N) return ST_INVALID_ARG;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  cudaError_t e = lda == K ? cudaMemcpyAsync(a_staging, a_host, (size_t)M * K * 2, cudaMemcpyHostToDevice, st)
-                           : cudaMemcpy2DAsync(a_staging, (size_t)K * 2, a_host, (size_t)lda * 2, (size_t)K * 2, M,
-                                               cudaMemcpyHostToDevice, st);
+  cudaError_t e;
+  // Small activation blocks in pinned memory the GPU can address are fetched by a kernel whose PCIe
+  // reads lie under the previous GEMM of the stream (fetch_kernel.cu); the rest goes through the copy engine.
+  const void* a_mapped = nullptr;
+  if ((size_t)M * K * 2 <= (256u << 10) && (K % 8) == 0 && (lda % 8) == 0 && (((uintptr_t)a_staging) & 15) == 0) {
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, a_host) == cudaSuccess && attr.type == cudaMemoryTypeHost &&
+        attr.devicePointer && (((uintptr_t)attr.devicePointer) & 15) == 0)
+      a_mapped = attr.devicePointer;
+    else
+      (void)cudaGetLastError();  // an unregistered host pointer is not an error here
+  }
+  // Decode batches: the GEMV kernel's own first CTAs fetch the rows (one kernel, no copy operation at
+  // all) when the result can also go straight to the host buffer.
+  if (a_mapped && act_ok(act_dtype) && (ldc % 8) == 0 && (size_t)M * N * 2 <= (1u << 20)) {
+    int var;
+    b200q_plan_t pl;
+    cudaPointerAttributes cattr;
+    if (check_problem(M, N, K, wtype, zero_point, group, true, &var) == ST_OK &&
+        make_plan(M, N, K, var, group, &pl) == ST_OK && pl.kernel == 2 && pl.passes == 1 &&
+        M <= stream_rows_per_pass(M) && pl.splits * pl.ctas_per_split <= 2 * device_info().sm_count / stream_mt(M)) {
+      if (cudaPointerGetAttributes(&cattr, c_host) == cudaSuccess && cattr.type == cudaMemoryTypeHost &&
+          cattr.devicePointer && (((uintptr_t)cattr.devicePointer) & 15) == 0) {
+        if (!bq || !scales) return ST_INVALID_ARG;
+        if ((((uintptr_t)bq) & 15) || lda < K) return ST_INVALID_ARG;
+        return run_stream(a_staging, K, bq, scales, cattr.devicePointer, ldc, M, N, K, var, group, act_dtype, workspace,
+                          workspace_bytes, st, pl, nullptr, a_mapped, lda);
+      }
+      (void)cudaGetLastError();
+    }
+  }
+  if (a_mapped)
+    e = host_fetch_launch(a_mapped, lda, a_staging, M, K, st);
+  else
+    e = lda == K ? cudaMemcpyAsync(a_staging, a_host, (size_t)M * K * 2, cudaMemcpyHostToDevice, st)
+                 : cudaMemcpy2DAsync(a_staging, (size_t)K * 2, a_host, (size_t)lda * 2, (size_t)K * 2, M,
+                                     cudaMemcpyHostToDevice, st);
   if (e != cudaSuccess) { g_last_cuda_error = (int)e; return ST_CUDA; }
   // small results into mapped pinned memory: no copy-out operation on the stream
   void* c_direct = nullptr;

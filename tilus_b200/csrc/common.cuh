@@ -88,6 +88,21 @@ struct StreamParams {
   int ipt_shift;         // log2 of the items per column tile inside a k chunk when that is a power of two, else -1
   int act;               // activation / scale / output dtype: 0 fp16, 1 bf16
   int trig;              // 1: CTA 0 lets the next kernel of the stream launch only after its own griddepcontrol.wait
+  // Activations in pinned host memory (template value HOSTA of the kernel): the first `fetch_ctas` CTAs
+  // read A from `a_host` (device-side address of the host rows, row stride lda) before they wait for the
+  // previous kernel, store it to `a` (dense [M, K] staging on the device) afterwards and count themselves
+  // in on `fetch_flag`; every CTA stages from `a` once the count is complete.  `fetch_flag[1]` counts the
+  // CTAs that have seen it complete; the last of them puts both words back to zero.
+  // Such a launch reads nothing the previous kernel of the stream wrote.  With one K chunk and no column
+  // tiles shared between CTAs (`nowait`) it therefore does not wait for that kernel before its main loop,
+  // only before it writes its outputs (so that outputs of consecutive calls land in order); and it lets
+  // its own successor launch once all of its CTAs have staged their activations, i.e. once the staging
+  // buffer is free again.  Consecutive host calls then overlap: the next one streams weights while this
+  // one's results drain to the host.
+  const __half* a_host;
+  unsigned* fetch_flag;
+  int fetch_ctas;
+  int nowait;
   GatherArgs ga;
 };
 

@@ -93,7 +93,7 @@ template <int GATHER, int ACT>
 __device__ __forceinline__ void store_pair(const StreamParams& p, size_t gather_buf, unsigned tag, int m, int n,
                                            float v0, float v1) {
   const uint32_t h2 = (uint32_t)out_bits<ACT>(v0) | ((uint32_t)out_bits<ACT>(v1) << 16);
-  if constexpr (GATHER == 0) {
+  if constexpr (GATHER == 0 || GATHER == 3) {
     *reinterpret_cast<uint32_t*>(reinterpret_cast<unsigned short*>(p.c) + (size_t)m * p.ldc + n) = h2;
   } else if constexpr (GATHER == 1) {
     const size_t off = gather_buf + (size_t)m * p.ldc + p.ga.col_off + n;
@@ -224,8 +224,10 @@ __global__ void __launch_bounds__(stream_warps(MT) * 32, MT == 1 ? 2 : 1) stream
   // The next kernel of the stream may become resident as soon as there is room for it - once every
   // CTA of this launch has said so.  p.trig == 1: CTA 0 says so only after its own wait for the
   // previous kernel, which keeps the next kernel's CTAs off the SMs until the previous one has gone.
+  // Launches that fetch their activations from the host (GATHER == 3) say so after staging them: their
+  // successor may then overwrite the staging buffer at once.
   const bool late_trigger = p.trig == 1 && blockIdx.x == 0;
-  if (!late_trigger) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (GATHER != 3 && !late_trigger) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   const uint32_t bar0 = smem_base + warp * 64;
   const uint32_t ring_s = smem_base + HDR + warp * NST * SLOT_BYTES;
@@ -289,8 +291,27 @@ __global__ void __launch_bounds__(stream_warps(MT) * 32, MT == 1 ? 2 : 1) stream
   const bool sc_first_valid = (lane >> 1) < n_items * GI;
   if (sc_first_valid) sc_first = __ldg(scale_src(lane >> 1));
   for (int idx = tid; idx < p.T_own * 16 * MP; idx += NWARPS * 32) sAcc[idx] = 0.f;
-  // everything below may read what the previous kernel of the stream wrote
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  // Activations in host memory (GATHER == 3): the first CTAs bring them over PCIe now, under the
+  // previous kernel of the stream, and hold them in registers until that kernel has finished with the
+  // staging buffer.
+  constexpr int FETCH_PIECES = 4;
+  uint4 fetched[GATHER == 3 ? FETCH_PIECES : 1];
+  if (GATHER == 3 && (int)blockIdx.x < p.fetch_ctas) {
+    const int vec_per_row = p.K / 8, total = p.M * vec_per_row;
+#pragma unroll
+    for (int u = 0; u < FETCH_PIECES; ++u) {
+      const int idx = ((int)blockIdx.x * FETCH_PIECES + u) * NWARPS * 32 + tid;
+      if (idx < total) {
+        const int m = idx / vec_per_row, c = idx - m * vec_per_row;
+        fetched[GATHER == 3 ? u : 0] =
+            __ldcv(reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(p.a_host) + (size_t)m * p.lda + (size_t)c * 8));
+      }
+    }
+  }
+  // everything below may read what the previous kernel of the stream wrote (a launch with host
+  // activations, one K chunk and only own tiles reads nothing of it: it waits before its output instead)
+  const bool nowait = GATHER == 3 && p.nowait;
+  if (!nowait) asm volatile("griddepcontrol.wait;" ::: "memory");
   if (late_trigger) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   // ---- fused all-gather: this launch is fused call number E + 1 of the rank (E is kept on the
@@ -349,6 +370,48 @@ __global__ void __launch_bounds__(stream_warps(MT) * 32, MT == 1 ? 2 : 1) stream
     }
   }
   const unsigned out_tag = epoch + 1;  // tagged mode: what this call's output words carry
+  int a_ld = p.lda;  // row stride of what the staging loop reads
+  if constexpr (GATHER == 3) {
+    // fetching CTAs: registers -> dense device rows, then count in; everybody: wait for the count (bounded)
+    const int vec_per_row = p.K / 8, total = p.M * vec_per_row;
+    if ((int)blockIdx.x < p.fetch_ctas) {
+#pragma unroll
+      for (int u = 0; u < FETCH_PIECES; ++u) {
+        const int idx = ((int)blockIdx.x * FETCH_PIECES + u) * NWARPS * 32 + tid;
+        if (idx < total)
+          __stcg(reinterpret_cast<uint4*>(const_cast<unsigned short*>(a_base) + (size_t)idx * 8), fetched[u]);
+      }
+      __syncthreads();
+      if (tid == 0) {
+        __threadfence();
+        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.fetch_flag) : "memory");
+      }
+    }
+    if (tid == 0) {
+      uint64_t t0 = 0;
+      for (int spin = 0;; ++spin) {
+        unsigned v;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p.fetch_flag) : "memory");
+        if (v >= (unsigned)p.fetch_ctas) break;
+        uint64_t now;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+        if (spin == 0) t0 = now;
+        else if (now - t0 > 250000000ull) {  // give up: report, carry on with what is there
+          atomicExch(p.status, ST_DEVICE_TIMEOUT);
+          p.status[1] = 6;  // where: wait for the CTAs that fetch the activations
+          p.status[2] = blockIdx.x;
+          break;
+        }
+      }
+      // the last CTA to get here puts the two words back to zero for the next launch
+      if (atomicAdd(p.fetch_flag + 1, 1u) == gridDim.x - 1) {
+        atomicExch(p.fetch_flag, 0u);
+        atomicExch(p.fetch_flag + 1, 0u);
+      }
+    }
+    __syncthreads();
+    a_ld = p.K;
+  }
 
   // ---- stage the activation chunk A[0:M, kb_base*512 : +KBc*512] as fp16 (pre-scaled where the
   // weight type needs it), and the zero-point term of every 128-row group ----
@@ -393,7 +456,7 @@ __global__ void __launch_bounds__(stream_warps(MT) * 32, MT == 1 ? 2 : 1) stream
             tlo[GATHER == 2 ? u : 0] = ld_tagged2(src);
             thi[GATHER == 2 ? u : 0] = ld_tagged2(src + 2);
           } else {
-            const uint4* src = reinterpret_cast<const uint4*>(a_base + (size_t)mq[u] * p.lda + (size_t)kb_base * 512 + kq[u]);
+            const uint4* src = reinterpret_cast<const uint4*>(a_base + (size_t)mq[u] * a_ld + (size_t)kb_base * 512 + kq[u]);
             vq[u] = GATHER ? __ldcg(src) : __ldg(src);  // gathered rows were written through L2 by other GPUs
           }
         }
@@ -462,6 +525,7 @@ __global__ void __launch_bounds__(stream_warps(MT) * 32, MT == 1 ? 2 : 1) stream
   }
   if (sc_first_valid) *reinterpret_cast<uint4*>(sc_warp + ((lane >> 1) % SCG) * 32 + (lane & 1) * 16) = sc_first;
   __syncthreads();  // activations staged, tile sums cleared, first scales cached
+  if (GATHER == 3) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   const int items_per_tile_total = p.KB * NI;
   bool ok = true;
@@ -648,6 +712,7 @@ __global__ void __launch_bounds__(stream_warps(MT) * 32, MT == 1 ? 2 : 1) stream
   }
 
   // ---- the CTA's own tiles ----
+  if (nowait) asm volatile("griddepcontrol.wait;" ::: "memory");  // outputs of consecutive calls land in order
   if (p.T_own > 0) {
     __syncthreads();
     const int n0 = own_tile0 * 16, ncols = p.T_own * 16;
@@ -711,7 +776,7 @@ __global__ void __launch_bounds__(stream_warps(MT) * 32, MT == 1 ? 2 : 1) stream
   // of the output row are in place.  Every CTA orders its stores before its arrival at GPU scope;
   // the last arriver, which has observed all arrivals, releases at system scope: by cumulativity
   // every CTA's stores are visible to whoever acquires the flag. ----
-  if (GATHER) {
+  if (GATHER == 1 || GATHER == 2) {
     __syncthreads();
     if (tid == 0 && GATHER == 2) {
       // tagged words need no release: every word announces itself.  The last CTA only moves the call
@@ -774,6 +839,8 @@ template <int VAR>
 static cudaError_t launch_var(int var, const StreamParams& p, int mt, int smem_bytes, cudaStream_t stream) {
   if constexpr (VAR % B200Q_NPARTS == B200Q_PART) {
     if (var == VAR) {
+      if (p.a_host != nullptr)
+        return mt == 1 ? launch_act<VAR, 1, 3>(p, smem_bytes, stream) : launch_act<VAR, 2, 3>(p, smem_bytes, stream);
       if (p.ga.G > 0 && p.ga.mode == 1)
         return mt == 1 ? launch_act<VAR, 1, 2>(p, smem_bytes, stream) : launch_act<VAR, 2, 2>(p, smem_bytes, stream);
       if (p.ga.G > 0)
