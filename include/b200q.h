@@ -108,7 +108,7 @@ int b200q_gemm(const void* a, int lda, const void* bq, const void* scales, void*
  * on the stream.  Pinned memory the GPU can address: a small kernel whose PCIe reads run under the
  * previous kernel of the stream.  Pinned memory and a decode batch (M <= 16 on the stream kernel, result
  * written straight to pinned c_host): no separate operation at all - the first CTAs of the GEMV kernel
- * fetch the rows, the others wait for them (bounded, status[1] = 6), and consecutive such calls overlap on
+ * fetch the rows, the others wait for them (bounded, status[1] = 9), and consecutive such calls overlap on
  * the GPU: a call does not wait for the kernel before it until it writes its outputs, which therefore
  * still land in call order.  For that, `a_staging` and `workspace` must belong to the host calls of this
  * stream alone: no other kernel may read `a_staging` while such calls are queued. */
@@ -277,8 +277,9 @@ int b200q_gemm_swiglu_cast(const void* a, int lda, const void* bq, const void* s
 
 /* Reads the device status header of a workspace (synchronises `stream`): status[0] is 0 or
  * B200Q_ERR_DEVICE_TIMEOUT, status[1..3] say which wait gave up (1: 2 = tcgen05 prefill pipeline,
- * 3 = decode kernel's weight ring, 5 = wait for a peer's columns, 6 = tcgen05 small-batch pipeline;
- * 2: CTA; 3: warp or thread).  Clears the header.  A launch that gave up may leave partial sums
+ * 3 = decode kernel's weight ring, 5 = wait for a peer's columns, 6 = tcgen05 small-batch pipeline,
+ * 7 / 8 = gather push / collect, 9 = wait for the CTAs that fetch host activations; 2: CTA; 3: warp or
+ * thread).  Clears the header.  A launch that gave up may leave partial sums
  * behind: zero the workspace before it is used again.  workspace == NULL names the built-in
  * scratch of b200q_gemm_static_ws, which this call then puts back to zero itself. */
 int b200q_device_status(void* workspace, int32_t status[4], void* stream);

@@ -614,7 +614,7 @@ static int run_gemm(const void* a, int lda, const void* bq, const void* scales, 
   if (!a || !bq || !scales || !c) return ST_INVALID_ARG;
   if (((uintptr_t)a | (uintptr_t)bq | (uintptr_t)c) & 15) return ST_INVALID_ARG;
   if (((uintptr_t)scales) & 1) return ST_INVALID_ARG;
-  if (lda < K || ldc < N || (lda % 8) != 0 || (ldc & 1)) return ST_INVALID_ARG;  // outputs leave in column pairs
+  if (lda < K || ldc < N || (lda % 8) != 0) return ST_INVALID_ARG;
   if (pl.kernel == 1 && pl.passes == 2) {
     // the full 256-row tiles on the tcgen05 kernel, the short last tile on the decode kernel
     const int tail = M % 256;

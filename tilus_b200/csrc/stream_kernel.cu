@@ -85,17 +85,15 @@ __device__ __forceinline__ unsigned short out_bits(float v) {
   if constexpr (ACT == 0) return __half_as_ushort(__float2half_rn(v));
   else return __bfloat16_as_ushort(__float2bfloat16_rn(v));
 }
-// Two adjacent output values (columns n and n + 1 of row m, n even).  Plain launches write C; launches
-// with a fused all-gather write into the full output row of every rank (peer-mapped pointers, stores
-// only): a 4-byte store into the dense row buffer, or - tagged mode - one 64-bit store of the two
-// values with the call number `tag` in the upper half.
+// Two adjacent output values (columns n and n + 1 of row m, n even) of a launch with a fused
+// all-gather, written into the full output row of every rank (peer-mapped pointers, stores only): a
+// 4-byte store into the dense row buffer, or - tagged mode - one 64-bit store of the two values with
+// the call number `tag` in the upper half.
 template <int GATHER, int ACT>
 __device__ __forceinline__ void store_pair(const StreamParams& p, size_t gather_buf, unsigned tag, int m, int n,
                                            float v0, float v1) {
   const uint32_t h2 = (uint32_t)out_bits<ACT>(v0) | ((uint32_t)out_bits<ACT>(v1) << 16);
-  if constexpr (GATHER == 0 || GATHER == 3) {
-    *reinterpret_cast<uint32_t*>(reinterpret_cast<unsigned short*>(p.c) + (size_t)m * p.ldc + n) = h2;
-  } else if constexpr (GATHER == 1) {
+  if constexpr (GATHER == 1) {
     const size_t off = gather_buf + (size_t)m * p.ldc + p.ga.col_off + n;
     for (int g = 0; g < p.ga.G; ++g)
       *reinterpret_cast<uint32_t*>(reinterpret_cast<unsigned short*>(p.ga.out[g]) + off) = h2;
@@ -108,6 +106,12 @@ __device__ __forceinline__ void store_pair(const StreamParams& p, size_t gather_
                    : "memory");
   }
 }
+// One output value of a launch without gather: a 2-byte store into C.
+template <int ACT>
+__device__ __forceinline__ void store_one(const StreamParams& p, int m, int n, float v) {
+  reinterpret_cast<unsigned short*>(p.c)[(size_t)m * p.ldc + n] = out_bits<ACT>(v);
+}
+constexpr bool gather_pairs(int gather) { return gather == 1 || gather == 2; }
 // two tagged words (16 bytes) as they are now in memory; each 64-bit half is read atomically
 __device__ __forceinline__ ulonglong2 ld_tagged2(const unsigned long long* src) {
   ulonglong2 v;
@@ -398,7 +402,7 @@ __global__ void __launch_bounds__(stream_warps(MT) * 32, MT == 1 ? 2 : 1) stream
         if (spin == 0) t0 = now;
         else if (now - t0 > 250000000ull) {  // give up: report, carry on with what is there
           atomicExch(p.status, ST_DEVICE_TIMEOUT);
-          p.status[1] = 6;  // where: wait for the CTAs that fetch the activations
+          p.status[1] = 9;  // where: wait for the CTAs that fetch the activations
           p.status[2] = blockIdx.x;
           break;
         }
@@ -665,25 +669,43 @@ __global__ void __launch_bounds__(stream_warps(MT) * 32, MT == 1 ? 2 : 1) stream
         last = __shfl_sync(0xffffffffu, last, 0);
         if (last) {  // every share has arrived: convert, write C, put the scratch back to zero
           __threadfence();
+          if constexpr (!gather_pairs(GATHER)) {
 #pragma unroll
-          for (int mt = 0; mt < MT; ++mt) {
-            const int m0 = mt * 8 + 2 * j;
-            const bool rows = m0 < p.M;
+            for (int mt = 0; mt < MT; ++mt) {
+              const int m0 = mt * 8 + 2 * j;
+              if (m0 < p.M) {
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              float2* src = reinterpret_cast<float2*>(dst + (r + h * 8) * MP + m0);
-              float2 v = make_float2(0.f, 0.f);
-              if (rows) {
-                v = __ldcg(src);
-                __stcg(src, make_float2(0.f, 0.f));
+                for (int h = 0; h < 2; ++h) {
+                  float2* src = reinterpret_cast<float2*>(dst + (r + h * 8) * MP + m0);
+                  const float2 v = __ldcg(src);
+                  __stcg(src, make_float2(0.f, 0.f));
+                  const int n = cur_tile * 16 + r + h * 8;
+                  store_one<ACT>(p, m0, n, v.x);
+                  if (m0 + 1 < p.M) store_one<ACT>(p, m0 + 1, n, v.y);
+                }
               }
-              // columns r and r ^ 1 sit four lanes apart (same rows): the even one writes row m0 of
-              // both columns, the odd one row m0 + 1
-              const float ox = __shfl_xor_sync(0xffffffffu, v.x, 4), oy = __shfl_xor_sync(0xffffffffu, v.y, 4);
-              const int nb = cur_tile * 16 + (r & ~1) + h * 8;
-              if (rows) {
-                if (!(r & 1)) store_pair<GATHER, ACT>(p, gather_buf, out_tag, m0, nb, v.x, ox);
-                else if (m0 + 1 < p.M) store_pair<GATHER, ACT>(p, gather_buf, out_tag, m0 + 1, nb, oy, v.y);
+            }
+          } else {
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+              const int m0 = mt * 8 + 2 * j;
+              const bool rows = m0 < p.M;
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                float2* src = reinterpret_cast<float2*>(dst + (r + h * 8) * MP + m0);
+                float2 v = make_float2(0.f, 0.f);
+                if (rows) {
+                  v = __ldcg(src);
+                  __stcg(src, make_float2(0.f, 0.f));
+                }
+                // columns r and r ^ 1 sit four lanes apart (same rows): the even one writes row m0 of
+                // both columns, the odd one row m0 + 1
+                const float ox = __shfl_xor_sync(0xffffffffu, v.x, 4), oy = __shfl_xor_sync(0xffffffffu, v.y, 4);
+                const int nb = cur_tile * 16 + (r & ~1) + h * 8;
+                if (rows) {
+                  if (!(r & 1)) store_pair<GATHER, ACT>(p, gather_buf, out_tag, m0, nb, v.x, ox);
+                  else if (m0 + 1 < p.M) store_pair<GATHER, ACT>(p, gather_buf, out_tag, m0 + 1, nb, oy, v.y);
+                }
               }
             }
           }
@@ -717,9 +739,14 @@ __global__ void __launch_bounds__(stream_warps(MT) * 32, MT == 1 ? 2 : 1) stream
     __syncthreads();
     const int n0 = own_tile0 * 16, ncols = p.T_own * 16;
     if (p.S == 1) {  // all of K was here: write C
-      for (int m = 0; m < p.M; ++m)
-        for (int n = 2 * tid; n < ncols; n += 2 * NWARPS * 32)
-          store_pair<GATHER, ACT>(p, gather_buf, out_tag, m, n0 + n, sAcc[n * MP + m], sAcc[(n + 1) * MP + m]);
+      if constexpr (!gather_pairs(GATHER)) {
+        for (int m = 0; m < p.M; ++m)
+          for (int n = tid; n < ncols; n += NWARPS * 32) store_one<ACT>(p, m, n0 + n, sAcc[n * MP + m]);
+      } else {
+        for (int m = 0; m < p.M; ++m)
+          for (int n = 2 * tid; n < ncols; n += 2 * NWARPS * 32)
+            store_pair<GATHER, ACT>(p, gather_buf, out_tag, m, n0 + n, sAcc[n * MP + m], sAcc[(n + 1) * MP + m]);
+      }
     } else {
       // other k chunks hold the rest: meet in the global scratch; the last chunk to arrive converts
       for (int idx = tid * 4; idx < ncols * MP; idx += NWARPS * 32 * 4)
@@ -744,6 +771,18 @@ __global__ void __launch_bounds__(stream_warps(MT) * 32, MT == 1 ? 2 : 1) stream
         const int t = idx / (16 * MP);
         if (!s_last[t]) continue;
         if (!fenced) { __threadfence(); fenced = true; }
+        if constexpr (!gather_pairs(GATHER)) {
+          const int m = idx % MP, n = n0 + idx / MP;
+          if (m < p.M) {
+            float4* src = reinterpret_cast<float4*>(p.partial + (size_t)n0 * MP + idx);
+            const float4 v = __ldcg(src);
+            __stcg(src, make_float4(0.f, 0.f, 0.f, 0.f));
+            store_one<ACT>(p, m, n, v.x);
+            if (m + 1 < p.M) store_one<ACT>(p, m + 1, n, v.y);
+            if (m + 2 < p.M) store_one<ACT>(p, m + 2, n, v.z);
+            if (m + 3 < p.M) store_one<ACT>(p, m + 3, n, v.w);
+          }
+        } else {
         const int m = idx % MP, col = idx / MP;
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
         if (m < p.M) {
@@ -766,6 +805,7 @@ __global__ void __launch_bounds__(stream_warps(MT) * 32, MT == 1 ? 2 : 1) stream
             if (m + 1 < p.M) store_pair<GATHER, ACT>(p, gather_buf, out_tag, m + 1, nb, o.y, v.y);
             if (m + 3 < p.M) store_pair<GATHER, ACT>(p, gather_buf, out_tag, m + 3, nb, o.w, v.w);
           }
+        }
         }
         if ((idx % (16 * MP)) == 0) p.counters[own_tile0 + t] = 0;
       }
