@@ -57,7 +57,9 @@ INT_NAMES = [f"int{n}b" for n in range(1, 8)] + [f"uint{n}b" for n in range(1, 8
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("TILUS_REFERENCE_ROOT")
+    if not ref_root:
+        sys.exit("usage: make_golden.py <root of the reference checkout>  (or set TILUS_REFERENCE_ROOT)")
     out_dir = os.path.dirname(os.path.abspath(__file__))
     tilus, kat = _import_reference(ref_root)
     import tilus.hidet.ir.dtypes as D

@@ -251,14 +251,14 @@ umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
         for (int ci = 0; ci < 4; ++ci) {
           const int c0 = chunk0 * 32 + ci * 64;
           if (c0 < TM && m0 + c0 < p.M) {
-            uint32_t h[16];  // round 1: columns (n & ~1, +1), row 2 i + b0
+            uint32_t h[16];  // exchange 1: columns (n & ~1, +1), row 2 i + b0
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
               const uint32_t got = __shfl_xor_sync(0xffffffffu, hb[ci][i], 1);
               // even lane: (own row 2i, partner's row 2i); odd lane: (partner's row 2i+1, own row 2i+1)
               h[i] = b0 ? __byte_perm(hb[ci][i], got, 0x3276) : __byte_perm(hb[ci][i], got, 0x5410);
             }
-            uint32_t w2[8][2];  // round 2: columns (n & ~3 .. +3), row 4 j + 2 b1 + b0
+            uint32_t w2[8][2];  // exchange 2: columns (n & ~3 .. +3), row 4 j + 2 b1 + b0
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
               const uint32_t mine = b1 ? h[2 * j + 1] : h[2 * j];
@@ -268,7 +268,7 @@ umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a) {
               w2[j][1] = b1 ? mine : got;
             }
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {  // round 3: columns (n & ~7 .. +7), row 8 k + (lane & 7)
+            for (int k = 0; k < 4; ++k) {  // exchange 3: columns (n & ~7 .. +7), row 8 k + (lane & 7)
               const uint32_t m0r = b2 ? w2[2 * k + 1][0] : w2[2 * k][0], m1r = b2 ? w2[2 * k + 1][1] : w2[2 * k][1];
               const uint32_t g0r = b2 ? w2[2 * k][0] : w2[2 * k + 1][0], g1r = b2 ? w2[2 * k][1] : w2[2 * k + 1][1];
               const uint32_t r0 = __shfl_xor_sync(0xffffffffu, g0r, 4), r1 = __shfl_xor_sync(0xffffffffu, g1r, 4);
