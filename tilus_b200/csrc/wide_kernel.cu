@@ -60,6 +60,7 @@ struct WideBarriers {
   uint32_t tmem_base;
   volatile int abort_flag;
   int last_flag;
+  int fin_pending, fin_n_tile, fin_m_tile;  // a finalize left for the whole CTA (see the teardown)
 };
 
 // a ring stage: the packed weights of 256 columns x 128 rows, then rpg (1, 2 or 4) rows of 256 scales
@@ -103,6 +104,7 @@ wide_kernel(const WideParams p, const __grid_constant__ CUtensorMap tmap_a) {
     for (int i = 0; i < 2; ++i) { mbar_init(BAR_ADDR(d_full, i), 1); mbar_init(BAR_ADDR(d_empty, i), 4); }
     bars->abort_flag = 0;
     bars->last_flag = 0;
+    bars->fin_pending = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -286,7 +288,16 @@ wide_kernel(const WideParams p, const __grid_constant__ CUtensorMap tmap_a) {
           const int old = atomicAdd(p.counters + n_tile * p.m_tiles + m_tile, 1);
           const int last = (old + 1 == p.splits) ? 1 : 0;
           if (last) __threadfence();
-          bars->last_flag = last;
+          // The CTA's last item: every role is done by then, so all 23 warps convert the tile after the
+          // roles have left their loops (four warps alone need a dozen L2 round trips for it, and the next
+          // kernel of the stream waits for the slowest CTA).
+          const bool defer = w + (int)gridDim.x >= total_items;
+          bars->last_flag = (last && !defer) ? 1 : 0;
+          if (last && defer) {
+            bars->fin_n_tile = n_tile;
+            bars->fin_m_tile = m_tile;
+            bars->fin_pending = 1;
+          }
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (bars->last_flag) {
@@ -455,6 +466,44 @@ wide_kernel(const WideParams p, const __grid_constant__ CUtensorMap tmap_a) {
   if (warp == 22) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(WIDE_TMEM_COLS) : "memory");
+  }
+  if (bars->fin_pending && !*abort_flag) {
+    // the last K range of the CTA's last tile arrived here: all threads convert the fp32 sums and
+    // restore the zeros (the counting thread's fence above ordered the other CTAs' additions before this)
+    const int n_tile = bars->fin_n_tile, m_tile = bars->fin_m_tile, m0 = m_tile * 128;
+    const int rows = min(128, p.M - m0), cols = min(256, p.N - n_tile * 256);
+    constexpr int FB = WIDE_FINALIZE_BATCH;
+    const int per_row = cols / 8, total = rows * per_row;
+    for (int base = tid; base < total; base += FB * WIDE_THREADS) {
+      float4 x[FB][2];
+#pragma unroll
+      for (int u = 0; u < FB; ++u) {
+        const int idx = base + u * WIDE_THREADS;
+        if (idx < total) {
+          const float4* src = reinterpret_cast<const float4*>(
+              p.partial + (size_t)(m0 + idx / per_row) * p.N + n_tile * 256 + (idx % per_row) * 8);
+          x[u][0] = __ldcg(src);
+          x[u][1] = __ldcg(src + 1);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < FB; ++u) {
+        const int idx = base + u * WIDE_THREADS;
+        if (idx < total) {
+          const int mm = m0 + idx / per_row, nn = n_tile * 256 + (idx % per_row) * 8;
+          float4* src = reinterpret_cast<float4*>(p.partial + (size_t)mm * p.N + nn);
+          uint4 o;
+          o.x = pack2<ACT>(x[u][0].x, x[u][0].y);
+          o.y = pack2<ACT>(x[u][0].z, x[u][0].w);
+          o.z = pack2<ACT>(x[u][1].x, x[u][1].y);
+          o.w = pack2<ACT>(x[u][1].z, x[u][1].w);
+          *reinterpret_cast<uint4*>(p.c + (size_t)mm * p.ldc + nn) = o;
+          __stcg(src, make_float4(0.f, 0.f, 0.f, 0.f));
+          __stcg(src + 1, make_float4(0.f, 0.f, 0.f, 0.f));
+        }
+      }
+    }
+    if (tid == 0) p.counters[n_tile * p.m_tiles + m_tile] = 0;
   }
 #undef BAR_ADDR
 #undef ITEM_COORDS
