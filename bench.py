@@ -266,6 +266,76 @@ def _sweep_shape(dt, n, k, group, ms_list, dev, reps, scale_range=(0.005, 0.02))
     return out
 
 
+def _sweep_followers(dev, hbm) -> dict:
+    """The rows the path was widened into: bfloat16 activations on the headline shape, and the gate_up
+    projection with SwiGLU and the per-token FP8 cast behind it (one library call), each checked against
+    its oracle on what was timed."""
+    from oracle import cast_oracle as co
+    from oracle import quant_oracle as qo
+    from tilus_b200 import QuantizedLinear, bfloat16, dtypes, ops, packing, synth
+
+    out = {}
+    dt = dtypes.uint4b
+    # ---- bf16 activations, decode GEMV M = 1, K = N = 8192 ----
+    n = k = 8192
+    prob = synth.make_problem(1, n, k, dt, GROUP, seed=100)
+    count = _layer_count(dt, n, k)
+    bq = packing.interleave(prob["codes"].to(dev), dt)
+    sc = prob["scales"].to(torch.bfloat16).to(dev)
+    layers = []
+    for _ in range(count):
+        layer = QuantizedLinear(bfloat16, dt, GROUP, k, n, zero_point=prob["zero_point"]).to(dev)
+        layer.load_packed(bq.clone(), sc.clone(), layout="b200")
+        layers.append(layer)
+    acts = [a.to(torch.bfloat16) for a in _acts(1, k, count, dev, seed=1)]
+    rounds = max(1, 40 // count)
+    g, outs = _capture(layers, acts, rounds)
+    _time_graph(g, 3)
+    ms = _time_graph(g, 10) / (10 * count * rounds)
+    cols = torch.arange(3, n, n // 64)[:64]
+    ref = qo.quantized_matmul_bf16(acts[0].cpu(), prob["codes"][:, cols].numpy(), prob["scales"][:, cols].to(torch.bfloat16),
+                                   dt, GROUP, prob["zero_point"]).float().numpy()
+    got = outs[0][:, cols.to(dev)].float().cpu().numpy()
+    nbytes = synth.gemm_bytes(1, n, k, dt.nbits, GROUP)
+    out["bf16_decode_u4_M1_K8192_N8192"] = {
+        "us": round(ms * 1e3, 3), "gbs": round(nbytes / (ms * 1e-3) / 1e9, 1),
+        "hbm_frac": round(nbytes / (ms * 1e-3) / 1e9 / hbm, 4),
+        "rel_err": float(f"{abs(got - ref).max() / max(abs(ref).max(), 1e-30):.3g}")}
+    del g, outs, layers, acts
+    torch.cuda.empty_cache()
+    # ---- gate_up (K = 4096, N = 2 x 14336) + SwiGLU + per-token FP8 cast, M = 8, one call per layer ----
+    k, n, m = 4096, 28672, 8
+    prob = synth.make_problem(m, n, k, dt, GROUP, seed=101)
+    count = _layer_count(dt, n, k)
+    layers = _make_layers(dt, n, k, GROUP, count, dev, seed=101, distinct=False, prob0=prob)
+    acts = _acts(m, k, count, dev, seed=2)
+    res = [None] * count
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for i, (layer, a) in enumerate(zip(layers, acts)):
+            res[i] = layer.forward_swiglu_cast(a)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=side):
+        for i, (layer, a) in enumerate(zip(layers, acts)):
+            res[i] = layer.forward_swiglu_cast(a)
+    _time_graph(g, 3)
+    ms = _time_graph(g, 10) / (10 * count)
+    q, sf, gate_up = res[0]
+    want_codes, want_sf, _ = co.swiglu_forward_and_per_token_cast(gate_up.float().cpu().numpy(), group=128)
+    deq = q.float().cpu().numpy().reshape(m, -1, 128) * sf.cpu().numpy()[:, :, None]
+    want = co.e4m3_decode(want_codes).astype("float32").reshape(m, -1, 128) * want_sf[:, :, None]
+    out["gate_up_swiglu_fp8_cast_u4_M8_K4096_N28672"] = {
+        "us": round(ms * 1e3, 3),
+        "gemm_rel_err": float(f"{_spot_check(prob, acts[0].cpu(), gate_up, torch.arange(3, n, n // 64)[:64]):.3g}"),
+        "cast_scale_max_abs_diff": float(f"{abs(sf.cpu().numpy() - want_sf).max():.3g}"),
+        "cast_dequantized_rel_err": float(f"{abs(deq - want).max() / max(abs(want).max(), 1e-30):.3g}")}
+    del g, res, layers, acts
+    torch.cuda.empty_cache()
+    return out
+
+
 def run_profile_case(args) -> None:
     """A few plain (non-graph) launches of one kernel on inputs larger than L2."""
     from tilus_b200 import dtypes
@@ -680,6 +750,7 @@ def run_b200(args) -> None:
                 f"M{m}": {"us": round(v["us"], 2), "tflops": round(v["tflops"], 2), "gbs": round(v["gbs"], 1),
                           "rel_err": float(f"{v['rel_err']:.3g}")}
                 for m, v in r.items()}
+        extra.update(_sweep_followers(dev, hbm))
         if not args.no_prefill:
             r = _sweep_shape(dtypes.int4b, 28672, 8192, GROUP, [4096], dev, 3)[4096]
             extra["prefill_i4_M4096_K8192_N28672"] = {
