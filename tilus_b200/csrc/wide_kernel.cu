@@ -52,6 +52,9 @@ constexpr int WIDE_WG_MAX = 8;      // packed 128-row weight groups in the ring 
 #endif
 constexpr int WIDE_TMEM_COLS = 512; // two accumulators of 256 columns
 
+// rows of the tcgen05.mma instruction: the 64-row form for batches of up to 64 rows
+__host__ __device__ constexpr int wide_umma_rows(int a_rows) { return a_rows <= 64 ? 64 : 128; }
+
 struct WideBarriers {
   uint64_t a_full[WIDE_SA], a_empty[WIDE_SA];
   uint64_t b_full[WIDE_SB], b_empty[WIDE_SB];
@@ -77,7 +80,10 @@ wide_kernel(const WideParams p, const __grid_constant__ CUtensorMap tmap_a) {
   // accumulator rows that nobody reads, so for small batches the stages are laid a_rows * 128 bytes
   // apart and the MMA's surplus rows alias the following stages: what is saved goes to the packed ring.
   const uint32_t ASTAGE = (uint32_t)p.a_rows * 128u;
-  const uint32_t AREGION = (WIDE_SA - 1) * ASTAGE + 128u * 128u;
+  // Batches of up to 64 rows use the 64-row form of the instruction: it reads half the activation bytes
+  // from shared memory, whose bandwidth is what the MMAs of this kernel wait for.
+  const int UM = wide_umma_rows(p.a_rows);
+  const uint32_t AREGION = (WIDE_SA - 1) * ASTAGE + (uint32_t)UM * 128u;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const uint32_t smem_unaligned = (uint32_t)__cvta_generic_to_shared(smem_raw);
   const uint32_t smem_base = (smem_unaligned + 1023u) & ~1023u;
@@ -229,11 +235,14 @@ wide_kernel(const WideParams p, const __grid_constant__ CUtensorMap tmap_a) {
     for (int w = blockIdx.x; w < total_items && good; w += gridDim.x, ++it) {
       ITEM_COORDS(w)
       const int buf = it & 1;
-      const int m = m0 + ew * 32 + lane;
+      // accumulator row r lives in lane r (128-row instruction) or in lane 32 * (r / 16) + r % 16 (64-row
+      // instruction: sixteen rows at the start of each 32-lane quadrant)
+      const bool lane_has_row = UM == 128 || lane < 16;
+      const int m = m0 + (UM == 128 ? ew * 32 + lane : ew * 16 + lane);
       if (!mbar_wait_abortable(BAR_ADDR(d_full, buf), (uint32_t)(it >> 1) & 1u, abort_flag)) { good = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t daddr = tmem + ((uint32_t)(ew * 32) << 16) + (uint32_t)(buf * 256);
-      const bool rows_here = m0 + ew * 32 < p.M;  // any row of this warp inside the batch
+      const bool rows_here = m0 + (UM == 128 ? ew * 32 : ew * 16) < p.M;  // any row of this warp inside the batch
       for (int c0 = 0; c0 < 256; c0 += 32) {
         const int n = n_tile * 256 + c0;
         if (!rows_here || n >= p.N) continue;  // warp-uniform
@@ -249,7 +258,7 @@ wide_kernel(const WideParams p, const __grid_constant__ CUtensorMap tmap_a) {
             : "r"(daddr + (uint32_t)c0)
             : "memory");
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (m < p.M) {
+        if (m < p.M && lane_has_row) {
           const int ncols = min(32, p.N - n);  // multiple of 16
           if (p.splits == 1) {
             __half* dst = p.c + (size_t)m * p.ldc + n;
@@ -409,7 +418,7 @@ wide_kernel(const WideParams p, const __grid_constant__ CUtensorMap tmap_a) {
   } else {
     // ================= MMA issuer =================
     if (lane == 0) {
-      const uint32_t idesc = umma_idesc<ACT>(256);  // M = 128, N = 256
+      const uint32_t idesc = (umma_idesc<ACT>(256) & ~(31u << 24)) | ((uint32_t)(UM >> 4) << 24);  // M = UM, N = 256
       bool good = true;
       int bi = 0, it = 0;
       for (int w = blockIdx.x; w < total_items && good; w += gridDim.x, ++it) {
@@ -557,7 +566,7 @@ cudaError_t B200Q_CAT(wide_launch_part, B200Q_PART)(int var, const WideParams& p
 #if B200Q_PART == 0
 // dynamic shared memory: alignment slack + activation stages + B operand stages + packed ring + barriers
 int wide_smem_bytes(int bits, int wg_stages, int a_rows, int rpg) {
-  return 1024 + (WIDE_SA - 1) * a_rows * 128 + 128 * 128 + WIDE_SB * 256 * 128 + wg_stages * wide_wstage_bytes(bits, rpg) +
+  return 1024 + (WIDE_SA - 1) * a_rows * 128 + wide_umma_rows(a_rows) * 128 + WIDE_SB * 256 * 128 + wg_stages * wide_wstage_bytes(bits, rpg) +
          (int)sizeof(WideBarriers) + 64;
 }
 // rows one activation copy fills: the batch rounded up to 32, 64 or 128
