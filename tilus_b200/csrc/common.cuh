@@ -33,9 +33,9 @@ constexpr int BLOCK_K = 512;
 constexpr size_t WS_HEADER_BYTES = 256;
 inline size_t ws_counter_bytes(int N) { return (((size_t)(N / BLOCK_N) * 4) + 255) / 256 * 256; }
 
-// ---- stream kernel (up to 16 rows per launch; the default for M <= 8): item-balanced, ring-fed --
-// warps per CTA.  Up to 8 rows (MT = 1) two CTAs share an SM: 12 warps each leave 85 registers per
-// thread, which the loop needs to stay out of local memory (16 warps at 64 registers spilled and
+// ---- stream kernel (up to 16 rows per launch, the kernel for M <= 16): item-balanced, ring-fed --
+// warps per CTA.  Up to 8 rows (MT = 1) two CTAs share an SM: 12 warps each leave up to 85 registers per
+// thread (the loop uses 72), which keeps it out of local memory (16 warps at 64 registers spilled and
 // measured 5-10 % slower; 10 and 14 warps were no better).  9..16 rows (MT = 2): one CTA has the SM.
 constexpr int stream_warps(int mt) { return mt == 1 ? 12 : 16; }
 // bytes of mbarriers in front of the rings: 8 slots of 8 bytes per warp, rounded up to 1 KB
