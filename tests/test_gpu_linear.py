@@ -127,6 +127,14 @@ def test_forward_host_back_to_back_calls_keep_their_order(M):
             assert float((outs[i].float() - w).abs().max()) <= 2e-3 * float(w.abs().max()), i
         for o in outs:
             o.zero_()
+    # a long run of calls queued at once: every call's result against forward() on the same input
+    many = [torch.zeros(M, n, dtype=torch.float16).pin_memory() for _ in range(32)]
+    for i, o in enumerate(many):
+        (la if i % 3 else lb).forward_host(xs[i % 4], o)
+    torch.cuda.synchronize()
+    for i, o in enumerate(many):
+        w = (la if i % 3 else lb)(xs[i % 4].cuda()).cpu().float()
+        assert float((o.float() - w).abs().max()) <= 2e-3 * float(w.abs().max()), i
     from tilus_b200 import ops
     assert ops.device_status(ops.get_workspace(torch.device("cuda", 0), 1 << 20)) == [0, 0, 0, 0]
 
