@@ -97,6 +97,25 @@ def test_forward_host_matches_forward(M):
         layer.forward_host(x.cuda())
 
 
+@pytest.mark.parametrize("M", [1, 9])
+def test_forward_host_bf16(M):
+    """The host path with bfloat16 activations (the kernel's first CTAs fetch bf16 rows, the result goes to
+    pinned bf16 memory)."""
+    from tilus_b200 import bfloat16
+
+    k, n = 1024, 768
+    layer = QuantizedLinear(bfloat16, D.int4b, 128, k, n).cuda()
+    layer.load_and_quantize(torch.randn(n, k, generator=torch.Generator().manual_seed(3)))
+    x = torch.randn(M, k, generator=torch.Generator().manual_seed(4)).to(torch.bfloat16)
+    want = layer(x.cuda()).cpu().float()
+    out = torch.zeros(M, n, dtype=torch.bfloat16).pin_memory()
+    for _ in range(2):
+        layer.forward_host(x.pin_memory(), out)
+        torch.cuda.synchronize()
+        assert float((out.float() - want).abs().max()) <= 1e-2 * float(want.abs().max())
+        out.zero_()
+
+
 @pytest.mark.parametrize("M", [1, 3, 16])
 def test_forward_host_back_to_back_calls_keep_their_order(M):
     """Consecutive host calls overlap on the GPU (a call with pinned activations does not wait for the

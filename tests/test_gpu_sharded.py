@@ -189,6 +189,37 @@ def test_tagged_gather_wait_runs_out_and_reports():
     assert int(ws.count_nonzero()) == 0
 
 
+@pytest.mark.parametrize("M", [1, 12])
+def test_tagged_gather_bf16_chain(M):
+    """bfloat16 activations through the tagged hand-over: two chained layers on a two-rank group against
+    the bf16 oracle (rows handed over as bf16 pairs with their tags)."""
+    from tilus_b200 import bfloat16
+
+    dev = torch.device("cuda:0")
+    dt, g, world = D.int4b, 128, 2
+    dims = [(1024, 2048), (2048, 512)]
+    probs = [synth.make_problem(M, n, k, dt, g, seed=50 + i) for i, (k, n) in enumerate(dims)]
+    regions, ctxs = _virtual_group(world, 16, 2048, dev, 16)
+    x0 = (probs[0]["a"] * 0.25).to(torch.bfloat16)
+    xs = [x0.to(dev)] * world
+    ref = x0
+    for (k, n), prob in zip(dims, probs):
+        lins = []
+        for r in range(world):
+            lin = sharded.ShardedQuantizedLinear(bfloat16, dt, g, k, n, shard=(world, r)).to(dev)
+            lin.load_codes(prob["codes"], prob["scales"].to(torch.bfloat16))
+            lins.append(lin)
+        xs = [ctxs[r].gemm(xs[r], lins[r]) for r in range(world)]
+        ref = qo.quantized_matmul_bf16(ref, prob["codes"].numpy(), prob["scales"].to(torch.bfloat16), dt, g, 0)
+    want = ref.float().numpy()
+    for r in range(world):
+        got = ctxs[r].fetch(xs[r])
+        assert got.dtype == torch.bfloat16
+        err = np.abs(got.float().cpu().numpy() - want).max() / np.abs(want).max()
+        assert err <= 2e-2, (r, err)
+        assert ctxs[r].calls_completed(True) == len(dims)
+
+
 def test_tagged_gather_two_outside_calls_in_a_row():
     """Two tagged calls in a row that take their activations from outside: the context puts a wait for
     the first one's rows between them (the rule of the tagged mode), and results stay right."""
