@@ -64,7 +64,8 @@ typedef struct b200q_plan {
                             kernel 3: 128-row weight groups in the packed ring) */
   int32_t warps;         /* warps per CTA (output only) */
   int32_t passes;        /* launches: 2 when kernel 1 takes the full 256-row tiles and kernel 2 a last tile of <= 16 rows */
-  int32_t pdl;           /* 1: launch with programmatic stream serialization (overlap with the previous kernel) */
+  int32_t pdl;           /* 1: launch with programmatic stream serialization (overlap with the previous kernel);
+                            kernel 3 always is, kernel 1 never */
   int32_t reserved;      /* 0 */
   uint64_t workspace_bytes;
 } b200q_plan_t;

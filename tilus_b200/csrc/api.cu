@@ -302,7 +302,7 @@ static void plan_wide(int M, int N, int K, int bits, int group, const DeviceInfo
   pl->tile_m = 128;
   pl->warps = 23;
   pl->passes = 1;
-  pl->pdl = 0;
+  pl->pdl = 1;  // always launched as a programmatic dependent
 }
 
 // The persistent CTAs of the transposed tcgen05 kernel take tiles round by round.  When the last round
