@@ -515,9 +515,9 @@ def measure_stack(world, rank, dev, steps, warmup, batches=(1, 8, 32, 64), tagge
     return {"workload": "llama3_8b_linear_stack_u4_g128", "layers": n_layers, "linears_per_step": 4 * n_layers,
             "scaling": "strong", "unit": "ms per 128-linear step", "per_gpu_weight_bytes": weight_bytes,
             "gather": {"nccl": "ncclAllGather per layer (M > 1: + one permute copy)",
-                       "fused": f"M <= {min(tagged_rows, 16)} on 2+ GPUs: peer stores of tagged words from the GEMV "
-                                "kernel, polled by the next one (b200q_gemm_gather, B200Q_GATHER_TAGGED); "
-                                "else M <= 16: peer stores from the GEMV kernel + per-rank flags; "
+                       "fused": f"M <= {tagged_rows} on 2+ GPUs: rows handed over as tagged words, polled by the next "
+                                "kernel (b200q_gemm_gather / b200q_gather_push, B200Q_GATHER_TAGGED), else per-rank flags; "
+                                "M <= 16: peer stores from the GEMV kernel itself; "
                                 "M > 16: GEMM, then a push kernel (peer stores + flags) and a collect kernel "
                                 "(b200q_gather_push)"},
             "results": results}

@@ -183,8 +183,8 @@ size_t b200q_static_workspace_limit(void);
  * activations from outside (`a_prev_offset < 0`) must not follow another such call directly unless a
  * b200q_gather_collect (wait only is enough) lies between them, and every rank issues its calls on
  * one stream.  b200q_gather_collect turns the latest call's tagged rows into dense rows;
- * b200q_gather_push takes the flag mode only.  Tagged and flag calls use separate buffers and
- * counters and do not see each other. */
+ * b200q_gather_push stores a shard as tagged words and counts as a call of this mode.  Tagged and flag
+ * calls use separate buffers and counters and do not see each other. */
 #define B200Q_GATHER_FLAGS 0
 #define B200Q_GATHER_TAGGED 1
 typedef struct b200q_gather {

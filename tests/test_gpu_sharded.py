@@ -244,8 +244,9 @@ def test_tagged_gather_two_outside_calls_in_a_row():
     assert ops.device_status(ops.get_workspace(dev, 1 << 20)) == [0, 0, 0, 0]
 
 
+@pytest.mark.parametrize("tagged", [False, True], ids=["flags", "tagged"])
 @pytest.mark.parametrize("M", [20, 64])
-def test_push_collect_gather_above_16_rows(M):
+def test_push_collect_gather_above_16_rows(M, tagged):
     """More than 16 rows: local GEMM, then push (shard to every rank's row buffer + flags) and collect
     (wait for all shards, copy the rows out).  Two ranks played on one stream: both push, then both
     collect - a collect waits for the pushes of the same call, so they must all have been queued."""
@@ -253,7 +254,7 @@ def test_push_collect_gather_above_16_rows(M):
     dt, g, world = D.int4b, 128, 2
     dims = [(512, 1024), (1024, 512)]
     probs = [synth.make_problem(M, n, k, dt, g, seed=30 + i) for i, (k, n) in enumerate(dims)]
-    regions, ctxs = _virtual_group(world, 64, 1024, dev)
+    regions, ctxs = _virtual_group(world, 64, 1024, dev, 64 if tagged else 0)
     x = [(probs[0]["a"] * 0.25).to(torch.float16).to(dev)] * world
     ref = x[0].cpu().numpy()
     for (k, n), prob in zip(dims, probs):
@@ -264,10 +265,10 @@ def test_push_collect_gather_above_16_rows(M):
             lins.append(lin)
         shards = [lins[r].local(x[r]) for r in range(world)]
         for r in range(world):
-            ctxs[r].push(shards[r], lins[r])
+            ctxs[r].push(shards[r], lins[r], tagged)
         full = [torch.empty(M, n, dtype=torch.float16, device=dev) for _ in range(world)]
         for r in range(world):
-            ctxs[r].collect(full[r], M, n)
+            ctxs[r].collect(full[r], M, n, tagged)
         x = full
         ref = qo.quantized_matmul(ref, prob["codes"].numpy(), prob["scales"].numpy(), dt, g, 0)
     torch.cuda.synchronize()
@@ -277,4 +278,4 @@ def test_push_collect_gather_above_16_rows(M):
         got = x[r].float().cpu().numpy()
         err = np.abs(got - ref.astype(np.float32)).max() / np.abs(ref.astype(np.float32)).max()
         assert err <= 2e-2, (r, err)
-        assert ctxs[r].calls_completed() == len(dims)
+        assert ctxs[r].calls_completed(tagged) == len(dims)

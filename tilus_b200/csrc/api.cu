@@ -717,7 +717,6 @@ int b200q_gather_push(const void* shard, int lds, int M, int N_loc, void* worksp
   if (!shard || !gather || M < 1 || N_loc < 8) return ST_INVALID_ARG;
   if ((N_loc % 8) != 0 || (lds % 8) != 0 || lds < N_loc || (((uintptr_t)shard) & 15)) return ST_INVALID_ARG;
   if ((gather->ldc % 8) != 0 || (gather->col_offset % 8) != 0) return ST_INVALID_ARG;
-  if (gather->mode != B200Q_GATHER_FLAGS) return ST_UNSUPPORTED;  // the push kernel writes dense rows
   if (!workspace || workspace_bytes < WS_HEADER_BYTES || ((uintptr_t)workspace & 255)) return ST_WORKSPACE;
   GatherArgs ga;
   const int st = fill_gather_args(gather, M, N_loc, workspace, &ga);

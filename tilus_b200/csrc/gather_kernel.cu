@@ -59,6 +59,36 @@ __global__ void __launch_bounds__(256) gather_push_kernel(const PushParams p) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
   const unsigned epoch = *reinterpret_cast<volatile const unsigned*>(p.ga.epoch);
+  if (p.ga.mode == 1) {
+    // Tagged words: every pair of values leaves with the call number in one 64-bit store, into buffer
+    // (E + 1) % 3 of every rank.  Nothing to wait for and nothing to fence: the collect kernels poll the
+    // words, and the buffer written here was last read two calls ago (every rank has since pushed twice,
+    // each time after collecting).  The last CTA only moves this rank's call counter on.
+    const size_t buf = (size_t)((epoch + 1) % GATHER_TAG_BUFFERS) * (size_t)p.ga.buf_elems;
+    const int vec_per_row = p.N_loc / 8;
+    const int total = p.M * vec_per_row;
+    const unsigned long long tag = (unsigned long long)(epoch + 1) << 32;
+    for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
+      const int m = idx / vec_per_row, v = idx - m * vec_per_row;
+      const uint4 x = *reinterpret_cast<const uint4*>(p.src + (size_t)m * p.lds + v * 8);
+      const size_t word = buf + (((size_t)m * p.ldc + p.ga.col_off + v * 8) >> 1);
+      const unsigned long long w0 = tag | x.x, w1 = tag | x.y, w2 = tag | x.z, w3 = tag | x.w;
+      for (int g = 0; g < p.ga.G; ++g) {
+        unsigned long long* dst = reinterpret_cast<unsigned long long*>(p.ga.out[g]) + word;
+        asm volatile("st.relaxed.sys.global.v2.u64 [%0], {%1, %2};" ::"l"(dst), "l"(w0), "l"(w1) : "memory");
+        asm volatile("st.relaxed.sys.global.v2.u64 [%0], {%1, %2};" ::"l"(dst + 2), "l"(w2), "l"(w3) : "memory");
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      unsigned* done = p.ga.epoch + 8;
+      if (atomicAdd(done, 1u) == gridDim.x - 1) {
+        atomicExch(done, 0u);
+        *p.ga.epoch = epoch + 1;
+      }
+    }
+    return;
+  }
   // nobody may still be reading the buffer about to be overwritten: every rank has finished call E
   if (epoch != 0) wait_flags(p, epoch, 7);
   const size_t buf = ((epoch + 1) & 1u) ? (size_t)p.ga.buf_elems : 0;

@@ -123,9 +123,11 @@ class PeerGather:
     a sequence of them can be captured in a CUDA graph and replayed.  All ranks must make the
     same sequence of calls.
 
-    Batches of at most `tagged_rows` rows (default: every fused call, M <= 16) use the tagged hand-over
-    instead (B200Q_GATHER_TAGGED): three more row buffers of 8-byte words {two outputs, call number} and
-    a call counter of their own; no flags, no grid-wide wait - the next call polls the words it reads.
+    Batches of at most `tagged_rows` rows (default 16: every fused call) use the tagged hand-over instead
+    (B200Q_GATHER_TAGGED): three more row buffers of 8-byte words {two outputs, call number} and a call
+    counter of their own; no flags, no grid-wide wait - the next call (or, above 16 rows, the collect
+    kernel) polls the words it reads.  Above 16 rows the flags are faster (twice the bytes to push and to
+    poll: 3.11 vs 2.91 ms at M = 32 on two GPUs), so the default leaves those batches on flags.
     Measured on two B200s over NVLink (128-linear decode stack): 1.71 -> 1.51 ms per step at M = 1,
     1.80 -> 1.66 ms at M = 8.
     """
@@ -137,7 +139,7 @@ class PeerGather:
         assert 1 <= world <= 8 and len(ptrs) == world
         self.world, self.rank, self.ptrs = world, rank, list(ptrs)
         self.max_rows, self.max_cols = max_rows, max_cols
-        self.tagged_rows = min(tagged_rows, 16, max_rows)
+        self.tagged_rows = min(tagged_rows, max_rows)
         self._tag_prev = None  # (rows, row width, took its activations from outside) of the latest tagged call
         self.device = torch.device(device)
         self._owned = None     # this rank's region, if allocated by create()
@@ -151,7 +153,7 @@ class PeerGather:
 
     @staticmethod
     def region_bytes(max_rows: int, max_cols: int, tagged_rows: int = 16) -> int:
-        tagged_rows = min(tagged_rows, 16, max_rows)
+        tagged_rows = min(tagged_rows, max_rows)
         return PeerGather._tag_off(max_rows, max_cols) + PeerGather.TAG_BUFFERS * tagged_rows * (max_cols // 2) * 8
 
     @classmethod
@@ -257,8 +259,10 @@ class PeerGather:
                 if full is None:
                     full = torch.empty(M, N_full, dtype=self.dtype, device=self.device)
                     self._full[(M, N_full, self.dtype)] = full
-                self.push(shard, layer)
-                self.collect(full, M, N_full)
+                self.push(shard, layer, tagged)
+                self.collect(full, M, N_full, tagged)
+            if tagged:
+                self._tag_prev = (M, N_full, False)  # collected: nothing of it is left to wait for
             return full
         if isinstance(x, GatheredRow):
             lda, a_ptr = x.row_stride, None
@@ -284,9 +288,10 @@ class PeerGather:
         _lib.check(st)
         return GatheredRow(M, N_full, 0, N_full, tagged)
 
-    def push(self, shard: torch.Tensor, layer: "ShardedQuantizedLinear"):
-        """First half of a gathered call with more than 16 rows: this rank's shard [M, N/G] to every rank."""
-        g = self._desc(layer.out_features, layer.n0)
+    def push(self, shard: torch.Tensor, layer: "ShardedQuantizedLinear", tagged: bool = False):
+        """First half of a gathered call with more than 16 rows: this rank's shard [M, N/G] to every rank
+        (dense rows + flags, or tagged words)."""
+        g = self._desc(layer.out_features, layer.n0, tagged)
         with torch.cuda.device(self.device):
             ws = ops.get_workspace(self.device, 1 << 20)
             _lib.check(_lib.load().b200q_gather_push(
