@@ -26,7 +26,9 @@ constexpr int BLOCK_K = 512;
 
 // ---- workspace -----------------------------------------------------------------------------
 // [0, 256)                    : status header, int32[64]; word 0 = device error code,
-//                               words 1..3 = where it was raised
+//                               words 1..3 = where it was raised; word 8 = arrival counter of a
+//                               gather launch's CTAs; words 16, 17 = the counters of a launch that
+//                               fetches its activations from host memory (all zero between launches)
 // [256, 256 + cnt_bytes)      : int32 arrival counters, one per 16-column tile
 // [256 + cnt_bytes, ...)      : fp32 split-K partial sums [M][N]
 // Everything past the header must be zero when a GEMM starts; the kernels leave it zero.

@@ -59,6 +59,7 @@ class QuantizedLinear(nn.Module):
         )
         self.register_buffer("layout_version", torch.tensor(packing.LAYOUT_VERSION, dtype=torch.int32))
         self._ws_need = {}  # workspace bytes per batch size M (filled on first use)
+        self._host_calls = {}  # prepared b200q_gemm_host calls per (buffers, stream), see ops.linear_forward_host
 
     # -- loading ---------------------------------------------------------------------
     def load_and_quantize(self, weight: torch.Tensor):
@@ -155,7 +156,7 @@ class QuantizedLinear(nn.Module):
             out_host = torch.empty(x_host.shape[0], self.out_features, dtype=self.act_torch_dtype).pin_memory()
         return ops.linear_forward_host(x_host, out_host, self.quantized_weight.data, self.scales.data,
                                        self.w_dtype.code, self.zero_point, self.group_size, self.in_features,
-                                       self.out_features, self._ws_need)
+                                       self.out_features, self._ws_need, self._host_calls)
 
     def forward_swiglu_cast(self, x: torch.Tensor, num_per_channels: int = 128, swiglu_clamp_value=None):
         """For a gate_up projection (out_features = 2 * hidden, gate columns first): this layer's GEMM

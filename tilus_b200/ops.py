@@ -147,7 +147,8 @@ _host_staging: dict = {}
 
 
 def linear_forward_host(x_host: torch.Tensor, out_host: torch.Tensor, bq: torch.Tensor, scales: torch.Tensor,
-                        code: int, zero_point: int, group_size: int, K: int, N: int, ws_need: dict) -> torch.Tensor:
+                        code: int, zero_point: int, group_size: int, K: int, N: int, ws_need: dict,
+                        prepared: dict) -> torch.Tensor:
     """QuantizedLinear.forward_host: activations and result live in host memory (pinned, so that the
     copies are asynchronous).  One library call queues copy-in, GEMM and copy-out on the current
     stream of the layer's device; the caller synchronises that stream before reading ``out_host``."""
@@ -158,7 +159,7 @@ def linear_forward_host(x_host: torch.Tensor, out_host: torch.Tensor, bq: torch.
     stream = torch._C._cuda_getCurrentRawStream(dev.index)
     key = (x_host.data_ptr(), out_host.data_ptr(), x_host.shape, x_host.stride(), out_host.stride(), x_host.dtype,
            out_host.dtype, stream, bq.data_ptr(), scales.data_ptr())
-    hit = ws_need.get(key)
+    hit = prepared.get(key)
     if hit is not None:
         if torch._C._cuda_getDevice() == dev.index:
             st = hit[0](*hit[1])
@@ -203,11 +204,10 @@ def linear_forward_host(x_host: torch.Tensor, out_host: torch.Tensor, bq: torch.
         st = lib.b200q_gemm_host(*args)
     if st != 0:
         _lib.check(st)
-    if len(ws_need) > 256:  # a caller that keeps changing buffers: start over rather than grow
-        for k in [k for k in ws_need if isinstance(k, tuple)]:
-            del ws_need[k]
+    if len(prepared) > 256:  # a caller that keeps changing buffers: start over rather than grow
+        prepared.clear()
     # the entry keeps the device buffers it names alive (a later, larger request replaces them in the pools)
-    ws_need[key] = (lib.b200q_gemm_host, args, ws, stage)
+    prepared[key] = (lib.b200q_gemm_host, args, ws, stage)
     return out_host
 
 
