@@ -116,6 +116,32 @@ def test_forward_host_bf16(M):
         out.zero_()
 
 
+def test_forward_host_replays_from_a_cuda_graph_with_fresh_inputs():
+    """Host calls captured into a CUDA graph: every replay reads what the pinned activation buffer holds
+    at that time (the kernel fetches it over PCIe, nothing is baked in) and writes the pinned result."""
+    k, n, M = 1024, 512, 2
+    layer = QuantizedLinear(float16, D.int4b, 128, k, n).cuda()
+    layer.load_and_quantize(torch.randn(n, k, generator=torch.Generator().manual_seed(5)))
+    x = torch.zeros(M, k, dtype=torch.float16).pin_memory()
+    outs = [torch.zeros(M, n, dtype=torch.float16).pin_memory() for _ in range(3)]
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for o in outs:
+            layer.forward_host(x, o)  # warm-up on the capture stream
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for o in outs:
+                layer.forward_host(x, o)
+        for seed in (6, 7):
+            x.copy_(torch.randn(M, k, generator=torch.Generator().manual_seed(seed)).half())
+            graph.replay()
+            side.synchronize()
+            want = layer(x.cuda()).cpu().float()
+            for o in outs:
+                assert float((o.float() - want).abs().max()) <= 2e-3 * float(want.abs().max())
+
+
 @pytest.mark.parametrize("M", [1, 3, 16])
 def test_forward_host_back_to_back_calls_keep_their_order(M):
     """Consecutive host calls overlap on the GPU (a call with pinned activations does not wait for the
