@@ -111,8 +111,9 @@ int b200q_gemm(const void* a, int lda, const void* bq, const void* scales, void*
  * written straight to pinned c_host): no separate operation at all - the first CTAs of the GEMV kernel
  * fetch the rows, the others wait for them (bounded, status[1] = 9), and consecutive such calls overlap on
  * the GPU: a call does not wait for the kernel before it until it writes its outputs, which therefore
- * still land in call order.  For that, `a_staging` and `workspace` must belong to the host calls of this
- * stream alone: no other kernel may read `a_staging` while such calls are queued. */
+ * still land in call order (a call only starts early when the previous b200q_gemm_host call of this
+ * thread with the same `stream` and `a_staging` was such a call too).  `a_staging` must belong to the
+ * b200q_gemm_host calls of one thread and stream, `workspace` to this stream's calls of this library. */
 int b200q_gemm_host(const void* a_host, int lda, const void* bq, const void* scales, void* c_host, int ldc, int M,
                     int N, int K, int wtype, int zero_point, int group, int act_dtype, void* a_staging,
                     void* c_staging, void* workspace, size_t workspace_bytes, void* stream);

@@ -116,6 +116,29 @@ def test_forward_host_bf16(M):
         out.zero_()
 
 
+def test_forward_host_decode_call_behind_a_larger_batch():
+    """A decode-batch host call queued directly behind a host call for a larger batch: the second starts
+    while the first still runs, so the two must not share a staging buffer (the operator layer keeps
+    one per kind)."""
+    k, n = 2048, 2048
+    layer = QuantizedLinear(float16, D.int4b, 128, k, n).cuda()
+    layer.load_and_quantize(torch.randn(n, k, generator=torch.Generator().manual_seed(8)))
+    big = torch.randn(64, k, generator=torch.Generator().manual_seed(9)).half().pin_memory()
+    small = torch.randn(1, k, generator=torch.Generator().manual_seed(10)).half().pin_memory()
+    out_big = torch.zeros(64, n, dtype=torch.float16).pin_memory()
+    out_small = torch.zeros(1, n, dtype=torch.float16).pin_memory()
+    want_big = layer(big.cuda()).cpu().float()
+    want_small = layer(small.cuda()).cpu().float()
+    for _ in range(5):
+        layer.forward_host(big, out_big)
+        layer.forward_host(small, out_small)
+        layer.forward_host(small, out_small)
+        torch.cuda.synchronize()
+        assert float((out_big.float() - want_big).abs().max()) <= 2e-3 * float(want_big.abs().max())
+        assert float((out_small.float() - want_small).abs().max()) <= 2e-3 * float(want_small.abs().max())
+        out_big.zero_(); out_small.zero_()
+
+
 def test_forward_host_replays_from_a_cuda_graph_with_fresh_inputs():
     """Host calls captured into a CUDA graph: every replay reads what the pinned activation buffer holds
     at that time (the kernel fetches it over PCIe, nothing is baked in) and writes the pinned result."""

@@ -538,7 +538,7 @@ static int fill_gather_args(const b200q_gather_t* gather, int M, int N, void* wo
 static int run_stream(const void* a, int lda, const void* bq, const void* scales, void* c, int ldc, int M, int N,
                       int K, int var, int group, int act, void* workspace, size_t ws_bytes, cudaStream_t stream,
                       const b200q_plan_t& pl, const b200q_gather_t* gather = nullptr, const void* a_host = nullptr,
-                      int lda_host = 0) {
+                      int lda_host = 0, bool staging_released = false) {
   // a_host: device-side address of activations in pinned host memory (row stride lda_host); `a` is then
   // the dense [M, K] device staging the kernel's first CTAs fill (see StreamParams)
   const int bits = var_bits(var);
@@ -599,7 +599,9 @@ static int run_stream(const void* a, int lda, const void* bq, const void* scales
     p.c = reinterpret_cast<__half*>(c) + (size_t)m0 * ldc;
     p.M = mc;
     p.T_own = stream_tiles_owned(mc, p.NT, p.CPC);
-    p.nowait = (a_host && p.S == 1 && p.T_own * p.CPC == p.NT) ? 1 : 0;
+    // (staging_released: the previous user of the staging buffer on this stream lets go of it before it
+    // releases its successor - only then may this launch write it without waiting)
+    p.nowait = (a_host && staging_released && p.S == 1 && p.T_own * p.CPC == p.NT) ? 1 : 0;
     const int smem = stream_smem(mc, p.KBc * 512, bits, pl.stages, p.T_own);
     if (smem > device_info().max_smem) return ST_UNSUPPORTED;
     cudaError_t e = stream_launch(var, p, stream_mt(mc), smem, stream);
@@ -800,6 +802,25 @@ int b200q_gemm(const void* a, int lda, const void* bq, const void* scales, void*
 // is written exactly once, goes straight to the host buffer when that is pinned memory the GPU
 // can address (the kernel's stores are the transfer); otherwise through the second staging
 // buffer and a copy.
+// Who used a staging buffer last on a stream, as far as this thread's b200q_gemm_host calls know: a
+// decode launch that fetches its own activations has finished reading the buffer by the time its
+// successor can start; every other kernel reads it until it ends.  (Within a captured graph the order
+// of launches is the order of capture; the first launch of a graph follows everything before it.)
+struct StagingUse { cudaStream_t stream; const void* buf; bool released; };
+static bool staging_released_by_last_use(cudaStream_t st, const void* buf, bool now_released) {
+  static thread_local StagingUse uses[8];
+  static thread_local int next = 0;
+  for (StagingUse& u : uses)
+    if (u.stream == st && u.buf == buf && u.buf != nullptr) {
+      const bool was = u.released;
+      u.released = now_released;
+      return was;
+    }
+  uses[next] = {st, buf, now_released};
+  next = (next + 1) % 8;
+  return false;  // unknown history: wait
+}
+
 int b200q_gemm_host(const void* a_host, int lda, const void* bq, const void* scales, void* c_host, int ldc, int M,
                     int N, int K, int wtype, int zero_point, int group, int act_dtype, void* a_staging,
                     void* c_staging, void* workspace, size_t workspace_bytes, void* stream) {
@@ -831,12 +852,14 @@ int b200q_gemm_host(const void* a_host, int lda, const void* bq, const void* sca
           cattr.devicePointer && (((uintptr_t)cattr.devicePointer) & 15) == 0) {
         if (!bq || !scales) return ST_INVALID_ARG;
         if ((((uintptr_t)bq) & 15) || lda < K) return ST_INVALID_ARG;
+        const bool released = staging_released_by_last_use(st, a_staging, true);
         return run_stream(a_staging, K, bq, scales, cattr.devicePointer, ldc, M, N, K, var, group, act_dtype, workspace,
-                          workspace_bytes, st, pl, nullptr, a_mapped, lda);
+                          workspace_bytes, st, pl, nullptr, a_mapped, lda, released);
       }
       (void)cudaGetLastError();
     }
   }
+  (void)staging_released_by_last_use(st, a_staging, false);  // what follows reads the buffer until it ends
   if (a_mapped)
     e = host_fetch_launch(a_mapped, lda, a_staging, M, K, st);
   else

@@ -194,10 +194,14 @@ def linear_forward_host(x_host: torch.Tensor, out_host: torch.Tensor, bq: torch.
         if ws is None or ws.numel() < need:
             ws = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=dev)
             _workspaces[wkey] = ws
-        stage = _host_staging.get(wkey)
+        # Decode batches (the kernel's own CTAs fetch the activations and consecutive calls overlap) keep
+        # staging buffers of their own, so that a call for a larger batch in between does not make the
+        # next decode call wait for it (the library only lets a call start early behind a call of its kind).
+        skey = wkey + (M <= 16,)
+        stage = _host_staging.get(skey)
         if stage is None or stage[0].numel() < M * K or stage[1].numel() < M * N:
             stage = (torch.empty(M * K, dtype=torch.int16, device=dev), torch.empty(M * N, dtype=torch.int16, device=dev))
-            _host_staging[wkey] = stage
+            _host_staging[skey] = stage
         args = (x_host.data_ptr(), x_host.stride(0), bq.data_ptr(), scales.data_ptr(), out_host.data_ptr(),
                 out_host.stride(0), M, N, K, code, zero_point, group_size, act, stage[0].data_ptr(),
                 stage[1].data_ptr(), ws.data_ptr(), ws.numel(), stream)
